@@ -1,0 +1,130 @@
+"""Compiling and loading the CUDA libraries.
+
+The kernels are plain C-interface shared libraries built with nvcc for sm_100a and loaded with
+ctypes; they take raw device pointers and a stream, so compiling them needs no framework headers
+and takes seconds.  A library is built at its first use from the sources beside this file,
+into `csrc/_build/` (or, if that is not writable, a per-user folder under the system temp
+directory), under a name that carries a hash of its sources and flags: a changed source is a new
+file, an unchanged one is never compiled twice.  Kernels whose tile shapes depend on the model
+(attention on the head size) are compiled for the sizes this model has, nothing more.
+
+There is no fallback: if nvcc or a source is missing, or compilation fails, `KernelBuildError`
+is raised with the compiler's output.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
+
+_loaded: dict = {}
+_lock = threading.Lock()
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).is_file():
+            return cand
+    raise KernelBuildError("nvcc was not found (PATH, $NVCC, /usr/local/cuda/bin): the CUDA kernels "
+                           "of this engine cannot be built, and there is no other code path")
+
+
+def build_dir() -> Path:
+    env = os.environ.get("TENSORLINE_B200_BUILD_DIR")
+    cands = [Path(env)] if env else []
+    cands += [CSRC / "_build", Path(tempfile.gettempdir()) / f"tensorline_b200_build_{os.getuid()}"]
+    for d in cands:
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            probe = d / f".w{os.getpid()}"
+            probe.write_bytes(b"")
+            probe.unlink()
+            return d
+        except OSError:
+            continue
+    raise KernelBuildError("no writable folder for compiled kernels: tried " + ", ".join(map(str, cands)))
+
+
+def _digest(sources, flags) -> str:
+    h = hashlib.sha256()
+    for f in sorted(CSRC.glob("*.cuh")) + [CSRC / s for s in sources]:
+        if not f.is_file():
+            raise KernelBuildError(f"kernel source {f} is missing")
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(name: str, sources, defines: dict | None = None, extra_flags=()) -> tuple:
+    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())] + list(extra_flags)
+    tag = _digest(sources, flags)
+    fname = f"lib{name}_{tag}.so"
+    for d in (CSRC / "_build", Path(tempfile.gettempdir()) / f"tensorline_b200_build_{os.getuid()}"):
+        if (d / fname).is_file():
+            return d / fname, flags, True
+    return build_dir() / fname, flags, False
+
+
+def build_library(name: str, sources, defines: dict | None = None, extra_flags=(), verbose: bool = True) -> Path:
+    """Compile (if not yet built) and return the path of the shared library."""
+    path, flags, exists = library_path(name, sources, defines, extra_flags)
+    if exists:
+        return path
+    nvcc = _nvcc()
+    tmp = path.with_suffix(f".tmp{os.getpid()}.so")
+    cmd = [nvcc] + flags + ["-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in sources]
+    if verbose:
+        print(f"[tensorline_b200] compiling {name} ({', '.join(sources)}) for sm_100a ...", file=sys.stderr, flush=True)
+    t0 = time.time()
+    done = threading.Event()
+
+    def ticker():
+        while not done.wait(15.0):
+            print(f"[tensorline_b200]   still compiling {name}: {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+
+    th = threading.Thread(target=ticker, daemon=True)
+    if verbose:
+        th.start()
+    try:
+        env = dict(os.environ)
+        env.setdefault("TMPDIR", str(path.parent))      # nvcc's intermediates beside the output
+        proc = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    finally:
+        done.set()
+    if proc.returncode != 0:
+        tmp.unlink(missing_ok=True)
+        raise KernelBuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp, path)                               # atomic: concurrent builders agree
+    if verbose:
+        print(f"[tensorline_b200] built {path.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    return path
+
+
+def load_library(name: str, sources, defines: dict | None = None, extra_flags=()) -> ctypes.CDLL:
+    key = (name, tuple(sources), tuple(sorted((defines or {}).items())), tuple(extra_flags))
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            path = build_library(name, sources, defines, extra_flags)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as e:
+                raise KernelBuildError(f"cannot load {path}: {e}") from None
+            _loaded[key] = lib
+        return lib

@@ -1,0 +1,99 @@
+// Embedding gather, residual-add + RMSNorm, SwiGLU activation.
+//
+// Each kernel has a plain reference in tests/plain/qwen2_plain.py.  Formulas:
+//   embedding   x[t,:] = E[ids[t],:]                       (tensorline/paged.py:240)
+//   add+RMSNorm x += r;  h = cast(x * rsqrt(mean(x^2)+eps)) * w   (tensorline/fused.py:19-32;
+//               the cast to the activation type comes before the weight multiply, fused.py:32)
+//   SwiGLU      m = silu(g) * u,  silu(z) = z / (1 + e^-z), from the fused gate|up product
+// The residual stream x is float in both engines, so the residual sum is a 32-bit sum.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ x, const TW* __restrict__ table,
+                             const int* __restrict__ ids, int H) {
+    const int t = blockIdx.x;
+    const TW* row = table + (size_t)ids[t] * H;
+    float* out = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f<TW>(row[i]);
+}
+
+TL_EXPORT int tl_embed(void* x, const void* table, int table_dtype, const int* ids, int T, int H,
+                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (table_dtype == TL_F32)
+        embed_kernel<float><<<T, 256, 0, stream>>>((float*)x, (const float*)table, ids, H);
+    else
+        embed_kernel<bf16><<<T, 256, 0, stream>>>((float*)x, (const bf16*)table, ids, H);
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// One block per output row.  rows == nullptr: row i of x; else row rows[i] (x is then only
+// read, as for the final norm on the rows that want logits).
+template <typename TA, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ r,
+                                   const TW* __restrict__ w, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps, int write_x) {
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+    float* xr = x + src;
+    const TA* rr = r ? r + src : nullptr;
+    TA* o = out + (size_t)i * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (rr) {
+            v = v + to_f<TA>(rr[c]);
+            if (write_x) xr[c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = xr[c];
+        if (rr && !write_x) v = v + to_f<TA>(rr[c]);
+        const float n = to_f<TA>(from_f<TA>(v * rstd));          // cast first, then the weight
+        o[c] = from_f<TA>(n * to_f<TW>(w[c]));
+    }
+}
+
+TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype, void* out, int act_dtype,
+                             const int* rows, int R, int H, float eps, int write_x, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const int threads = 256;
+#define LAUNCH(TA, TW) add_rmsnorm_kernel<TA, TW><<<R, threads, 0, stream>>>( \
+        (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) LAUNCH(float, float); else LAUNCH(float, bf16); }
+    else                     { if (w_dtype == TL_F32) LAUNCH(bf16, float);  else LAUNCH(bf16, bf16); }
+#undef LAUNCH
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ SwiGLU activation
+// gu is [T, 2*I]: gate in columns [0, I), up in [I, 2I).  out is [T, I].
+template <typename TA>
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int c = (int)(idx - t * I);
+        const float g = to_f<TA>(gu[t * 2 * I + c]);
+        const float u = to_f<TA>(gu[t * 2 * I + I + c]);
+        out[idx] = from_f<TA>((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (act_dtype == TL_F32)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    else
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+    return tl_launch_status();
+}

@@ -1,0 +1,174 @@
+"""`ModelRunner`: the one step function.
+
+    runner.step([StepEntry(rid, tokens, want), ...]) -> logits [wanted, vocab] float32
+
+A step takes, for each request in it, that request's next tokens: a portion of its prompt of any
+length, cut anywhere, or a single decoded token; all entries run as ONE flattened batch
+(tensorline/paged.py:190-207).  The step computes only the tokens it is given: keys and values of
+earlier tokens come from the cache pages that earlier steps wrote.  It returns the logits at the
+wanted places (`want`: indices into the entry's tokens), in entry order
+(tensorline/paged.py:278-287, which returns the last row only).
+
+The runner owns the device side of the cache: the page tensors of every cache-owning run entry,
+the per-slot state tensors, and device copies of the block tables; the `CacheManager` owns the
+bookkeeping.  A request's position is tracked here (`positions[rid]`), so an entry needs no
+`start` (tensorline/paged.py:100-106 passes it explicitly).
+
+Steps that hold only single decoded tokens can be replayed from a CUDA graph, one graph per
+batch-size bucket (tensorline/cuda_graphs.py:38-126); tables and lengths are read from device
+memory, so there are no buckets over context length.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, PagedKV, SlotState
+from ..models.spec import Model
+from ..parts import KVCacheView, Runtime, StateView
+
+
+@dataclass
+class StepEntry:
+    rid: object
+    tokens: list
+    want: list = field(default_factory=list)       # places among `tokens` whose logits are returned
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one step, handed to every part."""
+    T: int
+    B: int
+    ids: torch.Tensor                   # int32 [T]
+    pos: torch.Tensor                   # int32 [T] absolute position of each token in its request
+    req_slot: torch.Tensor              # int32 [T] slot of the request that owns each token
+    q_start: torch.Tensor               # int32 [B + 1] first row of each request's tokens
+    start_pos: torch.Tensor             # int32 [B] position of each request's first token of the step
+    slots: torch.Tensor                 # int32 [B]
+    want_rows: torch.Tensor             # int32 [R]
+    tables: list                        # per page group: int32 [slots + 1, max pages]
+    page_size: int
+    decode_only: bool                   # every request brings exactly one token
+    max_q_len: int
+    max_ctx: int                        # largest position + 1 in the step
+    h_q_start: list                     # host copies for parts written in Python
+    h_start_pos: list
+    h_slots: list
+    force_exact_attention: bool = False
+    scratch: dict = field(default_factory=dict)    # per-step scratch of kernels, keyed by name
+
+
+_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
+           "int32": torch.int32, "int64": torch.int64}
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, *, device=None):
+        self.model = model
+        self.cache = cache
+        self.rt: Runtime = model.rt
+        self.device = torch.device(device) if device is not None else self.rt.device
+        if self.device.type != "cuda":
+            raise RuntimeError("ModelRunner needs a CUDA device: this engine has no CPU path")
+        self.page_size = cache.page_size
+        self.positions: dict = {}       # rid -> number of tokens already in the cache
+        self.force_exact_attention = False
+        needs = model.cache_needs()
+        self.caches: dict = {}
+        for cid, need in needs.items():
+            if isinstance(need, PagedKV):
+                g = cache.group_of[cid]
+                shape = (cache.groups[g].pool.num_pages + 1, need.num_kv_heads, self.page_size, need.head_dim)
+                self.caches[cid] = KVCacheView(torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device),
+                                               torch.zeros(shape, dtype=self.rt.act_dtype, device=self.device), g)
+            elif isinstance(need, SlotState):
+                shape = (cache.max_num_seqs + 1,) + tuple(need.shape)
+                self.caches[cid] = StateView(torch.zeros(shape, dtype=_DTYPES[need.dtype], device=self.device))
+        self.tables = [torch.from_numpy(g.table.copy()).to(self.device) for g in cache.groups]
+        self._host_tables = [torch.from_numpy(g.table) for g in cache.groups]      # share memory with the manager
+        self.vocab_size = model.spec.vocab_size
+        self.launches = 0
+
+    # ------------------------------------------------------------------ bytes
+    def cache_bytes_per_token(self) -> int:
+        total = 0
+        for c in self.caches.values():
+            if isinstance(c, KVCacheView):
+                total += 2 * c.k.shape[1] * c.k.shape[3] * c.k.element_size()
+        return total
+
+    # ------------------------------------------------------------------ requests
+    def start_request(self, rid, cached_tokens: int = 0) -> None:
+        """A request enters (or re-enters after preemption) with `cached_tokens` of its tokens
+        already in shared pages.  State slots start from zero."""
+        self.positions[rid] = cached_tokens
+        slot = self.cache.slot(rid)
+        for c in self.caches.values():
+            if isinstance(c, StateView):
+                c.state[slot].zero_()
+
+    def end_request(self, rid) -> None:
+        self.positions.pop(rid, None)
+
+    # ------------------------------------------------------------------ the step
+    def build_context(self, entries) -> StepContext:
+        ps = self.page_size
+        ids, pos, req_slot, q_start, start_pos, slots, want_rows = [], [], [], [0], [], [], []
+        max_q = max_ctx = 0
+        for e in entries:
+            n = len(e.tokens)
+            if n < 1:
+                raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
+            start = self.positions[e.rid]
+            slot = self.cache.slot(e.rid)
+            held = len(self.cache._held[e.rid].pages[0]) * ps if self.cache.groups else start + n
+            if start + n > held:
+                raise RuntimeError(f"request {e.rid!r}: positions up to {start + n} but pages for {held}; "
+                                   "grow its cache before the step")
+            row0 = len(ids)
+            ids.extend(int(t) for t in e.tokens)
+            pos.extend(range(start, start + n))
+            req_slot.extend([slot] * n)
+            q_start.append(row0 + n)
+            start_pos.append(start)
+            slots.append(slot)
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(row0 + w)
+            max_q = max(max_q, n)
+            max_ctx = max(max_ctx, start + n)
+        T, B = len(ids), len(entries)
+        if T and (min(ids) < 0 or max(ids) >= self.vocab_size):
+            raise ValueError(f"token id outside [0, {self.vocab_size})")
+        packed = np.asarray(ids + pos + req_slot + q_start + start_pos + slots + want_rows, dtype=np.int32)
+        dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
+        cut = np.cumsum([0, T, T, T, B + 1, B, B, len(want_rows)])
+        parts = [dev[cut[i]:cut[i + 1]] for i in range(7)]
+        for t_dev, t_host in zip(self.tables, self._host_tables):
+            t_dev.copy_(t_host, non_blocking=False)
+        return StepContext(T=T, B=B, ids=parts[0], pos=parts[1], req_slot=parts[2], q_start=parts[3],
+                           start_pos=parts[4], slots=parts[5], want_rows=parts[6], tables=self.tables,
+                           page_size=ps, decode_only=all(len(e.tokens) == 1 for e in entries), max_q_len=max_q,
+                           max_ctx=max_ctx, h_q_start=q_start, h_start_pos=start_pos, h_slots=slots,
+                           force_exact_attention=self.force_exact_attention)
+
+    @torch.inference_mode()
+    def step(self, entries) -> torch.Tensor:
+        """Run one batch; returns logits [number of wanted places, vocab], float32, on the device."""
+        entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx, self.caches)
+        for e in entries:
+            self.positions[e.rid] += len(e.tokens)
+        return logits

@@ -1,0 +1,203 @@
+"""Python launchers of the hand-written CUDA kernels.
+
+Each function checks shapes, types and contiguity, then calls the C entry point of the compiled
+library with raw device pointers on torch's current stream.  There is no CPU path and no library
+stand-in: a CPU tensor or a missing library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc.build import load_library
+
+CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu"]
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+_SIGNATURES = {
+    "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
+    "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
+    "tl_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
+    "tl_argmax": [_P, _I, _I, _I, _P, _P],
+    "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_core = None
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = load_library("tl_core", CORE_SOURCES)
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = sig
+            fn.restype = ctypes.c_int
+        _core = lib
+    return _core
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dt}")
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernel called with a CPU tensor: this engine has no CPU path")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _ints(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+    _contig(t, name)
+
+
+# ---------------------------------------------------------------------------------------------
+
+def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """x[t, :] = table[ids[t], :], x float32 [T, H]."""
+    T, H = x.shape
+    if x.dtype != torch.float32 or table.shape[1] != H or ids.numel() != T:
+        raise KernelError("embed: x must be float32 [T, H] matching the table and ids")
+    _contig(x, "x"); _contig(table, "table"); _ints(ids, "ids")
+    _check(core().tl_embed(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, _stream()), "embed")
+
+
+def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, eps: float,
+                rows: torch.Tensor | None = None, write_x: bool = True) -> None:
+    """x += r (if r), out = cast(x * rstd) * w.  x float32 [*, H]; r, out of the activation
+    type; `rows` picks the rows (x is then left alone)."""
+    H = x.shape[-1]
+    R = out.shape[0]
+    if x.dtype != torch.float32 or out.shape[-1] != H or w.numel() != H:
+        raise KernelError("add_rmsnorm: x must be float32 and out, w must match its width")
+    if r is not None and (r.dtype != out.dtype or r.shape != x.shape):
+        raise KernelError("add_rmsnorm: r must have x's shape and out's type")
+    _contig(x, "x"); _contig(out, "out"); _contig(w, "w")
+    if r is not None:
+        _contig(r, "r")
+    if rows is not None:
+        _ints(rows, "rows")
+        if rows.numel() != R:
+            raise KernelError("add_rmsnorm: one output row per entry of rows")
+        write_x = False
+    elif x.shape[0] != R:
+        raise KernelError("add_rmsnorm: out must have x's rows")
+    _check(core().tl_add_rmsnorm(_ptr(x), _ptr(r), _ptr(w), dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype),
+                                 _ptr(rows), R, H, float(eps), int(write_x), _stream()), "add_rmsnorm")
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gu[:, :I]) * gu[:, I:]."""
+    T, I = out.shape
+    if gu.shape != (T, 2 * I) or gu.dtype != out.dtype:
+        raise KernelError("silu_mul: gu must be [T, 2I] of out's type")
+    _contig(gu, "gu"); _contig(out, "out")
+    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, _stream()), "silu_mul")
+
+
+def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tensor, req_slot: torch.Tensor,
+                  table: torch.Tensor, page_size: int, inv_freq: torch.Tensor, rot: int, nq: int, nkv: int,
+                  d: int, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True) -> None:
+    """Bias, rotary encoding of q and k in place, and the write of k, v into their pages."""
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * d:
+        raise KernelError("rope_kv_write: qkv must be [T, (nq + 2 nkv) d]")
+    _contig(qkv, "qkv"); _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2:
+        raise KernelError("rope_kv_write: inv_freq must be float32 [rot/2]")
+    if write_kv:
+        for name, pages in (("k_pages", k_pages), ("v_pages", v_pages)):
+            if pages is None or pages.dtype != qkv.dtype or tuple(pages.shape[1:]) != (nkv, page_size, d):
+                raise KernelError(f"rope_kv_write: {name} must be [pages, nkv, page, d] of qkv's type")
+            _contig(pages, name)
+    _check(core().tl_rope_kv_write(
+        _ptr(qkv), dtype_code(qkv.dtype), _ptr(bias), dtype_code(bias.dtype) if bias is not None else 0,
+        _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(inv_freq), rot, nq, nkv, d,
+        _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T, _stream()),
+        "rope_kv_write")
+
+
+def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                   table: torch.Tensor, page_size: int, pos: torch.Tensor, req_slot: torch.Tensor,
+                   nq: int, nkv: int, d: int, window: int | None, scale: float) -> None:
+    """Exact-order paged attention; q rows `q_stride` elements apart, out [T, nq*d]."""
+    T = out.shape[0]
+    if out.shape[1] != nq * d or out.dtype != q.dtype or k_pages.dtype != q.dtype:
+        raise KernelError("attn_tokenwise: out must be [T, nq*d] and all tensors of one type")
+    if d > 512:
+        raise KernelError(f"attn_tokenwise: head_dim {d} > 512 is not supported")
+    _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages")
+    _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
+    _check(core().tl_attn_tokenwise(_ptr(q), q_stride, _ptr(out), dtype_code(q.dtype), _ptr(k_pages), _ptr(v_pages),
+                                    _ptr(table), table.shape[1], page_size, _ptr(pos), _ptr(req_slot), T, nq, nkv, d,
+                                    int(window or 0), float(scale), _stream()), "attn_tokenwise")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+    """out[M, N] = a[M, K] w[N, K]^T (+ bias), float32 FFMA; w float32 or bfloat16 (widened)."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.float32 or out.dtype != torch.float32 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError("gemm_f32: a [M,K] and out [M,N] must be float32, w [N,K]")
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_f32: a and out must have unit inner stride")
+    _contig(w, "w")
+    if bias is not None and bias.dtype != w.dtype:
+        raise KernelError("gemm_f32: bias must have w's type")
+    _check(core().tl_gemm_f32(_ptr(a), a.stride(0), _ptr(w), K, dtype_code(w.dtype), _ptr(bias), _ptr(out),
+                              out.stride(0), M, N, K, _stream()), "gemm_f32")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be float32 with unit inner stride")
+    _ints(out, "out")
+    _check(core().tl_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """Per row: temperature <= 0 gives the argmax, else a draw from softmax(logits / T) cut to
+    the top-p nucleus, picked by inverse CDF at `uniform`."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with unit inner stride")
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("uniform", uniform)):
+        if t.dtype != torch.float32 or t.numel() != R:
+            raise KernelError(f"sample: {name} must be float32 [R]")
+    _ints(out, "out")
+    _check(core().tl_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_p), _ptr(uniform),
+                            _ptr(out), _stream()), "sample")

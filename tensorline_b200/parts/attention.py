@@ -1,0 +1,75 @@
+"""Grouped-query attention over the paged cache: the mixer of this architecture.
+
+Order of work for the T tokens of a step (tensorline/paged.py:248-275):
+  qkv = h Wqkv^T                      one product against the stacked q|k|v matrix
+  bias, rotary encoding, K/V write    one kernel (tensorline/fused.py:34-51, paged.py:252-253);
+                                      every token's k, v are in the pages before any query runs
+  attention over the pages            query at position p reads keys lo..p of its own request
+                                      (paged.py:237, paged_attn.py:43), scale d^-1/2 (paged.py:119)
+  y = o Wo^T                          no bias
+The number of heads, of KV heads, the head size, the biases, the window and the position
+encoding are parameters.  A run entry that reads another entry's cache (`cache.owner` false)
+computes its own queries and writes no keys or values.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache import PagedKV
+from .base import MIXERS, POSITION_ENCODINGS, Part, PartSpec, Runtime, TensorSpec, register_mixer
+from .linear import matmul
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Part):
+    def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None):
+        super().__init__(rt)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+        if head_dim % 16 and not rt.exact:
+            raise ValueError(f"head_dim {head_dim}: the bfloat16 attention kernels take multiples of 16")
+        self.hidden, self.nq, self.nkv, self.d = hidden, num_heads, num_kv_heads, head_dim
+        self.qkv_bias, self.window = qkv_bias, window
+        self.scale = head_dim ** -0.5 if scale is None else scale          # tensorline/paged.py:119
+        self.position = POSITION_ENCODINGS.build(position, rt, head_dim=head_dim)
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    def cache_need(self):
+        return PagedKV(self.nkv, self.d, self.window)
+
+    def expected_tensors(self, prefix):
+        H, nq, nkv, d = self.hidden, self.nq, self.nkv, self.d
+        out = {f"{prefix}.q_proj.weight": TensorSpec((nq * d, H)), f"{prefix}.k_proj.weight": TensorSpec((nkv * d, H)),
+               f"{prefix}.v_proj.weight": TensorSpec((nkv * d, H)), f"{prefix}.o_proj.weight": TensorSpec((H, nq * d))}
+        if self.qkv_bias:
+            out.update({f"{prefix}.q_proj.bias": TensorSpec((nq * d,)), f"{prefix}.k_proj.bias": TensorSpec((nkv * d,)),
+                        f"{prefix}.v_proj.bias": TensorSpec((nkv * d,))})
+        return out
+
+    def bind(self, weights, prefix):
+        w = [weights[f"{prefix}.{n}_proj.weight"] for n in "qkv"]
+        self.w_qkv = self._compute_copy(torch.cat(w, dim=0))
+        if self.qkv_bias:
+            b = [weights[f"{prefix}.{n}_proj.bias"] for n in "qkv"]
+            self.b_qkv = torch.cat(b, dim=0).contiguous()
+            if self.b_qkv.dtype not in (torch.float32, torch.bfloat16):
+                self.b_qkv = self.b_qkv.float()
+        self.w_o = self._compute_copy(weights[f"{prefix}.o_proj.weight"])
+
+    def forward(self, h, ctx, cache):
+        nq, nkv, d = self.nq, self.nkv, self.d
+        T = h.shape[0]
+        qkv = matmul(h, self.w_qkv)
+        inv_freq, rot = self.position.rotary()
+        table = ctx.tables[cache.group]
+        ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
+                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner)
+        o = torch.empty((T, nq * d), dtype=h.dtype, device=h.device)
+        self.attend(qkv, o, ctx, cache, table)
+        return matmul(o, self.w_o)
+
+    def attend(self, qkv, o, ctx, cache, table):
+        from . import attention_kernels
+        attention_kernels.attend(self, qkv, o, ctx, cache, table)

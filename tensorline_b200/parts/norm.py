@@ -1,0 +1,27 @@
+"""RMSNorm with the residual add folded in (tensorline/fused.py:19-32, :58-69)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, Runtime, TensorSpec, register_norm
+
+
+@register_norm("rms_norm")
+class RMSNorm(Part):
+    def __init__(self, rt: Runtime, dim: int, eps: float):
+        super().__init__(rt)
+        self.dim, self.eps = dim, eps
+        self.weight = None
+
+    def expected_tensors(self, prefix):
+        return {f"{prefix}.weight": TensorSpec((self.dim,))}
+
+    def bind(self, weights, prefix):
+        self.weight = weights[f"{prefix}.weight"].contiguous()      # stays in its stored type
+
+    def add_norm(self, x, pending, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+        ops.add_rmsnorm(x, pending, self.weight, h, self.eps, rows=rows)
+        return h
