@@ -1,0 +1,464 @@
+// Tensor-core paged attention in bfloat16, compiled for one head size (-DHEAD_DIM=d, d % 16 == 0).
+//
+//   tl_attn_prefill   causal grouped-query flash attention for a step that holds prompt portions
+//                     (and, beside them, single decoded tokens).  Replaces the padded SDPA calls of
+//                     tensorline/paged.py:263-274: fresh prompts, resumed portions and decoded
+//                     tokens all read K and V from the pages, where this step's own tokens were
+//                     written first (paged.py:252-253).
+//   tl_attn_decode    split-KV paged decode attention: one query token per request, the keys of a
+//                     request cut into `splits` ranges that run as separate blocks, float partials
+//                     (max, sum, unnormalised output) in scratch memory, merged by
+//   tl_attn_combine.  Replaces tensorline/paged_attn.py:25-58, which is serial over the context.
+//
+// Both put the g = nq / nkv query heads that share a KV head into the rows of the MMA tile, so K
+// and V of a KV head are read once for the whole group (tensorline/paged_attn.py:33-35).  Scores,
+// running max, sum and the output accumulator are float; P is rounded to bfloat16 for the P V
+// product (paged_attn.py:56).  Pages are [page, kv head, offset, d]: a head's part of a page is
+// contiguous.  Tensor-core path: mma.sync.m16n8k16 (bf16 in, f32 accumulate) fed by ldmatrix from
+// shared-memory tiles that cp.async fills; rows of a tile are padded by 16 bytes, which keeps
+// ldmatrix free of bank conflicts for every head size.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<head size>"
+#endif
+#if HEAD_DIM % 16 != 0 || HEAD_DIM < 16 || HEAD_DIM > 256
+#error "HEAD_DIM must be a multiple of 16 in [16, 256]"
+#endif
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+constexpr int DP = D + 8;              // padded row, elements
+constexpr int CH = D / 8;              // 16-byte chunks per row
+constexpr int KBLK = D / 16;           // k-blocks of Q K^T
+constexpr int BM = 64;                 // query rows per block (prefill)
+constexpr int BN = 64;                 // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;      // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnArgs {
+    const bf16* q; int q_stride;       // q rows: token t at q + t * q_stride, head h at + h * D
+    bf16* out;                         // [T, nq * D]
+    const bf16* k_pages; const bf16* v_pages;
+    const int* table; int max_pages; int page_size;
+    const int* q_start; const int* start_pos; const int* slots;
+    int B, nq, nkv, window;
+    float scale_log2;                  // scale * log2(e)
+    // decode only
+    int chunk, splits;
+    float* part_o; float* part_ml;     // [B, nq, splits, D] and [B, nq, splits, 2]
+};
+
+// Loads keys [key0, key0 + BN) of one KV head into a [BN][DP] tile; keys past `last_key` are zeros.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const int* tab, int page_size,
+                                             int nkv, int kh, int key0, int last_key, int tid, int nthreads) {
+    for (int idx = tid; idx < BN * CH; idx += nthreads) {
+        const int key = idx / CH, c = idx - key * CH;
+        const int j = key0 + key;
+        const bool valid = j <= last_key;
+        const bf16* src = pages;
+        if (valid) {
+            const int page = tab[j / page_size];
+            src = pages + (((size_t)page * nkv + kh) * page_size + (j % page_size)) * D + c * 8;
+        }
+        cp_async16(dst + key * DP + c * 8, src, valid);
+    }
+}
+
+// S[16 x (8*NB)] += Q[16 x D] K^T for the keys of `sK` starting at tile row `key_off`.
+template <int NB>
+__device__ __forceinline__ void qk_tile(float (&s)[NB][4], const bf16* sQ_rows, const bf16* sK, int key_off, int lane) {
+#pragma unroll
+    for (int kb = 0; kb < KBLK; ++kb) {
+        uint32_t a[4];
+        ldsm_x4(a, sQ_rows + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + kb * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int nb = 0; nb < NB; nb += 2) {
+            uint32_t b[4];
+            ldsm_x4(b, sK + (key_off + nb * 8 + (lane & 7) + (lane >> 4) * 8) * DP + kb * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[nb], a, b[0], b[1]);
+            mma_bf16(s[nb + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x D] += P[16 x (8*NB)] V for the keys of `sV` starting at tile row `key_off`.
+template <int NB>
+__device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&p)[NB][4], const bf16* sV, int key_off, int lane) {
+#pragma unroll
+    for (int kb = 0; kb < NB / 2; ++kb) {
+        uint32_t a[4];
+        a[0] = pack_bf16(p[2 * kb][0], p[2 * kb][1]);
+        a[1] = pack_bf16(p[2 * kb][2], p[2 * kb][3]);
+        a[2] = pack_bf16(p[2 * kb + 1][0], p[2 * kb + 1][1]);
+        a[3] = pack_bf16(p[2 * kb + 1][2], p[2 * kb + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < D / 8; nb += 2) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, sV + (key_off + kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + nb * 8 + (lane >> 4) * 8);
+            mma_bf16(o[nb], a, b[0], b[1]);
+            mma_bf16(o[nb + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Masks, scales and exponentiates one thread's share of S (rows ra = lane/4 and ra + 8), updates the
+// running max m[2], the per-thread partial sums l[2] and rescales O.  key0: position of S column 0.
+template <int NB>
+__device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
+                                             const int (&pos_r)[2], const int (&lo_r)[2], int key0, float scale_log2,
+                                             int lane) {
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+            const float v = (j <= pos_r[r] && j >= lo_r[r]) ? s[nb][e] * scale_log2 : -INFINITY;
+            s[nb][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;     // a row with no visible key yet
+        const float alpha = exp2f(m[r] - m_use);                    // m = -inf gives 0
+        m[r] = m_new;
+        l[r] *= alpha;
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) { o[nb][2 * r] *= alpha; o[nb][2 * r + 1] *= alpha; }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const float p0 = exp2f(s[nb][2 * r] - m_use), p1 = exp2f(s[nb][2 * r + 1] - m_use);
+            s[nb][2 * r] = p0; s[nb][2 * r + 1] = p1;
+            l[r] += p0 + p1;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ prefill
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [BM][DP]
+    bf16* sK = sQ + BM * DP;                               // [2][BN][DP]
+    bf16* sV = sK + 2 * BN * DP;                           // [2][BN][DP]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kh = blockIdx.y, g = A.nq / A.nkv;
+
+    int tile = blockIdx.x, b = 0;
+    for (; b < A.B; ++b) {
+        const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (b >= A.B) return;
+    const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
+    const int rows_total = qlen * g, row0 = tile * BM;
+    const int row_end = min(row0 + BM, rows_total);
+    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int pos_hi = sp + (row_end - 1) / g;
+    const int pos_first = sp + row0 / g;
+    const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
+    const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
+
+    for (int idx = tid; idx < BM * CH; idx += 128) {       // Q tile: row = (token, head of the group)
+        const int r = idx / CH, c = idx - r * CH;
+        const int R = row0 + r;
+        const bool valid = R < rows_total;
+        const bf16* src = A.q;
+        if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
+        cp_async16(sQ + r * DP + c * 8, src, valid);
+    }
+    load_kv_tile(sK, A.k_pages, tab, A.page_size, A.nkv, kh, kt_lo * BN, pos_hi, tid, 128);
+    load_kv_tile(sV, A.v_pages, tab, A.page_size, A.nkv, kh, kt_lo * BN, pos_hi, tid, 128);
+    cp_async_commit();
+
+    int pos_r[2], lo_r[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int R = row0 + warp * 16 + (lane >> 2) + r * 8;
+        pos_r[r] = R < rows_total ? sp + R / g : -1;       // -1: no key is visible, the row stays empty
+        lo_r[r] = A.window > 0 ? max(0, pos_r[r] - A.window + 1) : 0;
+    }
+    // the warp's own rows: first and last valid one (positions rise with the row index)
+    const int wr_first = row0 + warp * 16, wr_last = min(wr_first + 15, rows_total - 1);
+    const bool w_valid = wr_first < rows_total;
+    const int w_pos_hi = sp + wr_last / g;
+    const int w_lo = A.window > 0 ? max(0, sp + wr_first / g - A.window + 1) : 0;
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+        const int buf = (kt - kt_lo) & 1;
+        cp_async_wait<0>();
+        __syncthreads();                                   // tile kt is in; everyone is done with tile kt-1
+        if (kt < kt_hi) {
+            load_kv_tile(sK + (buf ^ 1) * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, (kt + 1) * BN, pos_hi, tid, 128);
+            load_kv_tile(sV + (buf ^ 1) * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, (kt + 1) * BN, pos_hi, tid, 128);
+        }
+        cp_async_commit();
+        // skip tiles wholly outside this warp's rows (above the diagonal or behind the window)
+        if (!w_valid || kt * BN > w_pos_hi || kt * BN + BN - 1 < w_lo) continue;
+        float s[BN / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+        qk_tile<BN / 8>(s, sQ + warp * 16 * DP, sK + buf * BN * DP, 0, lane);
+        softmax_step<BN / 8>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
+        pv_tile<BN / 8>(o, s, sV + buf * BN * DP, 0, lane);
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float lr = l[r];
+        lr += __shfl_xor_sync(0xffffffffu, lr, 1);
+        lr += __shfl_xor_sync(0xffffffffu, lr, 2);
+        const int R = row0 + warp * 16 + (lane >> 2) + r * 8;
+        if (R >= rows_total) continue;
+        const float inv = lr > 0.f ? 1.0f / lr : 0.f;
+        bf16* dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb)
+            *reinterpret_cast<uint32_t*>(dst + nb * 8) = pack_bf16(o[nb][2 * r] * inv, o[nb][2 * r + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------------ decode
+constexpr int DEC_STAGES = 3;
+
+// grid (splits * m_tiles, nkv, B); 4 warps; each stage is 64 keys, 16 per warp.
+__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [16][DP]
+    bf16* sK = sQ + 16 * DP;                               // [STAGES][BN][DP]
+    bf16* sV = sK + DEC_STAGES * BN * DP;                  // [STAGES][BN][DP]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = A.nq / A.nkv, m_tiles = (g + 15) / 16;
+    const int split = blockIdx.x / m_tiles, mt = blockIdx.x % m_tiles;
+    const int kh = blockIdx.y, b = blockIdx.z;
+    const int pos = A.start_pos[b], len = pos + 1;
+    const int lo = A.window > 0 ? max(0, len - A.window) : 0;
+    const int base = (lo / BN) * BN;
+    const int k_begin = base + split * A.chunk;
+    if (k_begin >= len) return;                            // an empty split: the combine step skips it too
+    const int k_end = min(len, k_begin + A.chunk);
+    const int n_stage = (k_end - k_begin + BN - 1) / BN;
+    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int qrow = A.q_start[b];
+
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int hg = mt * 16 + r;
+        const bool valid = hg < g;
+        const bf16* src = A.q;
+        if (valid) src = A.q + (size_t)qrow * A.q_stride + (size_t)(kh * g + hg) * D + c * 8;
+        cp_async16(sQ + r * DP + c * 8, src, valid);
+    }
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+        if (st < n_stage) {
+            load_kv_tile(sK + st * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, k_begin + st * BN, k_end - 1, tid, 128);
+            load_kv_tile(sV + st * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, k_begin + st * BN, k_end - 1, tid, 128);
+        }
+        cp_async_commit();
+    }
+    const int pos_r[2] = {k_end - 1, k_end - 1};           // every row sees all keys of the range
+    const int lo_r[2] = {max(lo, k_begin), max(lo, k_begin)};
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int st = 0; st < n_stage; ++st) {
+        cp_async_wait<DEC_STAGES - 2>();
+        __syncthreads();
+        if (st + DEC_STAGES - 1 < n_stage) {
+            const int nst = st + DEC_STAGES - 1, nb_ = nst % DEC_STAGES;
+            load_kv_tile(sK + nb_ * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, k_begin + nst * BN, k_end - 1, tid, 128);
+            load_kv_tile(sV + nb_ * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, k_begin + nst * BN, k_end - 1, tid, 128);
+        }
+        cp_async_commit();
+        const int buf = st % DEC_STAGES;
+        const int key0 = k_begin + st * BN + warp * 16;    // this warp's 16 keys of the stage
+        if (key0 >= k_end) continue;
+        float s[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+        qk_tile<2>(s, sQ, sK + buf * BN * DP, warp * 16, lane);
+        softmax_step<2>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        pv_tile<2>(o, s, sV + buf * BN * DP, warp * 16, lane);
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                       // the stage buffers become the merge area
+
+    // merge the four warps: each holds (m, l, O) over its own keys, same fragment layout
+    float* mO = reinterpret_cast<float*>(sK);              // [4][16][D]
+    float* mML = mO + 4 * 16 * D;                          // [4][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float lr = l[r];
+        lr += __shfl_xor_sync(0xffffffffu, lr, 1);
+        lr += __shfl_xor_sync(0xffffffffu, lr, 2);
+        const int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) { mML[(warp * 16 + row) * 2] = m[r]; mML[(warp * 16 + row) * 2 + 1] = lr; }
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            float* dst = mO + (warp * 16 + row) * D + nb * 8 + (lane & 3) * 2;
+            dst[0] = o[nb][2 * r]; dst[1] = o[nb][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * D; idx += 128) {
+        const int row = idx / D, col = idx - row * D;
+        const int hg = mt * 16 + row;
+        if (hg >= g) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mML[(w * 16 + row) * 2]);
+        float acc = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mML[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            acc += f * mO[(w * 16 + row) * D + col];
+            lt += f * mML[(w * 16 + row) * 2 + 1];
+        }
+        const int head = kh * g + hg;
+        if (A.splits == 1) {
+            A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+        } else {
+            const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
+            A.part_o[pi * D + col] = acc;
+            if (col == 0) { A.part_ml[pi * 2] = mm; A.part_ml[pi * 2 + 1] = lt; }
+        }
+    }
+}
+
+// grid (nq, B): merges the partials of the non-empty splits of one (request, head).
+__global__ void attn_combine_kernel(const AttnArgs A) {
+    const int head = blockIdx.x, b = blockIdx.y;
+    const int len = A.start_pos[b] + 1;
+    const int lo = A.window > 0 ? max(0, len - A.window) : 0;
+    const int base = (lo / BN) * BN;
+    const int ns = min(A.splits, (len - base + A.chunk - 1) / A.chunk);
+    const size_t p0 = ((size_t)b * A.nq + head) * A.splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < ns; ++s) mm = fmaxf(mm, A.part_ml[(p0 + s) * 2]);
+    float lt = 0.f;
+    for (int s = 0; s < ns; ++s) {
+        const float ms = A.part_ml[(p0 + s) * 2];
+        lt += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_ml[(p0 + s) * 2 + 1];
+    }
+    const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+    const int qrow = A.q_start[b];
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float ms = A.part_ml[(p0 + s) * 2];
+            acc += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_o[(p0 + s) * D + col];
+        }
+        A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+constexpr int PREFILL_SMEM = (BM + 4 * BN) * DP * 2;
+constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
+constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
+constexpr int DECODE_SMEM = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
+
+int g_attr_done = 0;
+int set_attrs() {
+    if (g_attr_done) return 0;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    g_attr_done = 1;
+    return 0;
+}
+
+}  // namespace
+
+TL_EXPORT int tl_attn_head_dim() { return D; }
+
+// total_tiles = sum over requests of ceil(q_len * g / 64), computed by the caller.
+TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                              const int* table, int max_pages, int page_size, const int* q_start,
+                              const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
+                              float scale, int total_tiles, cudaStream_t stream) {
+    if (total_tiles <= 0 || B <= 0) return 0;
+    if (nq % nkv || BN % page_size) return 1;
+    int e = set_attrs();
+    if (e) return e;
+    AttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
+    dim3 grid(total_tiles, nkv);
+    attn_prefill_kernel<<<grid, 128, PREFILL_SMEM, stream>>>(A);
+    return tl_launch_status();
+}
+
+// One query token per request (row q_start[b]).  `chunk` (a multiple of 64) keys per split; with
+// splits > 1 the partials go to part_o [B, nq, splits, D] and part_ml [B, nq, splits, 2] (float)
+// and tl_attn_combine must follow on the same stream.
+TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                             const int* table, int max_pages, int page_size, const int* q_start,
+                             const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
+                             float scale, int chunk, int splits, float* part_o, float* part_ml,
+                             cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (nq % nkv || BN % page_size || chunk % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return 1;
+    int e = set_attrs();
+    if (e) return e;
+    AttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
+    A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
+    const int g = nq / nkv, m_tiles = (g + 15) / 16;
+    dim3 grid(splits * m_tiles, nkv, B);
+    if (grid.z > 65535) return 1;
+    attn_decode_kernel<<<grid, 128, DECODE_SMEM, stream>>>(A);
+    e = tl_launch_status();
+    if (e || splits == 1) return e;
+    dim3 cgrid(nq, B);
+    attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
+    return tl_launch_status();
+}

@@ -58,6 +58,7 @@ class StepContext:
     h_start_pos: list
     h_slots: list
     force_exact_attention: bool = False
+    graph_max_ctx: int = 0              # > 0: the step is captured in a graph; size for this context
     scratch: dict = field(default_factory=dict)    # per-step scratch of kernels, keyed by name
 
 
@@ -172,3 +173,8 @@ class ModelRunner:
         for e in entries:
             self.positions[e.rid] += len(e.tokens)
         return logits
+
+    def step_and_sample(self, entries, sampler, rows) -> list:
+        """One step followed by one sampled token per wanted place; `rows` as `Sampler.sample`."""
+        logits = self.step(entries)
+        return sampler.sample(logits, rows)

@@ -38,6 +38,7 @@ class Request:
     done: bool = False
     admitted_once: bool = False
     error: Exception | None = None
+    seed: int = 0                       # seed of this request's sampling draws
 
     @property
     def num_generated(self) -> int:

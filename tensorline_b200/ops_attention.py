@@ -1,0 +1,96 @@
+"""Launchers of the tensor-core attention kernels (bfloat16), built per head size.
+
+`attend_bf16` picks the kernel for a step: steps of single decoded tokens use the split-KV decode
+kernel (with its combine pass when the keys are split), every other step uses the prefill kernel,
+which also serves decoded tokens that ride along with prompt portions.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc.build import load_library
+from .ops import KernelError, _check, _ptr, _stream
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_libs: dict = {}
+
+NUM_SMS = 148
+KEY_TILE = 64
+
+
+def attn_lib(head_dim: int):
+    """The attention library compiled for this head size (built at first use)."""
+    lib = _libs.get(head_dim)
+    if lib is None:
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise KernelError(f"head_dim {head_dim}: the bfloat16 attention kernels take multiples of 16 "
+                              "from 16 to 256")
+        lib = load_library(f"tl_attn_hd{head_dim}", ["attn_mma.cu"], {"HEAD_DIM": head_dim})
+        lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P]
+        lib.tl_attn_prefill.restype = ctypes.c_int
+        lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
+        lib.tl_attn_decode.restype = ctypes.c_int
+        _libs[head_dim] = lib
+    return lib
+
+
+def plan_splits(batch: int, nkv: int, group: int, span: int, max_splits: int = 64) -> tuple:
+    """(chunk, splits) for a decode step: enough blocks to fill the GPU about twice, each with at
+    least one tile of keys; `span` is the largest number of keys a request can read."""
+    m_tiles = -(-group // 16)
+    tiles = max(1, -(-span // KEY_TILE))
+    want = max(1, -(-2 * NUM_SMS // max(1, batch * nkv * m_tiles)))
+    splits = max(1, min(want, tiles, max_splits))
+    chunk = -(-tiles // splits) * KEY_TILE
+    splits = -(-tiles * KEY_TILE // chunk)
+    return chunk, splits
+
+
+def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
+            nq, nkv, d, window, scale) -> None:
+    g = nq // nkv
+    B = len(h_q_start) - 1
+    tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // KEY_TILE) for i in range(B))
+    if KEY_TILE % page_size:
+        raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
+    _check(attn_lib(d).tl_attn_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
+                                       table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
+                                       nq, nkv, int(window or 0), float(scale), tiles, _stream()), "attn_prefill")
+
+
+def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
+           nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None) -> None:
+    if KEY_TILE % page_size:
+        raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
+    if splits > 1:
+        if part_o is None or part_o.numel() < B * nq * splits * d or part_o.dtype != torch.float32:
+            raise KernelError("attn_decode: part_o must be float32 [B, nq, splits, d]")
+        if part_ml is None or part_ml.numel() < B * nq * splits * 2 or part_ml.dtype != torch.float32:
+            raise KernelError("attn_decode: part_ml must be float32 [B, nq, splits, 2]")
+    _check(attn_lib(d).tl_attn_decode(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
+                                      table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
+                                      nq, nkv, int(window or 0), float(scale), chunk, splits,
+                                      _ptr(part_o) if splits > 1 else None, _ptr(part_ml) if splits > 1 else None,
+                                      _stream()), "attn_decode")
+
+
+def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale) -> None:
+    if qkv.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        raise KernelError("attend_bf16: bfloat16 tensors only")
+    q_stride = qkv.shape[1]
+    if ctx.decode_only:
+        span = ctx.graph_max_ctx or ctx.max_ctx
+        if window:
+            span = min(span, window + KEY_TILE - 1)
+        chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((ctx.B, nq, splits, 2), dtype=torch.float32, device=qkv.device)
+        decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
+               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+    else:
+        prefill(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
+                ctx.h_q_start, nq, nkv, d, window, scale)

@@ -42,29 +42,18 @@ def make_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = 16, 
     return ModelRunner(model, cache), cfg
 
 
-def main(argv=None) -> int:
-    ap = argparse.ArgumentParser("trace_run", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
-    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
-    ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (rounded up per request to whole pages)")
-    ap.add_argument("--page-size", type=int, default=16)
-    a = ap.parse_args(argv)
-    if 64 % a.page_size:
-        ap.error("--page-size must divide 64")
-    out = Path(a.out)
-    out.mkdir(parents=True, exist_ok=True)
+class TraceSession:
+    """Feeds trace records to a runner, one step at a time; what `main` does for every line."""
 
-    from .engine.runner import StepEntry
+    def __init__(self, runner):
+        self.runner = runner
+        self.cache = runner.cache
 
-    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size)
-    cache = runner.cache
-    for line in sys.stdin:
-        line = line.strip()
-        if not line:
-            continue
-        rec = json.loads(line)
+    def run_step(self, rec: dict):
+        """Run one record; returns the logits [wanted, vocab] on the device (may be empty)."""
+        from .engine.runner import StepEntry
+
+        cache, runner = self.cache, self.runner
         entries = []
         for e in rec.get("entries", []):
             rid, toks = e["id"], e["tokens"]
@@ -80,12 +69,36 @@ def main(argv=None) -> int:
         logits = runner.step(entries)
         for e in entries:
             cache.advance(e.rid, runner.positions[e.rid], None)
-        if logits.shape[0]:
-            arr = logits.detach().float().cpu().contiguous().numpy().astype("<f4", copy=False)
-            arr.tofile(out / f"{rec['step']}.f32")
         for rid in rec.get("end", []):
             if cache.holds(rid):
                 cache.release(rid)
                 runner.end_request(rid)
+        return logits
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser("trace_run", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    ap.add_argument("--max-tokens", type=int, required=True,
+                    help="most tokens live requests hold at any time (rounded up per request to whole pages)")
+    ap.add_argument("--page-size", type=int, default=16)
+    a = ap.parse_args(argv)
+    if a.page_size < 1 or 64 % a.page_size:
+        ap.error("--page-size must divide 64")
+    out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size)
+    session = TraceSession(runner)
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        rec = json.loads(line)
+        logits = session.run_step(rec)
+        if logits.shape[0]:
+            arr = logits.detach().float().cpu().contiguous().numpy().astype("<f4", copy=False)
+            arr.tofile(out / f"{rec['step']}.f32")
         print(f"done {rec['step']}", flush=True)
     return 0

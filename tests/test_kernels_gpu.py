@@ -1,0 +1,245 @@
+"""Each CUDA kernel alone against its plain reference, at sizes that are not the engine's."""
+import math
+
+import pytest
+import torch
+
+from tests.gpu_helpers import BF16, F32, assert_close, i32, scatter_pages, table_tensor
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return F32 if dt == torch.float32 else BF16
+
+
+def rnd(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("wdt", DT)
+def test_embedding(wdt):
+    from tensorline_b200 import ops
+    table = rnd(53, 24, seed=1, dtype=wdt)
+    ids = [0, 52, 7, 7, 31]
+    x = torch.empty(5, 24, dtype=torch.float32, device="cuda")
+    ops.embed(x, table.cuda(), i32(ids))
+    assert torch.equal(x.cpu().double(), plain.embedding(table.double(), ids))
+
+
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("wdt", DT)
+@pytest.mark.parametrize("H", [100, 3, 1030])
+def test_add_rmsnorm(adt, wdt, H):
+    from tensorline_b200 import ops
+    T, eps = 7, 3e-5
+    x = rnd(T, H, seed=2, scale=3.0)
+    r = rnd(T, H, seed=3, dtype=adt)
+    w = (1 + rnd(H, seed=4, scale=0.3)).to(wdt)
+    xd, out = x.cuda(), torch.empty(T, H, dtype=adt, device="cuda")
+    ops.add_rmsnorm(xd, r.cuda(), w.cuda(), out, eps)
+    want_x = x.double() + r.double()
+    assert_close(xd, want_x, "residual sum", rtol=1e-6, atol=1e-6)            # a float32 sum
+    assert_close(out, plain.rms_norm(want_x, w.double(), eps), "norm", **tol(adt))
+    # without a residual, x stays as it is; with row selection too
+    xd2 = x.cuda()
+    ops.add_rmsnorm(xd2, None, w.cuda(), out, eps)
+    assert torch.equal(xd2.cpu(), x)
+    assert_close(out, plain.rms_norm(x.double(), w.double(), eps), "norm only", **tol(adt))
+    rows = [5, 0, 5]
+    out3 = torch.empty(3, H, dtype=adt, device="cuda")
+    xd3 = x.cuda()
+    ops.add_rmsnorm(xd3, r.cuda(), w.cuda(), out3, eps, rows=i32(rows))
+    assert torch.equal(xd3.cpu(), x)
+    assert_close(out3, plain.rms_norm(want_x[rows], w.double(), eps), "selected rows", **tol(adt))
+
+
+@pytest.mark.parametrize("adt", DT)
+def test_silu_mul(adt):
+    from tensorline_b200 import ops
+    T, I = 5, 37
+    gu = rnd(T, 2 * I, seed=5, scale=3.0, dtype=adt)
+    out = torch.empty(T, I, dtype=adt, device="cuda")
+    ops.silu_mul(gu.cuda(), out)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    assert_close(out, g / (1 + torch.exp(-g)) * u, "silu*up", **tol(adt))
+
+
+@pytest.mark.parametrize("wdt", DT)
+def test_gemm_f32_exact_order(wdt):
+    from tensorline_b200 import ops
+    M, N, K = 37, 70, 45
+    a, w = rnd(M, K, seed=6), rnd(N, K, seed=7, dtype=wdt)
+    out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm_f32(a.cuda(), w.cuda(), out)
+    assert_close(out, a.double() @ w.double().T, "gemm", **F32)
+    # a row's result does not depend on the other rows of the launch
+    one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+    ops.gemm_f32(a[17:18].cuda(), w.cuda(), one)
+    assert torch.equal(one[0], out[17])
+
+
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("rot", [None, 8])
+def test_rope_and_kv_write(adt, rot):
+    from tensorline_b200 import ops
+    nq, nkv, d, ps, theta = 3, 1, 24, 4, 5000.0
+    rdim = d if rot is None else rot
+    pos = [0, 1, 2, 9, 10, 4097]
+    slots = [1, 1, 1, 0, 0, 2]
+    T = len(pos)
+    qkv = rnd(T, (nq + 2 * nkv) * d, seed=8, dtype=adt)
+    bias = rnd((nq + 2 * nkv) * d, seed=9, scale=0.5, dtype=adt)
+    max_pages, num_pages = 1100, 3400
+    g = torch.Generator().manual_seed(3)
+    table = torch.randperm(num_pages, generator=g)[:3 * max_pages].reshape(3, max_pages).to(torch.int32)
+    kp = torch.zeros(num_pages + 1, nkv, ps, d, dtype=adt, device="cuda")
+    vp = torch.zeros_like(kp)
+    inv_freq = (theta ** (-torch.arange(0, rdim, 2, dtype=torch.float64) / rdim)).float()
+    q = qkv.cuda()
+    ops.rope_kv_write(q, bias.cuda(), i32(pos), i32(slots), table.cuda(), ps, inv_freq.cuda(), rdim, nq, nkv, d, kp, vp)
+    x = (qkv.double() + bias.double()).view(T, nq + 2 * nkv, d)
+    cos, sin = plain.rope_cos_sin(pos, rdim, theta)
+    rotated = torch.cat((plain.apply_rope(x[..., :rdim], cos, sin), x[..., rdim:]), dim=-1)
+    assert_close(q.view(T, -1, d)[:, :nq], rotated[:, :nq], "q", **tol(adt))
+    for t in range(T):
+        page, off = int(table[slots[t], pos[t] // ps]), pos[t] % ps
+        assert_close(kp[page, :, off], rotated[t, nq:nq + nkv], f"k of token {t}", **tol(adt))
+        assert_close(vp[page, :, off], x[t, nq + nkv:], f"v of token {t}", **tol(adt))
+    assert int((kp != 0).any(dim=-1).sum()) == T * nkv                       # nothing else was written
+
+
+def test_argmax_lowest_index_wins():
+    from tensorline_b200 import ops
+    logits = rnd(6, 5003, seed=10)
+    logits[2, 4000] = logits[2, 17] = 50.0
+    logits[3, 5002] = 60.0
+    logits[4, 0] = 60.0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.argmax(logits.cuda(), out)
+    want = logits.argmax(-1).tolist()
+    want[2] = 17
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("top_p", [1.0, 0.7, 0.2])
+def test_sampling_matches_reference_distribution(top_p):
+    """The picked token is the one the plain inverse-CDF picks for the same uniform number; the kept
+    set is the reference's nucleus."""
+    from tensorline_b200 import ops
+    V, R = 1237, 64
+    logits = rnd(R, V, seed=11, scale=2.5)
+    temps = torch.full((R,), 0.8)
+    temps[5] = 0.0                                                          # a greedy row among sampled ones
+    g = torch.Generator().manual_seed(12)
+    u = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), temps.cuda(), torch.full((R,), top_p).cuda(), u.cuda(), out)
+    got = out.tolist()
+    for r in range(R):
+        if temps[r] <= 0:
+            assert got[r] == int(logits[r].argmax())
+            continue
+        probs = plain.sampling_distribution(logits[r], float(temps[r]), top_p)
+        assert probs[got[r]] > 0, f"row {r}: token {got[r]} is outside the nucleus"
+        cdf = torch.cumsum(probs, 0)
+        lo = float(cdf[got[r]] - probs[got[r]])
+        assert lo - 1e-5 <= float(u[r]) <= float(cdf[got[r]]) + 1e-5, f"row {r}: u={float(u[r])} not in the token's interval"
+
+
+def _plain_attention_rows(q, k, v, pos_q, window):
+    """q [n, nq, d] at positions pos_q over the whole k, v [len, nkv, d]."""
+    n, nq, d = q.shape
+    g = nq // k.shape[1]
+    out = torch.empty_like(q)
+    for i, p in enumerate(pos_q):
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nq):
+            s = (k[lo:p + 1, h // g] @ q[i, h]) * d ** -0.5
+            out[i, h] = torch.softmax(s, 0) @ v[lo:p + 1, h // g]
+    return out
+
+
+ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in the step, window
+    (4, 2, 16, 4, [0, 5, 31], [9, 1, 2], None),
+    (3, 1, 32, 8, [0, 130], [70, 3], 24),
+    (7, 1, 128, 16, [300, 0, 65], [1, 1, 1], None),
+    (6, 2, 48, 16, [63, 64, 1399], [1, 1, 1], None),
+    (14, 2, 64, 64, [15, 0], [17, 200], 100),
+    (20, 1, 16, 2, [77], [1], None),
+    (5, 5, 80, 32, [257], [1], 33),
+]
+
+
+@pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16"])
+def test_paged_attention(case, kernel):
+    """Decode and prefill attention over scattered pages against the plain formula."""
+    from tensorline_b200 import ops, ops_attention
+    nq, nkv, d, ps, ctx_lens, step_lens, window = case
+    adt = torch.float32 if kernel == "exact_f32" else torch.bfloat16
+    B = len(ctx_lens)
+    max_pages, num_pages = 128, 300
+    kps = torch.zeros(num_pages + 1, nkv, ps, d, dtype=adt)
+    vps = torch.zeros_like(kps)
+    rows, qs, want, pos_all, slot_all = [], [], [], [], []
+    used = 0
+    for b in range(B):
+        n = ctx_lens[b] + step_lens[b]
+        k = rnd(n, nkv, d, seed=20 + b, dtype=adt)
+        v = rnd(n, nkv, d, seed=40 + b, dtype=adt)
+        q = rnd(step_lens[b], nq, d, seed=60 + b, scale=2.0, dtype=adt)
+        if b == 0 and n > 40:                       # one far key that must win: a planted score
+            k[3] *= 0; k[3, :, 0] = 8.0; q[-1] *= 0; q[-1, :, 0] = 8.0
+        need = -(-n // ps)
+        g = torch.Generator().manual_seed(100 + b)
+        mine = (torch.randperm(num_pages // B, generator=g)[:need] * B + b).tolist()   # interleaved, disjoint
+        for i in range(n):
+            kps[mine[i // ps], :, i % ps] = k[i]
+            vps[mine[i // ps], :, i % ps] = v[i]
+        rows.append(mine)
+        pq = list(range(ctx_lens[b], n))
+        want.append(_plain_attention_rows(q.double(), k.double(), v.double(), pq, window))
+        qs.append(q)
+        pos_all += pq
+        slot_all += [b] * step_lens[b]
+    q_all = torch.cat(qs).reshape(-1, nq * d).cuda()
+    T = q_all.shape[0]
+    out = torch.zeros(T, nq * d, dtype=adt, device="cuda")
+    table = table_tensor(rows, max_pages, num_pages)
+    kd, vd = kps.cuda(), vps.cuda()
+    scale = d ** -0.5
+    if kernel != "mma_bf16":
+        ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale)
+    else:
+        q_start = [0]
+        for n in step_lens:
+            q_start.append(q_start[-1] + n)
+        args = (q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))))
+        if all(n == 1 for n in step_lens):
+            span = max(c + 1 for c in ctx_lens)
+            for splits_wanted in (1, 3, 64):        # one range, a few, and more ranges than tiles
+                tiles = -(-span // 64)
+                splits = min(splits_wanted, tiles)
+                chunk = -(-tiles // splits) * 64
+                splits = -(-tiles * 64 // chunk)
+                po = torch.full((B, nq, splits, d), float("nan"), device="cuda")
+                pml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")
+                out.zero_()
+                ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml)
+                assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits", **BF16)
+            out.zero_()
+        ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale)
+    assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))
+
+
+def test_attention_refuses_unsupported_head_size():
+    from tensorline_b200 import ops, ops_attention
+    with pytest.raises(ops.KernelError):
+        ops_attention.attn_lib(24)
+    with pytest.raises(ops.KernelError):
+        ops_attention.attn_lib(272)
