@@ -88,10 +88,20 @@ class ModelRunner:
             elif isinstance(need, SlotState):
                 shape = (cache.max_num_seqs + 1,) + tuple(need.shape)
                 self.caches[cid] = StateView(torch.zeros(shape, dtype=_DTYPES[need.dtype], device=self.device))
-        self.tables = [torch.from_numpy(g.table.copy()).to(self.device) for g in cache.groups]
-        self._host_tables = [torch.from_numpy(g.table) for g in cache.groups]      # share memory with the manager
+        # The manager's tables move into pinned memory (it writes them in place), so that the copy
+        # to the device before each step is one asynchronous transfer per group.
+        self._host_tables = []
+        for g in cache.groups:
+            pinned = torch.from_numpy(g.table.copy()).pin_memory()
+            g.table = pinned.numpy()
+            self._host_tables.append(pinned)
+        self.tables = [t.to(self.device) for t in self._host_tables]
         self.vocab_size = model.spec.vocab_size
-        self.launches = 0
+        self.use_graphs = False
+        self.graph_replays = 0
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self._graphable = all(isinstance(c, KVCacheView) for c in self.caches.values())
 
     # ------------------------------------------------------------------ bytes
     def cache_bytes_per_token(self) -> int:
@@ -150,7 +160,7 @@ class ModelRunner:
         cut = np.cumsum([0, T, T, T, B + 1, B, B, len(want_rows)])
         parts = [dev[cut[i]:cut[i + 1]] for i in range(7)]
         for t_dev, t_host in zip(self.tables, self._host_tables):
-            t_dev.copy_(t_host, non_blocking=False)
+            t_dev.copy_(t_host, non_blocking=True)
         return StepContext(T=T, B=B, ids=parts[0], pos=parts[1], req_slot=parts[2], q_start=parts[3],
                            start_pos=parts[4], slots=parts[5], want_rows=parts[6], tables=self.tables,
                            page_size=ps, decode_only=all(len(e.tokens) == 1 for e in entries), max_q_len=max_q,
@@ -175,6 +185,109 @@ class ModelRunner:
         return logits
 
     def step_and_sample(self, entries, sampler, rows) -> list:
-        """One step followed by one sampled token per wanted place; `rows` as `Sampler.sample`."""
+        """One step followed by one sampled token per wanted place; `rows` as `Sampler.sample`.
+        A step of single decoded tokens that all want their logits replays a CUDA graph; if all of
+        them are greedy the argmax is part of the graph and only the tokens come back."""
+        entries = list(entries)
+        if self._can_replay(entries):
+            g = self._run_graph(entries)
+            n = len(entries)
+            if all(p.temperature <= 0 for p, _, _ in rows):
+                return g.tokens[:n].tolist()
+            return sampler.sample(g.logits[:n], rows)
         logits = self.step(entries)
         return sampler.sample(logits, rows)
+
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def _can_replay(self, entries) -> bool:
+        return (self.use_graphs and self._graphable and 0 < len(entries) <= self.cache.max_num_seqs
+                and all(len(e.tokens) == 1 and list(e.want) == [0] and self.positions[e.rid] > 0 for e in entries))
+
+    def _bucket(self, n: int) -> int:
+        """Batch sizes 1, 2, 4, ... and the sequence limit itself (tensorline/cuda_graphs.py:30-35)."""
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.cache.max_num_seqs)
+
+    def _capture(self, nb: int):
+        dev = self.device
+        buf = torch.zeros(7 * nb + 1, dtype=torch.int32, device=dev)
+        host = torch.zeros(7 * nb + 1, dtype=torch.int32).pin_memory()
+        cut = np.cumsum([0, nb, nb, nb, nb + 1, nb, nb, nb])
+        parts = [buf[cut[i]:cut[i + 1]] for i in range(7)]
+        pad = self.cache.padding_slot
+        host[2 * nb:3 * nb] = pad                                  # req_slot
+        host[3 * nb:4 * nb + 1] = torch.arange(nb + 1, dtype=torch.int32)   # q_start: one token each
+        host[5 * nb + 1:6 * nb + 1] = pad                          # slots
+        host[6 * nb + 1:7 * nb + 1] = torch.arange(nb, dtype=torch.int32)   # every row's logits
+        buf.copy_(host)
+        ctx = StepContext(T=nb, B=nb, ids=parts[0], pos=parts[1], req_slot=parts[2], q_start=parts[3],
+                          start_pos=parts[4], slots=parts[5], want_rows=parts[6], tables=self.tables,
+                          page_size=self.page_size, decode_only=True, max_q_len=1, max_ctx=self.cache.max_model_len,
+                          h_q_start=list(range(nb + 1)), h_start_pos=[0] * nb, h_slots=[pad] * nb,
+                          force_exact_attention=self.force_exact_attention, graph_max_ctx=self.cache.max_model_len)
+        from .. import ops
+        tokens = torch.zeros(nb, dtype=torch.int32, device=dev)
+
+        def run():
+            logits = self.model.forward(ctx, self.caches)
+            ops.argmax(logits, tokens)
+            return logits
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                              # warm-up outside the capture: lazy
+            for _ in range(2):                                     # library handles, workspaces, kernel attributes
+                run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = run()
+        g = _DecodeGraph(graph, buf, host, logits, tokens, nb)
+        self._graphs[nb] = g
+        return g
+
+    @torch.inference_mode()
+    def _run_graph(self, entries):
+        n = len(entries)
+        nb = self._bucket(n)
+        g = self._graphs.get(nb) or self._capture(nb)
+        h = g.host.numpy()
+        pad = self.cache.padding_slot
+        h[0:nb] = 0
+        h[nb:2 * nb] = 0
+        h[2 * nb:3 * nb] = pad
+        h[4 * nb + 1:5 * nb + 1] = 0
+        h[5 * nb + 1:6 * nb + 1] = pad
+        for i, e in enumerate(entries):
+            p = self.positions[e.rid]
+            slot = self.cache.slot(e.rid)
+            if p + 1 > len(self.cache._held[e.rid].pages[0]) * self.page_size:
+                raise RuntimeError(f"request {e.rid!r}: no page for position {p}; grow its cache before the step")
+            h[i] = e.tokens[0]
+            h[nb + i] = p
+            h[2 * nb + i] = slot
+            h[4 * nb + 1 + i] = p
+            h[5 * nb + 1 + i] = slot
+        g.buf.copy_(g.host, non_blocking=True)
+        for t_dev, t_host in zip(self.tables, self._host_tables):
+            t_dev.copy_(t_host, non_blocking=True)
+        g.graph.replay()
+        self.graph_replays += 1
+        for e in entries:
+            self.positions[e.rid] += 1
+        return g
+
+
+@dataclass
+class _DecodeGraph:
+    graph: object
+    buf: torch.Tensor
+    host: torch.Tensor
+    logits: torch.Tensor
+    tokens: torch.Tensor
+    batch: int

@@ -62,7 +62,8 @@ class TraceSession:
                     raise RuntimeError(f"step {rec['step']}: more than {cache.max_num_seqs} live requests")
                 runner.start_request(rid, 0)
             start = runner.positions[rid]
-            if not cache.grow(rid, start, start + len(toks)):
+            if start + len(toks) > cache.max_pages_per_seq * cache.page_size or \
+                    not cache.grow(rid, start, start + len(toks)):
                 raise RuntimeError(f"step {rec['step']}: request {rid!r} needs pages for {start + len(toks)} tokens "
                                    f"but the pool of {cache.num_pages} pages (--max-tokens) is exhausted")
             entries.append(StepEntry(rid, toks, list(e.get("want", []))))

@@ -1,0 +1,151 @@
+"""The engine end to end: greedy generation through the entry point against the plain model, under
+forced chunking, forced preemption, queueing, shared prefixes and seeded sampling."""
+import pytest
+import torch
+
+from tests.plain.qwen2_plain import PlainQwen2, forward, greedy_generate
+from tests.tiny import CONFIGS, PAGE_SIZE, random_tokens, write_tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["A", "B_FULL"])
+def tiny(request, tmp_path_factory):
+    name = request.param
+    folder = write_tiny(name, tmp_path_factory.mktemp(name))
+    plain = PlainQwen2(folder)
+    V = CONFIGS[name]["vocab_size"]
+    prompts = [random_tokens(V, n, seed=30 + n) for n in (1, 5, 17, 32)]
+    want = [greedy_generate(plain, p, 8) for p in prompts]
+    return name, folder, prompts, want
+
+
+@pytest.fixture(scope="module")
+def tiny_a(tmp_path_factory):
+    folder = write_tiny("B_FULL", tmp_path_factory.mktemp("bf"))
+    plain = PlainQwen2(folder)
+    prompts = [random_tokens(384, n, seed=30 + n) for n in (1, 5, 17, 32)]
+    return folder, prompts, [greedy_generate(plain, p, 8) for p in prompts]
+
+
+def engine(folder, dtype="float32", **kw):
+    from tensorline_b200 import Engine
+    opts = dict(block_size=8, num_blocks=32, max_num_seqs=8, max_model_len=128)
+    opts.update(kw)
+    return Engine(str(folder), dtype=dtype, **opts)
+
+
+def params(n=8, **kw):
+    from tensorline_b200 import SamplingParams
+    return SamplingParams(max_tokens=n, ignore_eos=True, **kw)
+
+
+# prompts of 1, 5, 17, 32 tokens that grow by 8: with pages of 4 (A) they hold 2+3+6+10 pages when the
+# last token is computed, with pages of 8 (B) 1+2+3+5; the "forced preemption" pool holds 10
+REGIMES = {
+    "plain": lambda name: {},
+    "forced chunking": lambda name: dict(max_batched_tokens=4),
+    "forced preemption": lambda name: dict(num_blocks=10, prefix_caching=False),
+    "queueing": lambda name: dict(max_num_seqs=2),
+    "no graphs": lambda name: dict(cuda_graphs=False),
+}
+
+
+@pytest.mark.parametrize("regime", sorted(REGIMES))
+def test_greedy_generation_equals_the_plain_model(tiny, regime):
+    """tzar-beep/Tensorline's tests/test_batching.py:67-85 with tokens in place of text."""
+    name, folder, prompts, want = tiny
+    opts = dict(block_size=PAGE_SIZE[name], num_blocks=64)
+    opts.update(REGIMES[regime](name))
+    eng = engine(folder, **opts)
+    outs = eng.generate(prompts, params())
+    assert [o.token_ids for o in outs] == want
+    assert all(o.finish_reason == "length" and o.stats.completion_tokens == 8 for o in outs)
+    st = eng.stats()
+    assert st["free_pages"] == st["num_pages"], "pages leaked"
+    if regime == "forced preemption":
+        assert st["preemptions"] > 0
+    if regime == "queueing":
+        assert st["max_running_seen"] == 2
+    if regime == "plain":
+        assert st["max_running_seen"] > 1 and st["graph_replays"] > 0
+    if regime == "no graphs":
+        assert st["graph_replays"] == 0
+
+
+def test_bfloat16_greedy_tokens_follow_the_plain_model_where_it_is_decided(tiny_a):
+    """bfloat16 must pick the plain model's token wherever the plain model's lead over the runner-up is
+    larger than twice the stated logit tolerance; it is followed until the first undecided position."""
+    from tests.gpu_helpers import BF16_MODEL_REL
+    folder, prompts, _ = tiny_a
+    plain = PlainQwen2(folder)
+    eng = engine(folder, dtype="bfloat16")
+    outs = eng.generate(prompts, params())
+    compared = 0
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            logits = forward(plain, seq)[-1]
+            top = torch.topk(logits, 2).values
+            if float(top[0] - top[1]) <= 2 * BF16_MODEL_REL * float(logits.abs().max()):
+                break
+            assert tok == int(logits.argmax())
+            compared += 1
+            seq.append(tok)
+    assert compared >= 4
+
+
+def test_request_that_does_not_fit_fails_and_others_go_on(tiny_a):
+    from tensorline_b200.engine import RequestDoesNotFit
+    folder, prompts, want = tiny_a
+    eng = engine(folder, num_blocks=2, prefix_caching=False)
+    with pytest.raises(RequestDoesNotFit):
+        eng.generate([prompts[2]], params())                 # 17 tokens, 16 fit
+    assert eng.generate([prompts[1]], params(3))[0].token_ids == want[1][:3]
+    assert eng.stats()["free_pages"] == 2
+    with pytest.raises(ValueError, match="max_model_len"):
+        eng.add_request(list(range(128)))
+
+
+def test_stop_token_ends_a_request_and_is_not_returned(tiny_a):
+    from tensorline_b200 import SamplingParams
+    folder, prompts, want = tiny_a
+    eng = engine(folder)
+    seq = want[3]
+    k = next(i for i in range(1, 8) if seq[i] not in seq[:i])     # a token that first appears at place k
+    out = eng.generate([prompts[3]], SamplingParams(max_tokens=8, stop_token_ids={seq[k]}))[0]
+    assert out.token_ids == seq[:k] and out.finish_reason == "stop"
+
+
+def test_shared_prefix_is_served_from_the_cache_and_changes_nothing(tmp_path):
+    """tests/test_prefix_cache.py:42-74 of tzar-beep/Tensorline, on the untied group-3 model."""
+    folder = write_tiny("B_FULL", tmp_path / "b")
+    shared = random_tokens(384, 16, seed=1)
+    prompts = [shared + random_tokens(384, n, seed=2 + n) for n in (7, 24, 48)]
+    opts = dict(block_size=8, num_blocks=40, max_model_len=256)
+    ref = engine(folder, prefix_caching=False, **opts).generate(prompts, params(12))
+    eng = engine(folder, **opts)
+    first = eng.generate([prompts[0]], params(12))
+    outs = eng.generate(prompts[1:], params(12))
+    assert [o.token_ids for o in first + outs] == [o.token_ids for o in ref]
+    assert first[0].stats.cached_tokens == 0 and all(o.stats.cached_tokens == 16 for o in outs)
+    again = eng.generate([prompts[1]], params(12))[0]        # fully cached: the last page is computed again
+    assert again.token_ids == ref[1].token_ids and 0 < again.stats.cached_tokens < len(prompts[1])
+    assert eng.stats()["free_pages"] == 40 and eng.stats()["prefix_hit_tokens"] > 0
+
+
+def test_seeded_sampling_does_not_depend_on_batching_or_preemption(tmp_path):
+    """Temperature 0.8, top-p 0.9, seeded: the same tokens alone, in a batch, and under preemption."""
+    folder = write_tiny("B", tmp_path / "b")
+    prompts = [random_tokens(384, n, seed=60 + n) for n in (7, 40, 64)]
+    sp = [params(12, temperature=0.8, top_p=0.9, seed=1000 + i) for i in range(3)]
+    opts = dict(block_size=8, max_model_len=256)
+    alone = [engine(folder, num_blocks=40, **opts).generate([p], s)[0].token_ids for p, s in zip(prompts, sp)]
+    together = engine(folder, num_blocks=40, **opts).generate(prompts, sp)
+    assert [o.token_ids for o in together] == alone
+    tight = engine(folder, num_blocks=16, **opts)
+    squeezed = tight.generate(prompts, sp)
+    assert [o.token_ids for o in squeezed] == alone and tight.stats()["preemptions"] > 0
+    assert len({tuple(t) for t in alone}) == 3 and all(len(t) == 12 for t in alone)
+    greedy = engine(folder, num_blocks=40, **opts).generate([prompts[0]], params(12))[0].token_ids
+    assert greedy != alone[0]
