@@ -61,6 +61,7 @@ class PageGroup:
     pool: PagePool
     caches: list = field(default_factory=list)          # ids of the cache entries that use this group
     table: np.ndarray | None = None                     # [max_slots + 1, max_pages_per_seq] int32
+    version: int = 0                                    # bumped at every write to `table`
 
     @property
     def scratch_page(self) -> int:
@@ -113,6 +114,14 @@ class CacheManager:
         self._free_slots = list(range(max_num_seqs - 1, -1, -1))
         self._held: dict = {}
         self.padding_slot = max_num_seqs                 # its table rows point at the scratch pages
+        # Called before any write to a group's table: the owner of a device copy that may still be
+        # in flight from this memory waits for it here.
+        self.before_table_write = None
+
+    def _touch(self, g: PageGroup) -> None:
+        if self.before_table_write is not None:
+            self.before_table_write()
+        g.version += 1
 
     # ------------------------------------------------------------------ figures
     @property
@@ -209,6 +218,7 @@ class CacheManager:
             gone = [(i, p) for i, p in enumerate(pages[:first]) if p >= 0]
             if gone:
                 g.pool.free([p for _, p in gone])
+                self._touch(g)
                 for i, _ in gone:
                     pages[i] = -1
                     g.table[held.slot, i] = g.scratch_page
@@ -237,11 +247,13 @@ class CacheManager:
             raise CacheError(f"request {rid!r} released but not admitted (double release)")
         for g, pages in zip(self.groups, held.pages):
             g.pool.free([p for p in pages if p >= 0])
+            self._touch(g)
             g.table[held.slot, :] = g.scratch_page
         self._free_slots.append(held.slot)
 
     def _write_table(self, group: int, slot: int, first: int, pages) -> None:
         if pages:
+            self._touch(self.groups[group])
             self.groups[group].table[slot, first:first + len(pages)] = pages
 
     # ------------------------------------------------------------------ self check (tests)

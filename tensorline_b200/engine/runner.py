@@ -28,6 +28,7 @@ import torch
 from ..cache import CacheManager, PagedKV, SlotState
 from ..models.spec import Model
 from ..parts import KVCacheView, Runtime, StateView
+from .. import ops
 
 
 @dataclass
@@ -96,12 +97,32 @@ class ModelRunner:
             g.table = pinned.numpy()
             self._host_tables.append(pinned)
         self.tables = [t.to(self.device) for t in self._host_tables]
+        self._table_versions = [g.version for g in cache.groups]
+        self._table_event = None
+        cache.before_table_write = self._wait_for_table_copy
         self.vocab_size = model.spec.vocab_size
         self.use_graphs = False
         self.graph_replays = 0
         self._graphs: dict = {}
         self._graph_pool = None
         self._graphable = all(isinstance(c, KVCacheView) for c in self.caches.values())
+
+    def _wait_for_table_copy(self) -> None:
+        if self._table_event is not None:
+            self._table_event.synchronize()
+            self._table_event = None
+
+    def _sync_tables(self) -> None:
+        """Copy the block tables that changed since the last step to the device."""
+        copied = False
+        for i, g in enumerate(self.cache.groups):
+            if self._table_versions[i] != g.version:
+                self.tables[i].copy_(self._host_tables[i], non_blocking=True)
+                self._table_versions[i] = g.version
+                copied = True
+        if copied:
+            self._table_event = torch.cuda.Event()
+            self._table_event.record()
 
     # ------------------------------------------------------------------ bytes
     def cache_bytes_per_token(self) -> int:
@@ -159,8 +180,7 @@ class ModelRunner:
         dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
         cut = np.cumsum([0, T, T, T, B + 1, B, B, len(want_rows)])
         parts = [dev[cut[i]:cut[i + 1]] for i in range(7)]
-        for t_dev, t_host in zip(self.tables, self._host_tables):
-            t_dev.copy_(t_host, non_blocking=True)
+        self._sync_tables()
         return StepContext(T=T, B=B, ids=parts[0], pos=parts[1], req_slot=parts[2], q_start=parts[3],
                            start_pos=parts[4], slots=parts[5], want_rows=parts[6], tables=self.tables,
                            page_size=ps, decode_only=all(len(e.tokens) == 1 for e in entries), max_q_len=max_q,
@@ -227,7 +247,6 @@ class ModelRunner:
                           page_size=self.page_size, decode_only=True, max_q_len=1, max_ctx=self.cache.max_model_len,
                           h_q_start=list(range(nb + 1)), h_start_pos=[0] * nb, h_slots=[pad] * nb,
                           force_exact_attention=self.force_exact_attention, graph_max_ctx=self.cache.max_model_len)
-        from .. import ops
         tokens = torch.zeros(nb, dtype=torch.int32, device=dev)
 
         def run():
@@ -245,9 +264,12 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = run()
-        g = _DecodeGraph(graph, buf, host, logits, tokens, nb)
+        per_replay = ops.launch_count() - before
+        hosts = [host] + [host.clone().pin_memory() for _ in range(3)]
+        g = _DecodeGraph(graph, buf, hosts, [None] * len(hosts), logits, tokens, nb, launches=per_replay)
         self._graphs[nb] = g
         return g
 
@@ -256,7 +278,10 @@ class ModelRunner:
         n = len(entries)
         nb = self._bucket(n)
         g = self._graphs.get(nb) or self._capture(nb)
-        h = g.host.numpy()
+        turn = g.turn = (g.turn + 1) % len(g.hosts)          # staging buffers take turns, so that the host
+        if g.events[turn] is not None:                       # may prepare a step while earlier ones still run
+            g.events[turn].synchronize()
+        h = g.hosts[turn].numpy()
         pad = self.cache.padding_slot
         h[0:nb] = 0
         h[nb:2 * nb] = 0
@@ -273,10 +298,12 @@ class ModelRunner:
             h[2 * nb + i] = slot
             h[4 * nb + 1 + i] = p
             h[5 * nb + 1 + i] = slot
-        g.buf.copy_(g.host, non_blocking=True)
-        for t_dev, t_host in zip(self.tables, self._host_tables):
-            t_dev.copy_(t_host, non_blocking=True)
+        g.buf.copy_(g.hosts[turn], non_blocking=True)
+        g.events[turn] = torch.cuda.Event()
+        g.events[turn].record()
+        self._sync_tables()
         g.graph.replay()
+        ops.count_launches(g.launches)
         self.graph_replays += 1
         for e in entries:
             self.positions[e.rid] += 1
@@ -287,7 +314,10 @@ class ModelRunner:
 class _DecodeGraph:
     graph: object
     buf: torch.Tensor
-    host: torch.Tensor
+    hosts: list                         # pinned staging buffers of the step's inputs
+    events: list                        # per staging buffer: its last copy to the device
     logits: torch.Tensor
     tokens: torch.Tensor
     batch: int
+    turn: int = 0
+    launches: int = 0                   # kernels of this package inside one replay

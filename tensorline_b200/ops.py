@@ -67,9 +67,25 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(status: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far in this process (a replayed CUDA graph counts the
+    launches it holds)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(status: int, what: str, launches: int = 1) -> None:
+    global _launches
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status} at launch")
+    _launches += launches
 
 
 def _contig(t: torch.Tensor, name: str) -> None:

@@ -73,7 +73,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                       nq, nkv, int(window or 0), float(scale), chunk, splits,
                                       _ptr(part_o) if splits > 1 else None, _ptr(part_ml) if splits > 1 else None,
-                                      _stream()), "attn_decode")
+                                      _stream()), "attn_decode", launches=2 if splits > 1 else 1)
 
 
 def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale) -> None:
