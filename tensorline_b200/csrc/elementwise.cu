@@ -60,15 +60,107 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     }
 }
 
+// The fast path: H a multiple of 4, each thread keeps its NV chunks of 4 values in registers, so
+// every load of the row is in flight at once and x, r are read exactly once.  Same arithmetic.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 t;
+        t.x = *reinterpret_cast<uint32_t*>(&a); t.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+};
+
+template <typename TA, typename TW, int NV>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ r,
+                                       const TW* __restrict__ w, TA* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps, int write_x) {
+    __shared__ float red[33];
+    const int i = blockIdx.x, nvec = H >> 2;
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+    float v[NV][4], wv[NV][4];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) {
+            Vec4<float>::load(x + src + 4 * c, v[k]);
+            Vec4<TW>::load(w + 4 * c, wv[k]);
+        }
+    }
+    if (r) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) {
+                float rv[4];
+                Vec4<TA>::load(r + src + 4 * c, rv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[k][e] = v[k][e] + rv[e];
+                if (write_x) Vec4<float>::store(x + src + 4 * c, v[k]);
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+        if (threadIdx.x + k * blockDim.x < nvec)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(v[k][e], v[k][e], ss);
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = to_f<TA>(from_f<TA>(v[k][e] * rstd)) * wv[k][e];
+            Vec4<TA>::store(out + (size_t)i * H + 4 * c, o);
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static void launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, const int* rows, int R, int H,
+                               float eps, int write_x, cudaStream_t stream) {
+    const int nvec = H >> 2;
+    const bool vec = (H & 3) == 0 && nvec <= 8192 &&
+                     ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out) & 15) == 0);
+#define VLAUNCH(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
+        add_rmsnorm_vec_kernel<TA, TW, NV><<<R, th, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x); }
+    if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x);
+    else if (nvec <= 1024) VLAUNCH(1)
+    else if (nvec <= 2048) VLAUNCH(2)
+    else if (nvec <= 4096) VLAUNCH(4)
+    else VLAUNCH(8)
+#undef VLAUNCH
+}
+
 TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype, void* out, int act_dtype,
                              const int* rows, int R, int H, float eps, int write_x, cudaStream_t stream) {
     if (R <= 0) return 0;
-    const int threads = 256;
-#define LAUNCH(TA, TW) add_rmsnorm_kernel<TA, TW><<<R, threads, 0, stream>>>( \
-        (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x)
-    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) LAUNCH(float, float); else LAUNCH(float, bf16); }
-    else                     { if (w_dtype == TL_F32) LAUNCH(bf16, float);  else LAUNCH(bf16, bf16); }
-#undef LAUNCH
+    if (act_dtype == TL_F32) {
+        if (w_dtype == TL_F32) launch_add_rmsnorm<float, float>(x, r, w, out, rows, R, H, eps, write_x, stream);
+        else launch_add_rmsnorm<float, bf16>(x, r, w, out, rows, R, H, eps, write_x, stream);
+    } else {
+        if (w_dtype == TL_F32) launch_add_rmsnorm<bf16, float>(x, r, w, out, rows, R, H, eps, write_x, stream);
+        else launch_add_rmsnorm<bf16, bf16>(x, r, w, out, rows, R, H, eps, write_x, stream);
+    }
     return tl_launch_status();
 }
 
