@@ -76,19 +76,40 @@ struct AttnArgs {
     float* part_o; float* part_ml;     // [B, nq, splits, D] and [B, nq, splits, 2]
 };
 
-// Loads keys [key0, key0 + BN) of one KV head into a [BN][DP] tile; keys past `last_key` are zeros.
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const int* tab, int page_size,
-                                             int nkv, int kh, int key0, int last_key, int tid, int nthreads) {
-    for (int idx = tid; idx < BN * CH; idx += nthreads) {
-        const int key = idx / CH, c = idx - key * CH;
-        const int j = key0 + key;
-        const bool valid = j <= last_key;
-        const bf16* src = pages;
-        if (valid) {
-            const int page = tab[j / page_size];
-            src = pages + (((size_t)page * nkv + kh) * page_size + (j % page_size)) * D + c * 8;
+// A [BN][DP] tile of keys (or values) of one KV head is filled by 128 threads, CH/2 chunks of 16
+// bytes each.  Which chunk a thread copies never changes, so its place inside a page, its page
+// within the tile and its place in shared memory are worked out once (`TileMap`); a tile then costs
+// one table read, one multiply-add and one cp.async per chunk.
+constexpr int LD_ITERS = CH / 2;       // BN * CH / 128
+
+struct TileMap {
+    uint32_t src[LD_ITERS];            // key << 26 | page within tile << 20 | element offset inside the page
+    uint32_t dst[LD_ITERS];            // element offset inside the shared tile
+    __device__ __forceinline__ void init(int tid, int page_size) {
+#pragma unroll
+        for (int i = 0; i < LD_ITERS; ++i) {
+            const int idx = tid + 128 * i;
+            const int key = idx / CH, c = idx - key * CH;
+            src[i] = ((uint32_t)key << 26) | ((uint32_t)(key / page_size) << 20) |
+                     (uint32_t)((key % page_size) * D + c * 8);
+            dst[i] = key * DP + c * 8;
         }
-        cp_async16(dst + key * DP + c * 8, src, valid);
+    }
+};
+
+// Loads keys [key0, key0 + BN) (key0 a multiple of BN) into `dst`; keys past `last_key` are zeros.
+// `tab` points at the table entry of key0's page: the request's table row in global memory, or a
+// copy of the block's part of it in shared memory.  `pages` points at the KV head's part of page 0.
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const int* tab, size_t page_stride,
+                                             int key0, int last_key, const TileMap& map) {
+    const int keys_valid = last_key - key0;               // keys 0..keys_valid of the tile exist
+#pragma unroll
+    for (int i = 0; i < LD_ITERS; ++i) {
+        const int key = map.src[i] >> 26;
+        const bool valid = key <= keys_valid;
+        const bf16* src = pages;
+        if (valid) src = pages + (size_t)tab[(map.src[i] >> 20) & 63] * page_stride + (map.src[i] & 0xFFFFF);
+        cp_async16(dst + map.dst[i], src, valid);
     }
 }
 
@@ -105,6 +126,22 @@ __device__ __forceinline__ void qk_tile(float (&s)[NB][4], const bf16* sQ_rows, 
             ldsm_x4(b, sK + (key_off + nb * 8 + (lane & 7) + (lane >> 4) * 8) * DP + kb * 16 + ((lane >> 3) & 1) * 8);
             mma_bf16(s[nb], a, b[0], b[1]);
             mma_bf16(s[nb + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// The same with the Q fragments already in registers.
+template <int NB>
+__device__ __forceinline__ void qk_tile_regs(float (&s)[NB][4], const uint32_t (&qf)[KBLK][4], const bf16* sK,
+                                             int key_off, int lane) {
+#pragma unroll
+    for (int kb = 0; kb < KBLK; ++kb) {
+#pragma unroll
+        for (int nb = 0; nb < NB; nb += 2) {
+            uint32_t b[4];
+            ldsm_x4(b, sK + (key_off + nb * 8 + (lane & 7) + (lane >> 4) * 8) * DP + kb * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[nb], qf[kb], b[0], b[1]);
+            mma_bf16(s[nb + 1], qf[kb], b[2], b[3]);
         }
     }
 }
@@ -150,13 +187,20 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    // Once the running maxima have settled, a tile leaves them as they are and nothing needs rescaling.
+    const bool grew = __any_sync(0xffffffffu, mx[0] > m[0] || mx[1] > m[1]);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
         const float m_new = fmaxf(m[r], mx[r]);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;     // a row with no visible key yet
-        const float alpha = exp2f(m[r] - m_use);                    // m = -inf gives 0
-        m[r] = m_new;
-        l[r] *= alpha;
+        if (grew) {
+            const float alpha = exp2f(m[r] - m_use);                // m = -inf gives 0
+            m[r] = m_new;
+            l[r] *= alpha;
 #pragma unroll
-        for (int nb = 0; nb < D / 8; ++nb) { o[nb][2 * r] *= alpha; o[nb][2 * r + 1] *= alpha; }
+            for (int nb = 0; nb < D / 8; ++nb) { o[nb][2 * r] *= alpha; o[nb][2 * r + 1] *= alpha; }
+        }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const float p0 = exp2f(s[nb][2 * r] - m_use), p1 = exp2f(s[nb][2 * r + 1] - m_use);
@@ -199,8 +243,14 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
         cp_async16(sQ + r * DP + c * 8, src, valid);
     }
-    load_kv_tile(sK, A.k_pages, tab, A.page_size, A.nkv, kh, kt_lo * BN, pos_hi, tid, 128);
-    load_kv_tile(sV, A.v_pages, tab, A.page_size, A.nkv, kh, kt_lo * BN, pos_hi, tid, 128);
+    TileMap map;
+    map.init(tid, A.page_size);
+    const size_t page_stride = (size_t)A.nkv * A.page_size * D;
+    const int ppt = BN / A.page_size;                       // pages per tile
+    const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
+    const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
+    load_kv_tile(sK, kbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map);
+    load_kv_tile(sV, vbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map);
     cp_async_commit();
 
     int pos_r[2], lo_r[2];
@@ -225,8 +275,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         cp_async_wait<0>();
         __syncthreads();                                   // tile kt is in; everyone is done with tile kt-1
         if (kt < kt_hi) {
-            load_kv_tile(sK + (buf ^ 1) * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, (kt + 1) * BN, pos_hi, tid, 128);
-            load_kv_tile(sV + (buf ^ 1) * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, (kt + 1) * BN, pos_hi, tid, 128);
+            load_kv_tile(sK + (buf ^ 1) * BN * DP, kbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map);
+            load_kv_tile(sV + (buf ^ 1) * BN * DP, vbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map);
         }
         cp_async_commit();
         // skip tiles wholly outside this warp's rows (above the diagonal or behind the window)
@@ -257,6 +307,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
 
 // ------------------------------------------------------------------------------------ decode
 constexpr int DEC_STAGES = 3;
+constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
+constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
+constexpr int DECODE_TAB_OFFSET = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
+constexpr int DECODE_MAX_TAB = 2048;                    // table entries a block may copy (8 KB)
 
 // grid (splits * m_tiles, nkv, B); 4 warps; each stage is 64 keys, 16 per warp.
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
@@ -275,8 +329,18 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     if (k_begin >= len) return;                            // an empty split: the combine step skips it too
     const int k_end = min(len, k_begin + A.chunk);
     const int n_stage = (k_end - k_begin + BN - 1) / BN;
-    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* gtab = A.table + (size_t)A.slots[b] * A.max_pages;
     const int qrow = A.q_start[b];
+    // this block's part of the request's block table, copied once
+    int* stab = reinterpret_cast<int*>(smem_raw + DECODE_TAB_OFFSET);
+    const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
+    const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
+    for (int i = tid; i < n_stage * ppt; i += 128) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
+    TileMap map;
+    map.init(tid, A.page_size);
+    const size_t page_stride = (size_t)A.nkv * A.page_size * D;
+    const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
+    const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
 
     for (int idx = tid; idx < 16 * CH; idx += 128) {
         const int r = idx / CH, c = idx - r * CH;
@@ -286,14 +350,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         if (valid) src = A.q + (size_t)qrow * A.q_stride + (size_t)(kh * g + hg) * D + c * 8;
         cp_async16(sQ + r * DP + c * 8, src, valid);
     }
+    cp_async_commit();                                     // group 0: the queries
+    __syncthreads();                                       // the table copy is visible
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
         if (st < n_stage) {
-            load_kv_tile(sK + st * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, k_begin + st * BN, k_end - 1, tid, 128);
-            load_kv_tile(sV + st * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, k_begin + st * BN, k_end - 1, tid, 128);
+            load_kv_tile(sK + st * BN * DP, kbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map);
+            load_kv_tile(sV + st * BN * DP, vbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map);
         }
         cp_async_commit();
     }
+    cp_async_wait<DEC_STAGES - 1>();                       // the queries are in
+    __syncthreads();
+    uint32_t qf[KBLK][4];                                  // Q fragments stay in registers for the whole range
+#pragma unroll
+    for (int kb = 0; kb < KBLK; ++kb)
+        ldsm_x4(qf[kb], sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + kb * 16 + (lane >> 4) * 8);
     const int pos_r[2] = {k_end - 1, k_end - 1};           // every row sees all keys of the range
     const int lo_r[2] = {max(lo, k_begin), max(lo, k_begin)};
     float o[D / 8][4];
@@ -306,8 +378,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         __syncthreads();
         if (st + DEC_STAGES - 1 < n_stage) {
             const int nst = st + DEC_STAGES - 1, nb_ = nst % DEC_STAGES;
-            load_kv_tile(sK + nb_ * BN * DP, A.k_pages, tab, A.page_size, A.nkv, kh, k_begin + nst * BN, k_end - 1, tid, 128);
-            load_kv_tile(sV + nb_ * BN * DP, A.v_pages, tab, A.page_size, A.nkv, kh, k_begin + nst * BN, k_end - 1, tid, 128);
+            load_kv_tile(sK + nb_ * BN * DP, kbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map);
+            load_kv_tile(sV + nb_ * BN * DP, vbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map);
         }
         cp_async_commit();
         const int buf = st % DEC_STAGES;
@@ -316,7 +388,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         float s[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
-        qk_tile<2>(s, sQ, sK + buf * BN * DP, warp * 16, lane);
+        qk_tile_regs<2>(s, qf, sK + buf * BN * DP, warp * 16, lane);
         softmax_step<2>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
         pv_tile<2>(o, s, sV + buf * BN * DP, warp * 16, lane);
     }
@@ -394,16 +466,14 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
 }
 
 constexpr int PREFILL_SMEM = (BM + 4 * BN) * DP * 2;
-constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
-constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
-constexpr int DECODE_SMEM = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
+constexpr int DECODE_SMEM_MAX = DECODE_TAB_OFFSET + DECODE_MAX_TAB * 4;
 
 int g_attr_done = 0;
 int set_attrs() {
     if (g_attr_done) return 0;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
+    e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM_MAX);
     if (e != cudaSuccess) return (int)e;
     g_attr_done = 1;
     return 0;
@@ -455,7 +525,9 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
-    attn_decode_kernel<<<grid, 128, DECODE_SMEM, stream>>>(A);
+    const int tab_entries = chunk / page_size;            // of the longest range a block can have
+    if (tab_entries > DECODE_MAX_TAB) return 1;
+    attn_decode_kernel<<<grid, 128, DECODE_TAB_OFFSET + tab_entries * 4, stream>>>(A);
     e = tl_launch_status();
     if (e || splits == 1) return e;
     dim3 cgrid(nq, B);

@@ -36,13 +36,20 @@ def attn_lib(head_dim: int):
     return lib
 
 
-def plan_splits(batch: int, nkv: int, group: int, span: int, max_splits: int = 64) -> tuple:
-    """(chunk, splits) for a decode step: enough blocks to fill the GPU about twice, each with at
-    least one tile of keys; `span` is the largest number of keys a request can read."""
+def decode_blocks_per_sm(head_dim: int) -> int:
+    """Decode blocks that fit one SM: three stages of 64 keys and values, rows padded by 8 elements."""
+    smem = 16 * (head_dim + 8) * 2 + max(2 * 3 * KEY_TILE * (head_dim + 8) * 2, (4 * 16 * head_dim + 128) * 4) + 2048
+    return max(1, min(3, (227 * 1024) // (smem + 1024)))
+
+
+def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128, max_splits: int = 128) -> tuple:
+    """(chunk, splits) for a decode step.  As many ranges of keys per request as fill the GPU's
+    resident blocks once (a second, partly filled round of blocks would double the time), each a
+    whole number of 64-key tiles; `span` is the largest number of keys a request can read."""
     m_tiles = -(-group // 16)
     tiles = max(1, -(-span // KEY_TILE))
-    want = max(1, -(-2 * NUM_SMS // max(1, batch * nkv * m_tiles)))
-    splits = max(1, min(want, tiles, max_splits))
+    resident = NUM_SMS * decode_blocks_per_sm(head_dim)
+    splits = max(1, min(resident // max(1, batch * nkv * m_tiles), tiles, max_splits))
     chunk = -(-tiles // splits) * KEY_TILE
     splits = -(-tiles * KEY_TILE // chunk)
     return chunk, splits
@@ -84,7 +91,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         span = ctx.graph_max_ctx or ctx.max_ctx
         if window:
             span = min(span, window + KEY_TILE - 1)
-        chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span)
+        chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span, d)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
