@@ -49,6 +49,77 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
     }
 }
 
+// The bfloat16 fast path (full rotary, d % 16 == 0): one block per token; the token's d/2 cosines and
+// sines are computed once into shared memory and shared by all heads; each thread moves 8 + 8 values
+// (two 16-byte loads, two 16-byte stores).  Same arithmetic as the kernel above.
+template <typename TW>
+__global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict__ bias,
+                                   const int* __restrict__ pos, const int* __restrict__ req_slot,
+                                   const int* __restrict__ table, int max_pages, int page_size,
+                                   const float* __restrict__ inv_freq, int nq, int nkv, int d,
+                                   bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int heads) {
+    extern __shared__ float cs[];                                // cos[half], sin[half]
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    const int half = d >> 1, per_head = half >> 3;               // threads per head
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf(__fmul_rn((float)p, inv_freq[i]), &s, &c);
+        cs[i] = c; cs[half + i] = s;
+    }
+    size_t page_base = 0;
+    if (heads > nq) {
+        const int page = table[(size_t)req_slot[t] * max_pages + p / page_size];
+        page_base = ((size_t)page * nkv * page_size + (p % page_size)) * d;
+    }
+    __syncthreads();
+    bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+    for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+        const int hh = item / per_head, i0 = (item - hh * per_head) * 8;
+        const uint4 av = *reinterpret_cast<const uint4*>(row + hh * d + i0);
+        const uint4 bv = *reinterpret_cast<const uint4*>(row + hh * d + half + i0);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+        float a[8], b[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            a[2 * k] = __low2float(a2[k]); a[2 * k + 1] = __high2float(a2[k]);
+            b[2 * k] = __low2float(b2[k]); b[2 * k + 1] = __high2float(b2[k]);
+        }
+        if (bias) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                a[k] += to_f<TW>(bias[hh * d + i0 + k]);
+                b[k] += to_f<TW>(bias[hh * d + half + i0 + k]);
+            }
+        }
+        if (hh < nq + nkv) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float c = cs[i0 + k], s = cs[half + i0 + k];
+                const float ra = __fmul_rn(a[k], c) - __fmul_rn(b[k], s);
+                const float rb = __fmul_rn(b[k], c) + __fmul_rn(a[k], s);
+                a[k] = ra; b[k] = rb;
+            }
+        }
+        uint4 ao, bo;
+        __nv_bfloat162* ao2 = reinterpret_cast<__nv_bfloat162*>(&ao);
+        __nv_bfloat162* bo2 = reinterpret_cast<__nv_bfloat162*>(&bo);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            ao2[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
+            bo2[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]);
+        }
+        bf16* dst = row + hh * d;
+        if (hh >= nq) {
+            const int kh = hh < nq + nkv ? hh - nq : hh - nq - nkv;
+            dst = (hh < nq + nkv ? k_pages : v_pages) + page_base + (size_t)kh * page_size * d;
+        }
+        *reinterpret_cast<uint4*>(dst + i0) = ao;
+        *reinterpret_cast<uint4*>(dst + half + i0) = bo;
+    }
+}
+
 TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int bias_dtype,
                                const int* pos, const int* req_slot, const int* table, int max_pages,
                                int page_size, const float* inv_freq, int rot, int nq, int nkv, int d,
@@ -57,6 +128,19 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
     const int heads = write_kv ? nq + 2 * nkv : nq;
     if (heads > 65535) return 1;
+    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0);
+    if (act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned) {
+        const int items = heads * (d / 16);
+        const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
+        const size_t smem = (size_t)d * sizeof(float);
+        if (bias_dtype == TL_F32)
+            rope_kv_vec_kernel<float><<<T, threads, smem, stream>>>((bf16*)qkv, (const float*)bias, pos, req_slot, table,
+                max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
+        else
+            rope_kv_vec_kernel<bf16><<<T, threads, smem, stream>>>((bf16*)qkv, (const bf16*)bias, pos, req_slot, table,
+                max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
+        return tl_launch_status();
+    }
     dim3 grid(T, heads);
     const int half = d / 2;
     const int threads = half < 256 ? ((half + 31) / 32) * 32 : 256;

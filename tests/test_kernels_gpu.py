@@ -59,9 +59,10 @@ def test_add_rmsnorm(adt, wdt, H):
 
 
 @pytest.mark.parametrize("adt", DT)
-def test_silu_mul(adt):
+@pytest.mark.parametrize("I", [37, 40])
+def test_silu_mul(adt, I):
     from tensorline_b200 import ops
-    T, I = 5, 37
+    T = 5
     gu = rnd(T, 2 * I, seed=5, scale=3.0, dtype=adt)
     out = torch.empty(T, I, dtype=adt, device="cuda")
     ops.silu_mul(gu.cuda(), out)
@@ -85,9 +86,10 @@ def test_gemm_f32_exact_order(wdt):
 
 @pytest.mark.parametrize("adt", DT)
 @pytest.mark.parametrize("rot", [None, 8])
-def test_rope_and_kv_write(adt, rot):
+@pytest.mark.parametrize("d", [24, 32])
+def test_rope_and_kv_write(adt, rot, d):
     from tensorline_b200 import ops
-    nq, nkv, d, ps, theta = 3, 1, 24, 4, 5000.0
+    nq, nkv, ps, theta = 3, 2, 4, 5000.0
     rdim = d if rot is None else rot
     pos = [0, 1, 2, 9, 10, 4097]
     slots = [1, 1, 1, 0, 0, 2]
