@@ -534,3 +534,89 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
     return tl_launch_status();
 }
+
+// ------------------------------------------------------------------------------------ no allocation
+// tl_attn_decode_static: the split-KV decode attention for callers that cannot allocate device
+// memory (declared in attn_static.h, which says who they are).  Same kernels as tl_attn_decode; the
+// float partials of the key ranges live in the file-scope array below instead of caller-provided
+// buffers.  This file has no counterpart for it in tzar-beep/Tensorline.
+#include "attn_static.h"
+#include <stdio.h>
+
+static __device__ __align__(256) float g_static_partials[TL_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_ptr[MAX_DEVICES] = {};      // device address of the array, per device, set at the first call
+
+int fail(char* err, int err_len, int code, const char* msg) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", msg);
+    return code;
+}
+}  // namespace
+
+TL_EXPORT int tl_attn_decode_static(const void* q, int q_stride, void* out, const void* k_pages,
+                                    const void* v_pages, const int* table, int max_pages, int page_size,
+                                    const int* q_start, const int* start_pos, const int* slots, int B, int nq,
+                                    int nkv, int window, float scale, int chunk, int splits,
+                                    cudaStream_t stream, char* err, int err_len) {
+    if (err && err_len > 0) err[0] = 0;
+    if (B <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || page_size <= 0 || BN % page_size || chunk <= 0 || chunk % BN || splits < 1)
+        return fail(err, err_len, 1, "tl_attn_decode_static: heads must group evenly, the page size must divide 64, "
+                                     "chunk must be a positive multiple of 64 and splits at least 1");
+    const size_t need = (size_t)B * nq * splits * (D + 2);         // partial outputs, then (max, sum) pairs
+    if (splits > 1 && need > (size_t)TL_ATTN_STATIC_SCRATCH_FLOATS) {
+        char msg[256];
+        snprintf(msg, sizeof msg, "tl_attn_decode_static: B*nq*splits*(head_dim+2) = %zu floats of partials exceed "
+                 "the static scratch of %d floats; use fewer splits or a smaller batch", need,
+                 (int)TL_ATTN_STATIC_SCRATCH_FLOATS);
+        return fail(err, err_len, 2, msg);
+    }
+    int dev = -1;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return fail(err, err_len, 3, "tl_attn_decode_static: no current CUDA device (or its index is 64 or more)");
+    if (g_static_ptr[dev] == nullptr) {
+        // Set-up, once per device, with that device current: in host code the array's name is only a
+        // handle; the address the kernels need comes from the runtime.
+        void* p = nullptr;
+        ce = cudaGetSymbolAddress(&p, g_static_partials);
+        if (ce != cudaSuccess || p == nullptr) {
+            char msg[256];
+            snprintf(msg, sizeof msg, "tl_attn_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(ce));
+            return fail(err, err_len, 4, msg);
+        }
+        g_static_ptr[dev] = static_cast<float*>(p);
+    }
+    int e = set_attrs();
+    if (e) return fail(err, err_len, 5, "tl_attn_decode_static: cannot raise the kernels' shared-memory limit");
+    const int tab_entries = chunk / page_size;
+    if (tab_entries > DECODE_MAX_TAB)
+        return fail(err, err_len, 6, "tl_attn_decode_static: chunk / page_size exceeds the block-table copy of a block");
+    AttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
+    A.chunk = chunk; A.splits = splits;
+    A.part_o = g_static_ptr[dev];
+    A.part_ml = g_static_ptr[dev] + (size_t)B * nq * splits * D;
+    const int g = nq / nkv, m_tiles = (g + 15) / 16;
+    dim3 grid(splits * m_tiles, nkv, B);
+    if (grid.z > 65535) return fail(err, err_len, 7, "tl_attn_decode_static: more than 65535 requests in one call");
+    attn_decode_kernel<<<grid, 128, DECODE_TAB_OFFSET + tab_entries * 4, stream>>>(A);
+    ce = cudaGetLastError();
+    if (ce == cudaSuccess && splits > 1) {
+        dim3 cgrid(nq, B);
+        attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
+        ce = cudaGetLastError();
+    }
+    if (ce != cudaSuccess) {
+        char msg[256];
+        snprintf(msg, sizeof msg, "tl_attn_decode_static: launch failed: %s", cudaGetErrorString(ce));
+        return fail(err, err_len, 8, msg);
+    }
+    return 0;
+}

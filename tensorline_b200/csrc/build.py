@@ -62,7 +62,7 @@ def build_dir() -> Path:
 
 def _digest(sources, flags) -> str:
     h = hashlib.sha256()
-    for f in sorted(CSRC.glob("*.cuh")) + [CSRC / s for s in sources]:
+    for f in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC / s for s in sources]:
         if not f.is_file():
             raise KernelBuildError(f"kernel source {f} is missing")
         h.update(f.name.encode())
