@@ -306,7 +306,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
 }
 
 // ------------------------------------------------------------------------------------ decode
-constexpr int DEC_STAGES = 3;
+#ifndef TL_DEC_STAGES
+#define TL_DEC_STAGES 3
+#endif
+constexpr int DEC_STAGES = TL_DEC_STAGES;
 constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
 constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
 constexpr int DECODE_TAB_OFFSET = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);

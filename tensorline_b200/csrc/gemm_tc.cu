@@ -1,0 +1,336 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (sm_100a): tcgen05.mma with the
+// accumulator in tensor memory, operands brought to shared memory by TMA.
+//
+//     D[a, b] = sum_k  A[a, k] * B[b, k]        A: [RA, K],  B: [RB, K],  both row-major (K-major)
+//
+// A is the operand that fills the 128 rows of the MMA tile, B the N side (BN = 16..256 columns).
+// The launcher maps a linear layer y = x W^T onto it in one of two ways:
+//   * many tokens (prefill):  A = x [T, K],  B = W [N, K];   y[a, b] = D[a, b]
+//   * few tokens (decode):    A = W [N, K],  B = x [T, K];   y[b, a] = D[a, b]   ("swap": the weight
+//     matrix takes the 128-row side, so a batch of 1..64 tokens wastes no tensor-core rows and every
+//     weight byte is streamed exactly once by large TMA copies).  With few 128-row tiles the K range is
+//     split over blockIdx.z and the float partials are summed by a second small kernel.
+//
+// One block = 6 warps: warp 0 issues the TMA loads (one thread), warp 1 allocates tensor memory and
+// issues the MMAs (one thread), warps 2..5 read the accumulator back (tcgen05.ld, one quarter of the
+// 128 lanes each) and store it.  A ring of STAGES shared-memory tiles (128-byte swizzle, as TMA writes
+// them and the MMA's shared-memory descriptors read them) is handed back and forth with mbarriers.
+// Every wait on an mbarrier is bounded: if it does not complete in about two seconds the block
+// records an error code in `status`, stops issuing work, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;                // rows of A per tile = MMA M
+constexpr int BK = 64;                 // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000LL;     // ~2 s at 2 GHz
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and records `code`) if the barrier did not flip in time or another
+// role of the block already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);             // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+    d |= (uint64_t)1 << 46;                             // version
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    void* out;            // bf16 or float [rows, ldo]
+    float* partial;       // [splits, RB or RA rows..] float, when splits > 1
+    int ldo;
+    int RA, RB, K;        // rows of A, rows of B, reduction length
+    int k_tiles_per_split;
+    int swap;             // 1: out[b, a] = D[a, b];  0: out[a, b] = D[a, b]
+    int out_f32;
+    int* status;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs G) {
+    extern __shared__ unsigned char smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* done_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN, split = blockIdx.z;
+    const int k_tiles_total = (G.K + BK - 1) / BK;
+    const int kt_begin = split * G.k_tiles_per_split;
+    const int kt_end = min(k_tiles_total, kt_begin + G.k_tiles_per_split);
+    const int n_kt = kt_end - kt_begin;                  // > 0 by construction of the grid
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        mbar_init(done_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                     // one warp allocates the accumulator columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        for (int i = 0; i < n_kt; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1)) break;
+            mbar_expect_tx(full_bar + s, STAGE_BYTES);
+            unsigned char* st = tiles + s * STAGE_BYTES;
+            tma_load_2d(st, &map_a, full_bar + s, (kt_begin + i) * BK, a0);
+            tma_load_2d(st + A_BYTES, &map_b, full_bar + s, (kt_begin + i) * BK, b0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        bool ok = true;
+        for (int i = 0; i < n_kt && ok; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, G.status, 2);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = smem_addr(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_bf16(tmem_base, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(b_addr + k * UMMA_K * 2), idesc,
+                          (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty_bar + s);                  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(done_bar);                   // the accumulator is complete
+    } else if (warp >= 2) {
+        // ---------------------------------------------------------------- epilogue: 4 warps, 32 lanes of TMEM each
+        if (mbar_wait(done_bar, 0, abort_flag, G.status, 3)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quarter = warp & 3;                // the TMEM lanes a warp may read: 32 * (warp % 4)
+            const int a = a0 + quarter * 32 + lane;      // row of A = TMEM lane
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(taddr + c0, r);
+                if (a >= G.RA) continue;
+                if (gridDim.z > 1) {                     // float partial, laid out like the output
+                    float* part = G.partial + (size_t)split * (G.swap ? (size_t)G.RB * G.RA : (size_t)G.RA * G.RB);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int b = b0 + c0 + j;
+                        if (b < G.RB) part[G.swap ? (size_t)b * G.RA + a : (size_t)a * G.RB + b] = __uint_as_float(r[j]);
+                    }
+                } else if (G.swap) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int b = b0 + c0 + j;
+                        if (b < G.RB) {
+                            if (G.out_f32) ((float*)G.out)[(size_t)b * G.ldo + a] = __uint_as_float(r[j]);
+                            else ((bf16*)G.out)[(size_t)b * G.ldo + a] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                } else {
+                    const int b = b0 + c0;
+                    if (G.out_f32) {
+                        float* dst = (float*)G.out + (size_t)a * G.ldo + b;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) if (b + j < G.RB) dst[j] = __uint_as_float(r[j]);
+                    } else {
+                        bf16* dst = (bf16*)G.out + (size_t)a * G.ldo + b;
+                        if (b + 16 <= G.RB && ((((uintptr_t)dst) & 15) == 0)) {
+                            uint4 v0, v1;
+                            uint32_t* p0 = reinterpret_cast<uint32_t*>(&v0);
+                            uint32_t* p1 = reinterpret_cast<uint32_t*>(&v1);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 lo = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                __nv_bfloat162 hi = __floats2bfloat162_rn(__uint_as_float(r[8 + 2 * j]), __uint_as_float(r[8 + 2 * j + 1]));
+                                p0[j] = *reinterpret_cast<uint32_t*>(&lo);
+                                p1[j] = *reinterpret_cast<uint32_t*>(&hi);
+                            }
+                            reinterpret_cast<uint4*>(dst)[0] = v0;
+                            reinterpret_cast<uint4*>(dst)[1] = v1;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) if (b + j < G.RB) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {                                   // give copies in flight time to land before the block's
+        const long long t0 = clock64();                  // shared memory is handed to another block
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// out = sum over splits of partial[s], converted; partial is [S, R, C] float, out [R, ldo].
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int out_f32,
+                                     int S, int R, int C, int ldo) {
+    const size_t total = (size_t)R * C;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < S; ++s) acc += partial[(size_t)s * total + idx];
+        const size_t r = idx / C, c = idx - r * C;
+        if (out_f32) ((float*)out)[r * ldo + c] = acc;
+        else ((bf16*)out)[r * ldo + c] = __float2bfloat16_rn(acc);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || fn == nullptr || q != cudaDriverEntryPointSuccess) return 100;
+    g_encode = (EncodeTiledFn)fn;
+    return 0;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of [box_rows, 64] and 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 101;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3 grid, cudaStream_t stream) {
+    constexpr int SMEM = STAGES * (BM + BN) * BK * 2 + 1024 + (2 * STAGES + 1) * 8 + 16;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, SMEM, stream>>>(ma, mb, G);
+    return tl_launch_status();
+}
+
+}  // namespace
+
+// y[T, N] = x[T, K] w[N, K]^T.  swap = 1 puts w on the 128-row side (few tokens), swap = 0 puts x there.
+// bn: columns of the other side per tile (16, 32, 64, 128 or 256).  splits > 1 needs `partial`
+// (splits * T * N floats) and sums it into y with a second kernel.  `status` (device int, zero before
+// the call) receives a non-zero code if a wait inside the kernel ran out.
+TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
+                         int bn, int splits, float* partial, int* status, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
+    if (splits < 1 || (splits > 1 && partial == nullptr)) return 1;
+    int e = get_encode();
+    if (e) return e;
+    const void* a = swap ? w : x;
+    const void* b = swap ? x : w;
+    const int RA = swap ? N : T, RB = swap ? T : N;
+    CUtensorMap ma, mb;
+    if ((e = make_map(&ma, a, RA, K, BM))) return e;
+    if ((e = make_map(&mb, b, RB, K, bn))) return e;
+    const int k_tiles = (K + BK - 1) / BK;
+    if (splits > k_tiles) splits = k_tiles;
+    const int per = (k_tiles + splits - 1) / splits;
+    splits = (k_tiles + per - 1) / per;                                                  // no empty split
+    GemmArgs G{};
+    G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
+    G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
+    dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return 1;
+    switch (bn) {
+        case 16:  e = launch<16, 5>(ma, mb, G, grid, stream); break;
+        case 32:  e = launch<32, 5>(ma, mb, G, grid, stream); break;
+        case 64:  e = launch<64, 4>(ma, mb, G, grid, stream); break;
+        case 128: e = launch<128, 6>(ma, mb, G, grid, stream); break;
+        case 256: e = launch<256, 4>(ma, mb, G, grid, stream); break;
+        default: return 1;
+    }
+    if (e || splits == 1) return e;
+    const size_t total = (size_t)T * N;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, y, out_f32, splits, T, N, ldo);
+    return tl_launch_status();
+}

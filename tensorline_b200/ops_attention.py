@@ -7,6 +7,7 @@ which also serves decoded tokens that ride along with prompt portions.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -27,7 +28,10 @@ def attn_lib(head_dim: int):
         if head_dim % 16 or not 16 <= head_dim <= 256:
             raise KernelError(f"head_dim {head_dim}: the bfloat16 attention kernels take multiples of 16 "
                               "from 16 to 256")
-        lib = load_library(f"tl_attn_hd{head_dim}", ["attn_mma.cu"], {"HEAD_DIM": head_dim})
+        defines = {"HEAD_DIM": head_dim}
+        if os.environ.get("TL_DEC_STAGES"):
+            defines["TL_DEC_STAGES"] = int(os.environ["TL_DEC_STAGES"])
+        lib = load_library(f"tl_attn_hd{head_dim}", ["attn_mma.cu"], defines)
         lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P]
         lib.tl_attn_prefill.restype = ctypes.c_int
         lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
@@ -38,7 +42,8 @@ def attn_lib(head_dim: int):
 
 def decode_blocks_per_sm(head_dim: int) -> int:
     """Decode blocks that fit one SM: three stages of 64 keys and values, rows padded by 8 elements."""
-    smem = 16 * (head_dim + 8) * 2 + max(2 * 3 * KEY_TILE * (head_dim + 8) * 2, (4 * 16 * head_dim + 128) * 4) + 2048
+    stages = int(os.environ.get("TL_DEC_STAGES", 3))
+    smem = 16 * (head_dim + 8) * 2 + max(2 * stages * KEY_TILE * (head_dim + 8) * 2, (4 * 16 * head_dim + 128) * 4) + 2048
     return max(1, min(3, (227 * 1024) // (smem + 1024)))
 
 

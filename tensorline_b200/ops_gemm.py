@@ -1,0 +1,90 @@
+"""Launcher of the tcgen05 / TMA matrix product (`csrc/gemm_tc.cu`).
+
+    y[T, N] = x[T, K] w[N, K]^T     bfloat16 in, float32 accumulation in tensor memory
+
+With few tokens the weight matrix takes the 128-row side of the MMA tile ("swap") and, if it gives
+fewer tiles than the GPU has SMs, the reduction is split across blocks.  A device status word records
+a wait that ran out inside a kernel; `check_status()` reads it (a synchronising call, used by tests and
+at the end of a generation, never inside a step).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .csrc.build import load_library
+from .ops import KernelError, _check, _ptr, _stream
+
+_P, _I = ctypes.c_void_p, ctypes.c_int
+_lib = None
+_status: dict = {}
+NUM_SMS = 148
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
+        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]
+        l.tl_gemm_tc.restype = ctypes.c_int
+        _lib = l
+    return _lib
+
+
+def status_word(device) -> torch.Tensor:
+    t = _status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device] = t
+    return t
+
+
+def check_status() -> None:
+    """Raise if any kernel launched so far gave up on a wait (synchronises the device)."""
+    for dev, t in _status.items():
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"tcgen05 matrix product on {dev}: a pipeline wait ran out (role {code}); "
+                              "its output is not valid")
+
+
+def plan(T: int, N: int, K: int) -> tuple:
+    """(swap, bn, splits) for a product of T tokens."""
+    k_tiles = -(-K // 64)
+    if T <= 64:
+        bn = 16 if T <= 16 else 32 if T <= 32 else 64
+        tiles = -(-N // 128)
+        splits = 1
+        if tiles < 2 * NUM_SMS:                       # too few tiles to fill two blocks per SM: split K
+            splits = max(1, min(k_tiles // 4, -(-2 * NUM_SMS // tiles)))
+        return 1, bn, splits
+    return 0, 128 if N <= 4096 else 256, 1
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
+            splits=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: bfloat16 operands only")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not x.is_contiguous() or not w.is_contiguous():
+        raise KernelError("gemm_tc: x [T, K] and w [N, K] must be contiguous with equal K")
+    if K % 8:
+        raise KernelError(f"gemm_tc: K = {K} must be a multiple of 8 (TMA needs 16-byte rows)")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tc: output is bfloat16 or float32")
+    p_swap, p_bn, p_splits = plan(T, N, K)
+    swap = p_swap if swap is None else int(swap)
+    bn = p_bn if bn is None else bn
+    splits = p_splits if splits is None else splits
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    elif out.shape != (T, N) or out.dtype != out_dtype or out.stride(1) != 1:
+        raise KernelError("gemm_tc: out must be [T, N] of the output type with unit inner stride")
+    partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    st = status_word(x.device)
+    _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K, swap, bn,
+                            splits, _ptr(partial), _ptr(st), _stream()), "gemm_tc", launches=2 if splits > 1 else 1)
+    return out

@@ -71,6 +71,17 @@ class PlainQwen2:
                     self.window[i] = int(c["sliding_window"])
         self.w = {k: v.to(F64) for k, v in read_safetensors(folder / "model.safetensors").items()}
 
+    @classmethod
+    def from_tensors(cls, config: dict, tensors: dict, dtype=F64):
+        """The same from an in-memory config.json dictionary and name -> tensor map (no files)."""
+        import tempfile
+        with tempfile.TemporaryDirectory() as tmp:
+            (Path(tmp) / "config.json").write_text(json.dumps(config))
+            (Path(tmp) / "model.safetensors").write_bytes(struct.pack("<Q", 2) + b"{}")
+            m = cls(tmp)
+        m.w = {k: v.detach().cpu().to(dtype) for k, v in tensors.items()}
+        return m
+
     def layer(self, i, name):
         return self.w[f"model.layers.{i}.{name}"]
 
@@ -167,14 +178,17 @@ def decoder_layer(m: PlainQwen2, i, x, cos, sin):
                       m.layer(i, "mlp.down_proj.weight"))
 
 
-def forward(m: PlainQwen2, ids) -> torch.Tensor:
+def forward(m: PlainQwen2, ids, rows=None) -> torch.Tensor:
     """Logits [T, V] (float64) at every position of one whole sequence
-    (tensorline/paged.py:240-287 without the cache)."""
+    (tensorline/paged.py:240-287 without the cache); `rows`: only these positions."""
     ids = list(ids)
     x = embedding(m.w["model.embed_tokens.weight"], ids)
     cos, sin = rope_cos_sin(range(len(ids)), m.d, m.theta)
+    cos, sin = cos.to(x.dtype), sin.to(x.dtype)               # float64 unless the weights were narrowed
     for i in range(m.L):
         x = decoder_layer(m, i, x, cos, sin)
+    if rows is not None:
+        x = x[list(rows)]
     h = rms_norm(x, m.w["model.norm.weight"], m.eps)
     head = m.w["model.embed_tokens.weight"] if m.tied else m.w["lm_head.weight"]
     return linear(h, head)
