@@ -103,6 +103,7 @@ struct GemmArgs {
     int swap;             // 1: out[b, a] = D[a, b];  0: out[a, b] = D[a, b]
     int out_f32;
     int* status;
+    int* counters;        // one per output tile, zero between calls: the last block of a tile to finish sums the partials
 };
 
 template <int BN, int STAGES>
@@ -117,6 +118,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* done_bar = empty_bar + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* last_flag = abort_flag + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN, split = blockIdx.z;
@@ -181,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld16(taddr + c0, r);
                 if (a >= G.RA) continue;
                 if (gridDim.z > 1) {                     // float partial, laid out like the output
-                    float* part = G.partial + (size_t)split * (G.swap ? (size_t)G.RB * G.RA : (size_t)G.RA * G.RB);
+                    float* part = G.partial + (size_t)split * (size_t)G.RA * G.RB;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int b = b0 + c0 + j;
@@ -222,6 +224,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 16; ++j) if (b + j < G.RB) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
                         }
                     }
+                }
+            }
+            if (gridDim.z > 1 && G.counters != nullptr) {
+                // Split K inside one launch: every block of a tile publishes its partial, the block that
+                // arrives last adds them up in split order (so the sum does not depend on who was last).
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+                const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+                if (threadIdx.x == 64) *last_flag = atomicAdd(G.counters + tile_id, 1) == (int)gridDim.z - 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    if (a < G.RA) {
+                        const size_t plane = (size_t)G.RA * G.RB;
+                        for (int c = 0; c < BN; ++c) {
+                            const int b = b0 + c;
+                            if (b >= G.RB) break;
+                            const size_t idx = G.swap ? (size_t)b * G.RA + a : (size_t)a * G.RB + b;
+                            float acc = 0.f;
+                            for (int sp = 0; sp < (int)gridDim.z; ++sp) acc += __ldcg(G.partial + sp * plane + idx);
+                            const size_t o = G.swap ? (size_t)b * G.ldo + a : (size_t)a * G.ldo + b;
+                            if (G.out_f32) ((float*)G.out)[o] = acc;
+                            else ((bf16*)G.out)[o] = __float2bfloat16_rn(acc);
+                        }
+                    }
+                    if (threadIdx.x == 64) G.counters[tile_id] = 0;       // ready for the next call
                 }
             }
         }
@@ -281,7 +309,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3 grid, cudaStream_t stream) {
-    constexpr int SMEM = STAGES * (BM + BN) * BK * 2 + 1024 + (2 * STAGES + 1) * 8 + 16;
+    constexpr int SMEM = STAGES * (BM + BN) * BK * 2 + 1024 + (2 * STAGES + 1) * 8 + 32;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -296,10 +324,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
 
 // y[T, N] = x[T, K] w[N, K]^T.  swap = 1 puts w on the 128-row side (few tokens), swap = 0 puts x there.
 // bn: columns of the other side per tile (16, 32, 64, 128 or 256).  splits > 1 needs `partial`
-// (splits * T * N floats) and sums it into y with a second kernel.  `status` (device int, zero before
+// (splits * T * N floats); with `counters` (n_counters zeroed ints, at least one per tile, left zeroed) the
+// last block of a tile sums the partials inside the same launch, else a second kernel does.  `status` (device int, zero before
 // the call) receives a non-zero code if a wait inside the kernel ran out.
 TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
-                         int bn, int splits, float* partial, int* status, cudaStream_t stream) {
+                         int bn, int splits, float* partial, int* status, int* counters, int n_counters,
+                         cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
     if (splits < 1 || (splits > 1 && partial == nullptr)) return 1;
@@ -320,6 +350,7 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
     dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return 1;
+    G.counters = (splits > 1 && counters != nullptr && (long long)grid.x * grid.y <= n_counters) ? counters : nullptr;
     switch (bn) {
         case 16:  e = launch<16, 5>(ma, mb, G, grid, stream); break;
         case 32:  e = launch<32, 5>(ma, mb, G, grid, stream); break;
@@ -328,7 +359,7 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
         case 256: e = launch<256, 4>(ma, mb, G, grid, stream); break;
         default: return 1;
     }
-    if (e || splits == 1) return e;
+    if (e || splits == 1 || G.counters != nullptr) return e;
     const size_t total = (size_t)T * N;
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, y, out_f32, splits, T, N, ldo);

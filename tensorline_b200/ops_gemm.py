@@ -5,7 +5,9 @@
 With few tokens the weight matrix takes the 128-row side of the MMA tile ("swap") and, if it gives
 fewer tiles than the GPU has SMs, the reduction is split across blocks.  A device status word records
 a wait that ran out inside a kernel; `check_status()` reads it (a synchronising call, used by tests and
-at the end of a generation, never inside a step).
+at the end of a generation, never inside a step).  With `fused_reduce` the last block of a tile sums the
+split partials inside the same launch instead of a second kernel (faster for one token, slower from a few
+tokens on, so it is off by default).
 """
 from __future__ import annotations
 
@@ -26,16 +28,20 @@ def lib():
     global _lib
     if _lib is None:
         l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
-        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]
+        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P]
         l.tl_gemm_tc.restype = ctypes.c_int
         _lib = l
     return _lib
 
 
+N_COUNTERS = 8192
+
+
 def status_word(device) -> torch.Tensor:
+    """[0]: the status word; [1:]: the per-tile arrival counters of split products (zero between calls)."""
     t = _status.get(device)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
+        t = torch.zeros(1 + N_COUNTERS, dtype=torch.int32, device=device)
         _status[device] = t
     return t
 
@@ -43,7 +49,7 @@ def status_word(device) -> torch.Tensor:
 def check_status() -> None:
     """Raise if any kernel launched so far gave up on a wait (synchronises the device)."""
     for dev, t in _status.items():
-        code = int(t.item())
+        code = int(t[0].item())
         if code:
             t.zero_()
             raise KernelError(f"tcgen05 matrix product on {dev}: a pipeline wait ran out (role {code}); "
@@ -57,14 +63,14 @@ def plan(T: int, N: int, K: int) -> tuple:
         bn = 16 if T <= 16 else 32 if T <= 32 else 64
         tiles = -(-N // 128)
         splits = 1
-        if tiles < 2 * NUM_SMS:                       # too few tiles to fill two blocks per SM: split K
-            splits = max(1, min(k_tiles // 4, -(-2 * NUM_SMS // tiles)))
+        if tiles < NUM_SMS:                           # too few tiles to give every SM a block: split K so that
+            splits = max(1, min(k_tiles // 4, (2 * NUM_SMS - 40) // tiles))   # one round of blocks is nearly full
         return 1, bn, splits
     return 0, 128 if N <= 4096 else 256, 1
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
-            splits=None, out: torch.Tensor | None = None) -> torch.Tensor:
+            splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False) -> torch.Tensor:
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: bfloat16 operands only")
     T, K = x.shape
@@ -86,5 +92,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     st = status_word(x.device)
     _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K, swap, bn,
-                            splits, _ptr(partial), _ptr(st), _stream()), "gemm_tc", launches=2 if splits > 1 else 1)
+                            splits, _ptr(partial), _ptr(st), (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS,
+                            _stream()), "gemm_tc", launches=1 if (splits == 1 or fused_reduce) else 2)
     return out

@@ -1,14 +1,25 @@
 """Matrix products of the parts: y = x W^T, weights [out, in] (tensorline/quant.py:3).
 
-The 32-bit engine uses the exact-order FFMA kernel of this package.  The bfloat16 engine calls
-the library product (cuBLAS through torch), as tzar-beep/Tensorline's engine does for every
-projection (tensorline/paged.py:248-250, :275-276, :287), with float32 accumulation.
+The 32-bit engine uses the exact-order FFMA kernel of this package.  The bfloat16 engine has two
+routes, both with float32 accumulation:
+  * the hand-written tcgen05 / TMA kernel (`csrc/gemm_tc.cu`) for steps of few tokens against large
+    matrices, where it streams the weights faster than the library (measured on the 7B shapes: gate|up,
+    down and the output head at up to 16 tokens);
+  * the library product (cuBLAS through torch) everywhere else, as tzar-beep/Tensorline's engine does
+    for every projection (tensorline/paged.py:248-250, :275-276, :287).
 """
 from __future__ import annotations
 
 import torch
 
 from .. import ops
+
+TC_MAX_TOKENS = 16                 # the hand-written kernel wins up to this many tokens ...
+TC_MIN_WEIGHT_ELEMENTS = 48 << 20  # ... against matrices of at least this many elements
+
+
+def use_tc(tokens: int, n: int, k: int) -> bool:
+    return tokens <= TC_MAX_TOKENS and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -19,6 +30,9 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         return out
     if not x.is_cuda:
         raise ops.KernelError("matmul called with a CPU tensor: this engine has no CPU path")
+    if use_tc(x.shape[0], w.shape[0], w.shape[1]) and x.is_contiguous():
+        from .. import ops_gemm
+        return ops_gemm.gemm_tc(x, w, out_dtype or x.dtype)
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.mm(x, w.t())

@@ -245,3 +245,36 @@ def test_attention_refuses_unsupported_head_size():
         ops_attention.attn_lib(24)
     with pytest.raises(ops.KernelError):
         ops_attention.attn_lib(272)
+
+
+TC_CASES = [  # tokens, N, K, forced (swap, bn, splits) or None for the launcher's plan
+    (8, 128, 64, (1, 16, 1)), (8, 200, 1000, (1, 16, 1)), (37, 300, 520, (1, 64, 3)), (1, 3584, 2048, None),
+    (16, 4608, 3584, None), (130, 200, 72, (0, 128, 1)), (300, 520, 1000, (0, 256, 1)), (5, 264, 2056, (1, 32, 4)),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=[f"T{c[0]}N{c[1]}K{c[2]}" for c in TC_CASES])
+@pytest.mark.parametrize("fused", [False, True])
+def test_tcgen05_matrix_product(case, fused):
+    """The tensor-memory kernel against float64: both operand orders, ragged edges in every dimension,
+    K split across blocks with either way of summing the partials, float32 and bfloat16 outputs."""
+    from tensorline_b200 import ops_gemm
+    T, N, K, forced = case
+    x = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    w = rnd(N, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()
+    want = x.double() @ w.double().T
+    kw = dict(zip(("swap", "bn", "splits"), forced)) if forced else {}
+    y32 = ops_gemm.gemm_tc(x, w, torch.float32, fused_reduce=fused, **kw)
+    y16 = ops_gemm.gemm_tc(x, w, torch.bfloat16, fused_reduce=fused, **kw)
+    ops_gemm.check_status()
+    assert_close(y32, want, "float32 out", rtol=1e-4, atol=1e-4 * float(want.abs().max()))
+    assert_close(y16, want, "bfloat16 out", rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    assert int(ops_gemm.status_word(x.device)[1:].abs().sum()) == 0          # arrival counters are back at zero
+
+
+def test_tcgen05_matrix_product_refuses_unaligned_k():
+    from tensorline_b200 import ops, ops_gemm
+    x = torch.zeros(4, 36, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 36, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops_gemm.gemm_tc(x, w)
