@@ -20,6 +20,7 @@ memory, so there are no buckets over context length.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -264,10 +265,20 @@ class ModelRunner:
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
-        before = ops.launch_count()
-        with torch.cuda.graph(graph, pool=self._graph_pool):
-            logits = run()
-        per_replay = ops.launch_count() - before
+        # Nothing may free device memory while the stream is capturing: collect garbage (graphs and
+        # pools of engines that are gone) now, and keep the collector off until the capture ends.
+        gc.collect()
+        torch.cuda.synchronize()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            before = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="thread_local"):
+                logits = run()
+            per_replay = ops.launch_count() - before
+        finally:
+            if gc_was_on:
+                gc.enable()
         hosts = [host] + [host.clone().pin_memory() for _ in range(3)]
         g = _DecodeGraph(graph, buf, hosts, [None] * len(hosts), logits, tokens, nb, launches=per_replay)
         self._graphs[nb] = g

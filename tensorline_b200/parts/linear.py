@@ -10,6 +10,8 @@ routes, both with float32 accumulation:
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -18,8 +20,11 @@ TC_MAX_TOKENS = 16                 # the hand-written kernel wins up to this man
 TC_MIN_WEIGHT_ELEMENTS = 48 << 20  # ... against matrices of at least this many elements
 
 
+TC_ENABLED = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: library products only (for A/B timing)
+
+
 def use_tc(tokens: int, n: int, k: int) -> bool:
-    return tokens <= TC_MAX_TOKENS and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0
+    return TC_ENABLED and tokens <= TC_MAX_TOKENS and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
