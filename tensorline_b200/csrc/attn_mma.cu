@@ -76,35 +76,38 @@ struct AttnArgs {
     float* part_o; float* part_ml;     // [B, nq, splits, D] and [B, nq, splits, 2]
 };
 
-// A [BN][DP] tile of keys (or values) of one KV head is filled by 128 threads, CH/2 chunks of 16
-// bytes each.  Which chunk a thread copies never changes, so its place inside a page, its page
+// A [ROWS][DP] tile of keys (or values) of one KV head is filled by 128 threads in chunks of 16
+// bytes.  Which chunk a thread copies never changes, so its place inside a page, its page
 // within the tile and its place in shared memory are worked out once (`TileMap`); a tile then costs
 // one table read, one multiply-add and one cp.async per chunk.
-constexpr int LD_ITERS = CH / 2;       // BN * CH / 128
-
+template <int ROWS>
 struct TileMap {
-    uint32_t src[LD_ITERS];            // key << 26 | page within tile << 20 | element offset inside the page
-    uint32_t dst[LD_ITERS];            // element offset inside the shared tile
+    static constexpr int ITERS = (ROWS * CH + 127) / 128;
+    uint32_t src[ITERS];               // key << 26 | page within tile << 20 | element offset inside the page
+    uint32_t dst[ITERS];               // element offset inside the shared tile; 0xFFFFFFFF: no chunk
     __device__ __forceinline__ void init(int tid, int page_size) {
 #pragma unroll
-        for (int i = 0; i < LD_ITERS; ++i) {
+        for (int i = 0; i < ITERS; ++i) {
             const int idx = tid + 128 * i;
             const int key = idx / CH, c = idx - key * CH;
             src[i] = ((uint32_t)key << 26) | ((uint32_t)(key / page_size) << 20) |
                      (uint32_t)((key % page_size) * D + c * 8);
-            dst[i] = key * DP + c * 8;
+            dst[i] = idx < ROWS * CH ? (uint32_t)(key * DP + c * 8) : 0xFFFFFFFFu;
         }
     }
 };
 
-// Loads keys [key0, key0 + BN) (key0 a multiple of BN) into `dst`; keys past `last_key` are zeros.
-// `tab` points at the table entry of key0's page: the request's table row in global memory, or a
-// copy of the block's part of it in shared memory.  `pages` points at the KV head's part of page 0.
+// Loads keys [key0, key0 + ROWS) (key0 a multiple of ROWS, ROWS a multiple of the page size) into
+// `dst`; keys past `last_key` are zeros.  `tab` points at the table entry of key0's page: the
+// request's table row in global memory, or a copy of the block's part of it in shared memory.
+// `pages` points at the KV head's part of page 0.
+template <int ROWS>
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const int* tab, size_t page_stride,
-                                             int key0, int last_key, const TileMap& map) {
+                                             int key0, int last_key, const TileMap<ROWS>& map) {
     const int keys_valid = last_key - key0;               // keys 0..keys_valid of the tile exist
 #pragma unroll
-    for (int i = 0; i < LD_ITERS; ++i) {
+    for (int i = 0; i < TileMap<ROWS>::ITERS; ++i) {
+        if ((ROWS * CH) % 128 != 0 && map.dst[i] == 0xFFFFFFFFu) continue;
         const int key = map.src[i] >> 26;
         const bool valid = key <= keys_valid;
         const bf16* src = pages;
@@ -166,9 +169,17 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&p)[N
     }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {          // 2^x, hardware approximation (about 2 ulp); -inf gives 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Masks, scales and exponentiates one thread's share of S (rows ra = lane/4 and ra + 8), updates the
-// running max m[2], the per-thread partial sums l[2] and rescales O.  key0: position of S column 0.
-template <int NB>
+// running max m[2] (kept in scaled units), the per-thread partial sums l[2] and rescales O.
+// key0: position of S column 0.  MASKED = false: the caller knows every key of the tile is visible
+// to every row of the warp, and the comparisons are skipped.
+template <int NB, bool MASKED>
 __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                              const int (&pos_r)[2], const int (&lo_r)[2], int key0, float scale_log2,
                                              int lane) {
@@ -178,15 +189,17 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-            const float v = (j <= pos_r[r] && j >= lo_r[r]) ? s[nb][e] * scale_log2 : -INFINITY;
-            s[nb][e] = v;
-            mx[r] = fmaxf(mx[r], v);
+            if (MASKED) {
+                const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                if (!(j <= pos_r[r] && j >= lo_r[r])) s[nb][e] = -INFINITY;
+            }
+            mx[r] = fmaxf(mx[r], s[nb][e]);
         }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        mx[r] *= scale_log2;                                        // the scale is positive: max commutes with it
     }
     // Once the running maxima have settled, a tile leaves them as they are and nothing needs rescaling.
     const bool grew = __any_sync(0xffffffffu, mx[0] > m[0] || mx[1] > m[1]);
@@ -195,7 +208,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
         const float m_new = fmaxf(m[r], mx[r]);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;     // a row with no visible key yet
         if (grew) {
-            const float alpha = exp2f(m[r] - m_use);                // m = -inf gives 0
+            const float alpha = fast_exp2(m[r] - m_use);            // m = -inf gives 0
             m[r] = m_new;
             l[r] *= alpha;
 #pragma unroll
@@ -203,7 +216,8 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            const float p0 = exp2f(s[nb][2 * r] - m_use), p1 = exp2f(s[nb][2 * r + 1] - m_use);
+            const float p0 = fast_exp2(fmaf(s[nb][2 * r], scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(s[nb][2 * r + 1], scale_log2, -m_use));
             s[nb][2 * r] = p0; s[nb][2 * r + 1] = p1;
             l[r] += p0 + p1;
         }
@@ -211,7 +225,11 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
 }
 
 // ------------------------------------------------------------------------------------ prefill
+// PBN: keys per tile.  32 leaves room for three blocks per SM (more warps to hide the latencies of the
+// MMA / ldmatrix chains); 64 serves pages of 64 tokens.
+template <int PBN>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
+    constexpr int BN = PBN;                                // shadows the decode tile size inside this kernel
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [BM][DP]
     bf16* sK = sQ + BM * DP;                               // [2][BN][DP]
@@ -219,7 +237,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int kh = blockIdx.y, g = A.nq / A.nkv;
 
-    int tile = blockIdx.x, b = 0;
+    // Blocks are handed out in index order and a tile's work grows with its position in the request
+    // (causal), so the tiles are taken from the end: the longest ones start first.
+    int tile = gridDim.x - 1 - blockIdx.x, b = 0;
     for (; b < A.B; ++b) {
         const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
         if (tile < nt) break;
@@ -243,7 +263,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
         cp_async16(sQ + r * DP + c * 8, src, valid);
     }
-    TileMap map;
+    TileMap<BN> map;
     map.init(tid, A.page_size);
     const size_t page_stride = (size_t)A.nkv * A.page_size * D;
     const int ppt = BN / A.page_size;                       // pages per tile
@@ -285,7 +305,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
         qk_tile<BN / 8>(s, sQ + warp * 16 * DP, sK + buf * BN * DP, 0, lane);
-        softmax_step<BN / 8>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
+        // the tile's keys are all visible to all rows of the warp: below every row's position, inside
+        // every row's window
+        const bool full = (kt * BN + BN - 1 <= sp + wr_first / g) &&
+                          (A.window <= 0 || kt * BN >= max(0, w_pos_hi - A.window + 1));
+        if (full) softmax_step<BN / 8, false>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
+        else      softmax_step<BN / 8, true>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
         pv_tile<BN / 8>(o, s, sV + buf * BN * DP, 0, lane);
     }
     cp_async_wait<0>();
@@ -339,7 +364,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
     const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
     for (int i = tid; i < n_stage * ppt; i += 128) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
-    TileMap map;
+    TileMap<BN> map;
     map.init(tid, A.page_size);
     const size_t page_stride = (size_t)A.nkv * A.page_size * D;
     const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
@@ -392,7 +417,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
         qk_tile_regs<2>(s, qf, sK + buf * BN * DP, warp * 16, lane);
-        softmax_step<2>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        if (key0 + 16 <= k_end && key0 >= lo) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        else                                  softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
         pv_tile<2>(o, s, sV + buf * BN * DP, warp * 16, lane);
     }
     cp_async_wait<0>();
@@ -468,13 +494,15 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
     }
 }
 
-constexpr int PREFILL_SMEM = (BM + 4 * BN) * DP * 2;
+template <int PBN> constexpr int prefill_smem() { return (BM + 4 * PBN) * DP * 2; }
 constexpr int DECODE_SMEM_MAX = DECODE_TAB_OFFSET + DECODE_MAX_TAB * 4;
 
 int g_attr_done = 0;
 int set_attrs() {
     if (g_attr_done) return 0;
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREFILL_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<32>());
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<64>());
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM_MAX);
     if (e != cudaSuccess) return (int)e;
@@ -502,7 +530,8 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     dim3 grid(total_tiles, nkv);
-    attn_prefill_kernel<<<grid, 128, PREFILL_SMEM, stream>>>(A);
+    if (page_size <= 32) attn_prefill_kernel<32><<<grid, 128, prefill_smem<32>(), stream>>>(A);
+    else                 attn_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(A);
     return tl_launch_status();
 }
 
