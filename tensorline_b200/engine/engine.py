@@ -176,6 +176,19 @@ class Engine:
             outs.append(Output(r.output_tokens, r.stats.finish_reason, r.stats, text, r.tokens[:r.prompt_len]))
         return outs
 
+    def render_chat(self, messages: list) -> str:
+        """Chat messages as one prompt string (tensorline/engine.py:79-84): the tokenizer's template
+        if it has one, else "role: content" lines."""
+        if self.tokenizer is not None and getattr(self.tokenizer, "chat_template", None):
+            return self.tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=True)
+        return "".join(f"{m['role']}: {m['content']}\n" for m in messages) + "assistant:"
+
+    def shutdown(self) -> None:
+        """Fail what is still queued and drop the device tensors (tensorline/batch_engine.py:144-157)."""
+        self.scheduler.fail_all(RuntimeError("engine shut down"))
+        self._sync_runner()
+        self.runner = self.model = None
+
     # ------------------------------------------------------------------ figures
     def stats(self) -> dict:
         s = self.scheduler

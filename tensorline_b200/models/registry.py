@@ -64,7 +64,13 @@ def load_model(folder, rt: Runtime):
     arch, cfg = load_config(folder)
     model = Model(arch.describe(cfg), rt)
     expected = model.expected_tensors()
-    weights = load_weights(folder, expected, device=rt.device)
+    if model.spec.tie_word_embeddings:
+        # A tied head is the embedding table: a stored head is neither loaded nor an error.
+        head = f"{model.spec.head_prefix}.weight"
+        expected = {k: v for k, v in expected.items() if k != head}
+        weights = load_weights(folder, expected, device=rt.device, ignore=(head,))
+    else:
+        weights = load_weights(folder, expected, device=rt.device)
     model.bind(weights)
     return model, cfg
 

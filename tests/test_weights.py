@@ -91,3 +91,15 @@ def test_sharded_folder_with_index(tmp_path):
     (out / "model.safetensors.index.json").write_text(json.dumps(index))
     w = load_weights(out, expected_tensors(Qwen2Config.from_dict(TINY_A)))
     assert all(torch.equal(w[k], t[k]) for k in names)
+
+
+def test_tied_model_ignores_a_stored_head(tmp_path):
+    """A checkpoint of a tied model that also stores lm_head.weight loads; the head is not read."""
+    from tensorline_b200.models import load_model
+    from tensorline_b200.parts import Runtime
+    folder = write_tiny("A", tmp_path / "m")
+    t = read_safetensors(folder / "model.safetensors")
+    t["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)
+    write_safetensors(folder / "model.safetensors", t)
+    model, _ = load_model(folder, Runtime(torch.device("cpu"), torch.float32))
+    assert model.head.weight is model.embedding.weight
