@@ -47,6 +47,36 @@ def decode_blocks_per_sm(head_dim: int) -> int:
     return max(1, min(3, (227 * 1024) // (smem + 1024)))
 
 
+_tc_libs: dict = {}
+TC_QUERY_TILE = 128
+
+
+def attn_tc_lib(head_dim: int):
+    """The tcgen05 prefill attention compiled for this head size (64, 128, 192 or 256)."""
+    lib = _tc_libs.get(head_dim)
+    if lib is None:
+        if head_dim % 64 or not 64 <= head_dim <= 256:
+            raise KernelError(f"head_dim {head_dim}: the tcgen05 attention kernel takes 64, 128, 192 or 256")
+        lib = load_library(f"tl_attn_tc_hd{head_dim}", ["attn_tc.cu"], {"HEAD_DIM": head_dim})
+        lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P]
+        lib.tl_attn_tc_prefill.restype = ctypes.c_int
+        _tc_libs[head_dim] = lib
+    return lib
+
+
+def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
+               nq, nkv, d, window, scale) -> None:
+    """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory."""
+    from .ops_gemm import status_word
+    g = nq // nkv
+    B = len(h_q_start) - 1
+    tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // TC_QUERY_TILE) for i in range(B))
+    _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
+                                             table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
+                                             nq, nkv, int(window or 0), float(scale), tiles,
+                                             _ptr(status_word(q.device)), _stream()), "attn_tc_prefill")
+
+
 def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128, max_splits: int = 128) -> tuple:
     """(chunk, splits) for a decode step.  As many ranges of keys per request as fill the GPU's
     resident blocks once (a second, partly filled round of blocks would double the time), each a
