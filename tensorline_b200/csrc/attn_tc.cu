@@ -8,12 +8,16 @@
 //     P = exp2(S - m)    128 threads, one row each: tcgen05.ld, mask (key <= position, window), running
 //                        max and sum in float, P rounded to bfloat16 into shared memory (the same swizzle)
 //     O += P V           tcgen05.mma, V as the MN-major operand, O in tensor memory
-// K and V come straight from the cache pages (cp.async, 16 bytes, swizzled on the way in): this step's own
-// tokens were written there first (tensorline/paged.py:252-253), so fresh prompts, resumed portions and
-// decoded tokens riding along are one case.  The running maximum is only raised when a tile exceeds it by
-// more than 2^8, so the correction of O (a round trip through registers) is rare.  Formulas as in
-// tensorline/paged_attn.py:46-57: scores, max, sum and the accumulator in float, P in bfloat16 for P V.
-// Every mbarrier wait is bounded; on a time-out the block records a code in `status` and leaves.
+// Three roles run concurrently.  Warps 0..3 do the softmax, one row per thread.  One thread of warp 4
+// issues the MMAs.  Warps 5 and 6 copy K and V from the cache pages (cp.async, 16 bytes, swizzled on the way in):
+// this step's own tokens were written there first (tensorline/paged.py:252-253), so fresh prompts, resumed
+// portions and decoded tokens riding along are one case.  S, P, K and V are double-buffered, so the
+// tensor cores compute S of tile i+1 and O of tile i-1 while the softmax threads work on tile i, and the
+// copies run two tiles ahead; the softmax, not the hand-over between roles, sets the pace.  The running
+// maximum is only raised when a tile exceeds it by more than 2^8, so the correction of O (a round trip
+// through registers) is rare.  Formulas as in tensorline/paged_attn.py:46-57: scores, max, sum and the
+// accumulator in float, P in bfloat16 for P V.  Every mbarrier wait is bounded; on a time-out the block
+// records a code in `status` and leaves.
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -28,16 +32,16 @@ namespace {
 constexpr int D = HEAD_DIM;
 constexpr int BM = 128;                 // query rows per block = MMA M = tensor-memory lanes
 constexpr int BN = 64;                  // keys per tile
-constexpr int THREADS = 160;            // warps 0..3: loads, softmax, epilogue (one row each); warp 4: MMA issue
+constexpr int THREADS = 224;            // warps 0..3: softmax and epilogue (one row each); warp 4: MMA issue; warps 5, 6: copies of K, of V
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 constexpr long long WAIT_CYCLES = 4000000000LL;
 
 constexpr int Q_BYTES = BM * D * 2, K_BYTES = BN * D * 2, V_BYTES = BN * D * 2, P_BYTES = BM * BN * 2;
-constexpr int SMEM_TILES = Q_BYTES + K_BYTES + 2 * V_BYTES + P_BYTES;
-constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 64;
-constexpr uint32_t TMEM_COLS = (BN + D) <= 256 ? 256 : 512;
-constexpr uint32_t S_COL = 0, O_COL = BN;
+constexpr int SMEM_TILES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + 2 * P_BYTES;
+constexpr int SMEM_BYTES = SMEM_TILES + 1024 + 128;
+constexpr uint32_t TMEM_COLS = (2 * BN + D) <= 256 ? 256 : 512;
+constexpr uint32_t S_COL = 0, O_COL = 2 * BN;             // S[0], S[1], then O
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -147,16 +151,23 @@ struct TcAttnArgs {
     int* status;
 };
 
-// Keys [key0, key0 + BN) of one KV head into a swizzled [BN][D] tile; keys past last_key are zeros.
-__device__ __forceinline__ void load_kv(uint32_t dst, const bf16* pages, const int* tab, int page_size, size_t page_stride,
-                                        int key0, int last_key, int tid) {
+// Keys [key0, key0 + BN) of one KV head into a swizzled [BN][D] tile, by one warp; keys past
+// last_key are zeros.  The page size is a power of two between 2 and 64 (shift, mask).  The tile's
+// page numbers are read once (one per lane) and handed around with shuffles, so no copy waits on a
+// table read of its own.
+__device__ __forceinline__ void load_kv(uint32_t dst, const bf16* pages, const int* tab, int ps_shift, size_t page_stride,
+                                        int key0, int last_key, int lane) {
     constexpr int CH = D / 8;
-    for (int idx = tid; idx < BN * CH; idx += 128) {
+    const int ps_mask = (1 << ps_shift) - 1;
+    int my_page = 0;
+    if (lane < (BN >> ps_shift) && key0 + (lane << ps_shift) <= last_key) my_page = tab[(key0 >> ps_shift) + lane];
+#pragma unroll
+    for (int i = 0; i < BN * CH / 32; ++i) {
+        const int idx = lane + 32 * i;
         const int key = idx / CH, c = idx - key * CH;
-        const int j = key0 + key;
-        const bool valid = j <= last_key;
-        const bf16* src = pages;
-        if (valid) src = pages + (size_t)tab[j / page_size] * page_stride + (size_t)(j % page_size) * D + c * 8;
+        const int page = __shfl_sync(0xffffffffu, my_page, key >> ps_shift);
+        const bool valid = key0 + key <= last_key;
+        const bf16* src = pages + (size_t)page * page_stride + (size_t)((key & ps_mask) * D + c * 8);
         cp_async16(dst + swz(BN, key, c), src, valid);
     }
 }
@@ -164,13 +175,17 @@ __device__ __forceinline__ void load_kv(uint32_t dst, const bf16* pages, const i
 __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAttnArgs A) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const uint32_t sQ = smem_addr(base), sK = sQ + Q_BYTES, sV = sK + K_BYTES, sP = sV + 2 * V_BYTES;
-    uint64_t* bar_s = reinterpret_cast<uint64_t*>(base + SMEM_TILES);      // an MMA batch finished (commit)
-    uint64_t* bar_p = bar_s + 1;                                           // 128 rows handed P / the next K, V over
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_p + 1);
+    const uint32_t sQ = smem_addr(base), sK = sQ + Q_BYTES, sV = sK + 2 * K_BYTES, sP = sV + 2 * V_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + SMEM_TILES);
+    uint64_t* bar_s = bars;         // [2] S(i) is complete (commit)
+    uint64_t* bar_o = bars + 2;     // [2] O += P(i) V(i) is complete (commit): P and V of that slot are free
+    uint64_t* bar_p = bars + 4;     // [2] the 128 rows have written P(i)
+    uint64_t* bar_k = bars + 6;     // [2] K(i) is in shared memory
+    uint64_t* bar_v = bars + 8;     // [2] V(i) is in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kh = blockIdx.y, g = A.nq / A.nkv;
 
     int tile = gridDim.x - 1 - blockIdx.x, b = 0;          // longest tiles (late rows of a request) first
@@ -189,8 +204,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN, n_kt = kt_hi - kt_lo + 1;
 
     if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_p, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_s + i, 1); mbar_init(bar_o + i, 1); mbar_init(bar_p + i, 128);
+            mbar_init(bar_k + i, 32); mbar_init(bar_v + i, 32);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -202,27 +219,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    const size_t page_stride = (size_t)A.nkv * A.page_size * D;
-    const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
-    const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
 
     if (warp < 4) {
-        // ------------------------------------------------------------ loads, softmax, epilogue: thread = row
-        constexpr int CH = D / 8;
-        for (int idx = tid; idx < BM * CH; idx += 128) {    // Q tile: row = (token, head of the group)
-            const int r = idx / CH, c = idx - r * CH;
-            const int R = row0 + r;
-            const bool valid = R < rows_total;
-            const bf16* src = A.q;
-            if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
-            cp_async16(sQ + swz(BM, r, c), src, valid);
-        }
-        load_kv(sK, kbase, tab, A.page_size, page_stride, kt_lo * BN, pos_hi, tid);
-        load_kv(sV, vbase, tab, A.page_size, page_stride, kt_lo * BN, pos_hi, tid);
-        cp_async_wait_all();
-        fence_async_proxy();
-        mbar_arrive(bar_p);                                 // phase 0: Q, K(0), V(0) are in shared memory
-
+        // ------------------------------------------------------------ softmax and epilogue: thread = row
         const int R = row0 + tid;
         const int pos_r = R < rows_total ? sp + R / g : -1; // -1: no key is visible
         const int lo_r = A.window > 0 ? max(0, pos_r - A.window + 1) : 0;
@@ -231,24 +230,25 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         bool ok = true;
 
         for (int i = 0; i < n_kt && ok; ++i) {
-            const int kt = kt_lo + i;
-            ok = mbar_wait(bar_s, i & 1, abort_flag, A.status, 1);          // S(kt) ready; K, P and the other V buffer are free
+            const int sl = i & 1, kt = kt_lo + i;
+            ok = mbar_wait(bar_s + sl, (i >> 1) & 1, abort_flag, A.status, 1);          // S(i) is ready
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i + 1 < n_kt) {
-                load_kv(sK, kbase, tab, A.page_size, page_stride, (kt + 1) * BN, pos_hi, tid);
-                load_kv(sV + ((i + 1) & 1) * V_BYTES, vbase, tab, A.page_size, page_stride, (kt + 1) * BN, pos_hi, tid);
-            }
             float s[BN];
-            tmem_ld32(lane_addr + S_COL, reinterpret_cast<float(&)[32]>(s[0]));
-            tmem_ld32(lane_addr + S_COL + 32, reinterpret_cast<float(&)[32]>(s[32]));
+            tmem_ld32(lane_addr + S_COL + sl * BN, reinterpret_cast<float(&)[32]>(s[0]));
+            tmem_ld32(lane_addr + S_COL + sl * BN + 32, reinterpret_cast<float(&)[32]>(s[32]));
             const int key0 = kt * BN;
             float mx = -INFINITY;
+            if (key0 + BN - 1 <= pos_r && key0 >= lo_r) {   // every key of the tile is visible to this row
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                const int j = key0 + c;
-                if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
-                mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < BN; ++c) mx = fmaxf(mx, s[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int j = key0 + c;
+                    if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
+                    mx = fmaxf(mx, s[c]);
+                }
             }
             mx *= A.scale_log2;
             // Raise the reference maximum only when a tile exceeds it by more than the threshold.  The
@@ -258,6 +258,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             const float m_new = raise ? fmaxf(mx, m_ref) : m_ref;
             const bool fix_o = raise && i > 0 && m_ref != -INFINITY;        // O holds earlier tiles of this row
             if (__any_sync(0xffffffffu, fix_o)) {
+                // O must be at rest: P(i-1) V(i-1), the last product issued so far, has to be complete
+                ok = mbar_wait(bar_o + ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, A.status, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float alpha = fix_o ? fast_exp2(m_ref - m_new) : 1.0f;
                 l *= alpha;
 #pragma unroll 1
@@ -271,6 +275,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             }
             m_ref = m_new;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            if (i >= 2) {                                   // the P slot is free once P(i-2) V(i-2) is complete
+                ok = mbar_wait(bar_o + sl, ((i - 2) >> 1) & 1, abort_flag, A.status, 3);
+                if (!ok) break;
+            }
             // P = exp2(S * scale - m), rounded to bfloat16, into the swizzled A-operand tile (row = tid)
 #pragma unroll
             for (int j8 = 0; j8 < BN / 8; ++j8) {
@@ -280,17 +288,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                     p[e] = fast_exp2(fmaf(s[j8 * 8 + e], A.scale_log2, -m_use));
                     l += p[e];
                 }
-                const uint32_t dst = sP + swz(BM, tid, j8);
+                const uint32_t dst = sP + sl * P_BYTES + swz(BM, tid, j8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
                              "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
             }
-            cp_async_wait_all();                            // this thread's share of K(kt+1), V(kt+1) has landed
-            fence_async_proxy();                            // generic-proxy writes (P, cp.async) before the MMA reads
+            fence_async_proxy();                            // generic-proxy writes of P before the MMA reads them
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p + sl);
         }
-        // ------------------------------------------------------------ epilogue
-        if (ok && mbar_wait(bar_s, n_kt & 1, abort_flag, A.status, 2)) {   // the last P V has finished
+        // ------------------------------------------------------------ epilogue: the last P V has finished
+        if (ok && mbar_wait(bar_o + ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, abort_flag, A.status, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             bf16* dst = nullptr;
@@ -310,35 +317,79 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 }
             }
         }
-    } else if (tid == 128) {
-        // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-        constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-        bool ok = mbar_wait(bar_p, 0, abort_flag, A.status, 3);
-        for (int i = 0; i < n_kt && ok; ++i) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (i > 0) {                                    // O += P(i-1) V(i-1)
-                const uint32_t v_addr = sV + ((i - 1) & 1) * V_BYTES;
+    } else if (warp == 4) {
+        // ------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            auto issue_qk = [&](int j) {                    // S[j & 1] = Q K(j)^T
+                const uint32_t k_addr = sK + (j & 1) * K_BYTES;
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)
-                    umma(tmem + O_COL, desc_kmajor(sP + k * 32), desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o,
-                         (i > 1 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < D / 16; ++k)
+                    umma(tmem + S_COL + (j & 1) * BN, desc_kmajor(sQ + (k >> 2) * BM * 128 + (k & 3) * 32),
+                         desc_kmajor(k_addr + (k >> 2) * BN * 128 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+                umma_commit(bar_s + (j & 1));
+            };
+            bool ok = true;
+            for (int j = 0; j < 2 && j < n_kt && ok; ++j) {
+                ok = mbar_wait(bar_k + j, 0, abort_flag, A.status, 5);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_qk(j);
             }
+            for (int i = 0; i < n_kt && ok; ++i) {
+                const int sl = i & 1, ph = (i >> 1) & 1;
+                ok = mbar_wait(bar_p + sl, ph, abort_flag, A.status, 6) &&          // P(i) is written, S[sl] is free
+                     mbar_wait(bar_v + sl, ph, abort_flag, A.status, 7);            // V(i) is in shared memory
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_addr = sV + sl * V_BYTES, p_addr = sP + sl * P_BYTES;
 #pragma unroll
-            for (int k = 0; k < D / 16; ++k)                // S = Q K(i)^T
-                umma(tmem + S_COL, desc_kmajor(sQ + (k >> 2) * BM * 128 + (k & 3) * 32),
-                     desc_kmajor(sK + (k >> 2) * BN * 128 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
-            umma_commit(bar_s);
-            ok = mbar_wait(bar_p, (i + 1) & 1, abort_flag, A.status, 4);    // P(i) and the next K, V are ready
+                for (int k = 0; k < BN / 16; ++k)           // O += P(i) V(i)
+                    umma(tmem + O_COL, desc_kmajor(p_addr + k * 32), desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o,
+                         (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar_o + sl);
+                if (i + 2 < n_kt) {
+                    ok = mbar_wait(bar_k + sl, ((i + 2) >> 1) & 1, abort_flag, A.status, 8);   // K(i+2) is in
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_qk(i + 2);
+                }
+            }
         }
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t v_addr = sV + ((n_kt - 1) & 1) * V_BYTES;
-#pragma unroll
-            for (int k = 0; k < BN / 16; ++k)
-                umma(tmem + O_COL, desc_kmajor(sP + k * 32), desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o,
-                     (n_kt > 1 || k > 0) ? 1u : 0u);
-            umma_commit(bar_s);
+    } else {
+        // ------------------------------------------------------------ copies: warp 5 brings Q and K, warp 6 brings V,
+        // each up to two tiles ahead of the softmax
+        constexpr int CH = D / 8;
+        int ps_shift = 0;
+        while ((1 << ps_shift) < A.page_size) ++ps_shift;
+        const size_t page_stride = (size_t)A.nkv * A.page_size * D;
+        const bool is_k = warp == 5;
+        const bf16* pages = (is_k ? A.k_pages : A.v_pages) + (size_t)kh * A.page_size * D;
+        if (is_k) {
+            for (int idx = lane; idx < BM * CH; idx += 32) {    // Q tile: row = (token, head of the group)
+                const int r = idx / CH, c = idx - r * CH;
+                const int R = row0 + r;
+                const bool valid = R < rows_total;
+                const bf16* src = A.q;
+                if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
+                cp_async16(sQ + swz(BM, r, c), src, valid);
+            }
+        }
+        uint64_t* bar_free = is_k ? bar_s : bar_o;           // K slot: free once S(j-2) is complete; V slot: once P V(j-2) is
+        uint64_t* bar_full = is_k ? bar_k : bar_v;
+        const uint32_t tiles = is_k ? sK : sV;
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int sl = j & 1;
+            if (j >= 2) {
+                ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10);
+                if (!ok) break;
+            }
+            load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, (kt_lo + j) * BN, pos_hi, lane);
+            cp_async_wait_all();
+            fence_async_proxy();
+            mbar_arrive(bar_full + sl);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -365,7 +416,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
                                  const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
                                  float scale, int total_tiles, int* status, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
-    if (nq % nkv || page_size <= 0 || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
+    if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size < 2 || page_size > BN || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
     if (!g_attr_done) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;

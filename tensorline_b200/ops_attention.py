@@ -19,6 +19,7 @@ _libs: dict = {}
 
 NUM_SMS = 148
 KEY_TILE = 64
+TC_PREFILL = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: mma.sync attention only (A/B timing)
 
 
 def attn_lib(head_dim: int):
@@ -134,5 +135,9 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
     else:
-        prefill(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
-                ctx.h_q_start, nq, nkv, d, window, scale)
+        # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05; steps of mostly
+        # single tokens (a few decoded tokens beside a short portion) keep the 64-row mma.sync tiles.
+        rows = ctx.T * (nq // nkv)
+        fn = prefill_tc if (TC_PREFILL and d % 64 == 0 and d <= 256 and rows >= 96 * ctx.B) else prefill
+        fn(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
+           ctx.h_q_start, nq, nkv, d, window, scale)
