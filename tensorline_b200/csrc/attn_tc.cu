@@ -117,8 +117,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
                    "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]),
                    "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
                  : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
     const uint32_t* u = reinterpret_cast<const uint32_t*>(r);
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -237,20 +237,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             float s[BN];
             tmem_ld32(lane_addr + S_COL + sl * BN, reinterpret_cast<float(&)[32]>(s[0]));
             tmem_ld32(lane_addr + S_COL + sl * BN + 32, reinterpret_cast<float(&)[32]>(s[32]));
+            tmem_ld_wait();                                 // both halves in flight, one wait
             const int key0 = kt * BN;
-            float mx = -INFINITY;
-            if (key0 + BN - 1 <= pos_r && key0 >= lo_r) {   // every key of the tile is visible to this row
-#pragma unroll
-                for (int c = 0; c < BN; ++c) mx = fmaxf(mx, s[c]);
-            } else {
+            if (!(key0 + BN - 1 <= pos_r && key0 >= lo_r)) {   // not every key of the tile is visible to this row
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int j = key0 + c;
                     if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
-                    mx = fmaxf(mx, s[c]);
                 }
             }
-            mx *= A.scale_log2;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four short chains, not one long one
+#pragma unroll
+            for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * A.scale_log2;
             // Raise the reference maximum only when a tile exceeds it by more than the threshold.  The
             // tensor-memory loads and stores are warp-wide instructions, so the warp corrects O together
             // (factor 1 for rows that do not move) if any of its rows has to.
@@ -268,6 +267,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     float o[32];
                     tmem_ld32(lane_addr + O_COL + c0, o);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[c] *= alpha;
                     tmem_st32(lane_addr + O_COL + c0, o);
@@ -280,18 +280,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 if (!ok) break;
             }
             // P = exp2(S * scale - m), rounded to bfloat16, into the swizzled A-operand tile (row = tid)
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j8 = 0; j8 < BN / 8; ++j8) {
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     p[e] = fast_exp2(fmaf(s[j8 * 8 + e], A.scale_log2, -m_use));
-                    l += p[e];
+                    l4[e & 3] += p[e];
                 }
                 const uint32_t dst = sP + sl * P_BYTES + swz(BM, tid, j8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
                              "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             fence_async_proxy();                            // generic-proxy writes of P before the MMA reads them
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar_p + sl);
@@ -306,6 +308,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             for (int c0 = 0; c0 < D; c0 += 32) {
                 float o[32];
                 tmem_ld32(lane_addr + O_COL + c0, o);
+                tmem_ld_wait();
                 if (dst) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {

@@ -174,15 +174,25 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
     (14, 2, 64, 64, [15, 0], [17, 200], 100),
     (20, 1, 16, 2, [77], [1], None),
     (5, 5, 80, 32, [257], [1], 33),
+    (28, 4, 128, 16, [0, 130, 700], [300, 3, 1], None),
+    (6, 2, 192, 32, [63, 64], [70, 1], None),
+    (4, 4, 256, 64, [257, 0], [1, 150], 33),
+    (7, 7, 64, 2, [30], [150], 50),
 ]
 
 
 @pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
-@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16"])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16"])
 def test_paged_attention(case, kernel):
     """Decode and prefill attention over scattered pages against the plain formula."""
     from tensorline_b200 import ops, ops_attention
     nq, nkv, d, ps, ctx_lens, step_lens, window = case
+    if kernel == "tcgen05_bf16" and (d % 64 or ps < 2):
+        with pytest.raises(ops.KernelError):
+            ops_attention.attn_tc_lib(d) if d % 64 else ops_attention.prefill_tc(
+                torch.zeros(1, nq * d, dtype=torch.bfloat16, device="cuda"), nq * d, None, None, None,
+                torch.zeros(1, 1, dtype=torch.int32, device="cuda"), ps, None, None, None, [0, 1], nq, nkv, d, None, 1.0)
+        return
     adt = torch.float32 if kernel == "exact_f32" else torch.bfloat16
     B = len(ctx_lens)
     max_pages, num_pages = 128, 300
@@ -215,7 +225,15 @@ def test_paged_attention(case, kernel):
     table = table_tensor(rows, max_pages, num_pages)
     kd, vd = kps.cuda(), vps.cuda()
     scale = d ** -0.5
-    if kernel != "mma_bf16":
+    if kernel == "tcgen05_bf16":
+        q_start = [0]
+        for n in step_lens:
+            q_start.append(q_start[-1] + n)
+        ops_attention.prefill_tc(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
+                                 q_start, nq, nkv, d, window, scale)
+        from tensorline_b200 import ops_gemm
+        ops_gemm.check_status()
+    elif kernel != "mma_bf16":
         ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale)
     else:
         q_start = [0]
