@@ -31,7 +31,10 @@ namespace {
 
 constexpr int D = HEAD_DIM;
 constexpr int BM = 128;                 // query rows per block = MMA M = tensor-memory lanes
-constexpr int BN = 64;                  // keys per tile
+#ifndef TL_TC_KEYS
+#define TL_TC_KEYS 64
+#endif
+constexpr int BN = TL_TC_KEYS;          // keys per tile (128 was measured slower than 64)
 constexpr int THREADS = 224;            // warps 0..3: softmax and epilogue (one row each); warp 4: MMA issue; warps 5, 6: copies of K, of V
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;
@@ -59,10 +62,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// `backoff`: the waiting warp sleeps between polls, so that its spinning does not take issue slots from
+// the softmax warp that shares its scheduler (used by the MMA and copy warps, whose hand-overs have slack).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          bool backoff = false) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
+        if (backoff) __nanosleep(40);
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CYCLES) {
@@ -152,7 +159,7 @@ struct TcAttnArgs {
 };
 
 // Keys [key0, key0 + BN) of one KV head into a swizzled [BN][D] tile, by one warp; keys past
-// last_key are zeros.  The page size is a power of two between 2 and 64 (shift, mask).  The tile's
+// last_key are zeros.  The page size is a power of two, at least BN / 32 (shift, mask).  The tile's
 // page numbers are read once (one per lane) and handed around with shuffles, so no copy waits on a
 // table read of its own.
 __device__ __forceinline__ void load_kv(uint32_t dst, const bf16* pages, const int* tab, int ps_shift, size_t page_stride,
@@ -235,9 +242,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float s[BN];
-            tmem_ld32(lane_addr + S_COL + sl * BN, reinterpret_cast<float(&)[32]>(s[0]));
-            tmem_ld32(lane_addr + S_COL + sl * BN + 32, reinterpret_cast<float(&)[32]>(s[32]));
-            tmem_ld_wait();                                 // both halves in flight, one wait
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32)
+                tmem_ld32(lane_addr + S_COL + sl * BN + c0, reinterpret_cast<float(&)[32]>(s[c0]));
+            tmem_ld_wait();                                 // all parts in flight, one wait
             const int key0 = kt * BN;
             if (!(key0 + BN - 1 <= pos_r && key0 >= lo_r)) {   // not every key of the tile is visible to this row
 #pragma unroll
@@ -335,25 +343,26 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             };
             bool ok = true;
             for (int j = 0; j < 2 && j < n_kt && ok; ++j) {
-                ok = mbar_wait(bar_k + j, 0, abort_flag, A.status, 5);
+                ok = mbar_wait(bar_k + j, 0, abort_flag, A.status, 5, true);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 issue_qk(j);
             }
             for (int i = 0; i < n_kt && ok; ++i) {
                 const int sl = i & 1, ph = (i >> 1) & 1;
-                ok = mbar_wait(bar_p + sl, ph, abort_flag, A.status, 6) &&          // P(i) is written, S[sl] is free
-                     mbar_wait(bar_v + sl, ph, abort_flag, A.status, 7);            // V(i) is in shared memory
+                ok = mbar_wait(bar_p + sl, ph, abort_flag, A.status, 6, true) &&          // P(i) is written, S[sl] is free
+                     mbar_wait(bar_v + sl, ph, abort_flag, A.status, 7, true);            // V(i) is in shared memory
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = sV + sl * V_BYTES, p_addr = sP + sl * P_BYTES;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)           // O += P(i) V(i)
-                    umma(tmem + O_COL, desc_kmajor(p_addr + k * 32), desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o,
+                    umma(tmem + O_COL, desc_kmajor(p_addr + (k >> 2) * BM * 128 + (k & 3) * 32),
+                         desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o,
                          (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar_o + sl);
                 if (i + 2 < n_kt) {
-                    ok = mbar_wait(bar_k + sl, ((i + 2) >> 1) & 1, abort_flag, A.status, 8);   // K(i+2) is in
+                    ok = mbar_wait(bar_k + sl, ((i + 2) >> 1) & 1, abort_flag, A.status, 8, true);   // K(i+2) is in
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_qk(i + 2);
@@ -386,7 +395,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         for (int j = 0; j < n_kt && ok; ++j) {
             const int sl = j & 1;
             if (j >= 2) {
-                ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10);
+                ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
                 if (!ok) break;
             }
             load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, (kt_lo + j) * BN, pos_hi, lane);
@@ -419,7 +428,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
                                  const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
                                  float scale, int total_tiles, int* status, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
-    if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size < 2 || page_size > BN || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
+    if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size * 32 < BN || page_size > 64 || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
     if (!g_attr_done) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;

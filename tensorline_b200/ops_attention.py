@@ -65,12 +65,18 @@ def attn_tc_lib(head_dim: int):
     return lib
 
 
+def tc_min_page(head_dim: int) -> int:
+    """One warp hands the page numbers of a 64-key tile around by shuffle: at most 32 pages per tile."""
+    return 2
+
+
 def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
                nq, nkv, d, window, scale) -> None:
     """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory."""
     from .ops_gemm import status_word
-    if page_size < 2 or page_size > KEY_TILE or page_size & (page_size - 1):
-        raise KernelError(f"page size {page_size}: the tcgen05 attention kernel takes powers of two from 2 to {KEY_TILE}")
+    if page_size < tc_min_page(d) or page_size > KEY_TILE or page_size & (page_size - 1):
+        raise KernelError(f"page size {page_size}: the tcgen05 attention kernel for head size {d} takes powers of two "
+                          f"from {tc_min_page(d)} to {KEY_TILE}")
     g = nq // nkv
     B = len(h_q_start) - 1
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // TC_QUERY_TILE) for i in range(B))
@@ -140,6 +146,6 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05; steps of mostly
         # single tokens (a few decoded tokens beside a short portion) keep the 64-row mma.sync tiles.
         rows = ctx.T * (nq // nkv)
-        fn = prefill_tc if (TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= 2 and rows >= 96 * ctx.B) else prefill
+        fn = prefill_tc if (TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rows >= 96 * ctx.B) else prefill
         fn(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
            ctx.h_q_start, nq, nkv, d, window, scale)
