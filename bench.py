@@ -201,14 +201,17 @@ def e2e_decode(eng, batch, ctx0, steps, warmup, vocab):
         eng.step()
     for _ in range(warmup):
         eng.step()
+    eng.flush()                                                     # nothing in flight when the clock starts
     torch.cuda.synchronize()
     replays0 = eng.runner.graph_replays
+    before = sum(r.num_generated for r in reqs)
     t0 = time.perf_counter()
-    produced = 0
     for _ in range(steps):
-        produced += len(eng.step())
+        eng.step()                                                  # with overlap on, launches step t+1, then reads step t
+    eng.flush()                                                     # the last step's tokens are on the host
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    produced = sum(r.num_generated for r in reqs) - before
     assert produced == batch * steps and eng.runner.graph_replays - replays0 == steps
     nb = eng.runner._bucket(batch)
     h2d = (7 * nb + 1) * 4                                          # the step's packed inputs

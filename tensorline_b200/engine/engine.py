@@ -98,6 +98,11 @@ class Engine:
         eos = self.model.spec.eos_token_id
         self.default_stops = {eos} if eos is not None else set()     # tensorline/engine.py:76-77
         self._known_to_runner: set = set()
+        # Overlap (tensorline/batch_engine.py:478-533): in steady greedy decoding the next step is launched
+        # from the tokens still on the device before the previous step's tokens are read back.
+        self.overlap = bool(o.overlap and o.cuda_graphs)
+        self._inflight = None                            # (requests, DecodeHandle) of the step not yet read back
+        self.overlapped_steps = 0
 
     # ------------------------------------------------------------------ requests
     def _encode(self, prompt):
@@ -117,7 +122,7 @@ class Engine:
         return req
 
     def abort(self, req: Request) -> None:
-        self.scheduler.abort(req)
+        self.scheduler.abort(req)       # a step in flight for it finishes on the device; its token is dropped
         self._sync_runner()
 
     def _sync_runner(self) -> None:
@@ -126,12 +131,61 @@ class Engine:
             self.runner.end_request(rid)
             self._known_to_runner.discard(rid)
 
+    # ------------------------------------------------------------------ overlap
+    def _launch(self, reqs, prev=None):
+        """Start a decode step for `reqs` without waiting for its tokens."""
+        entries = [StepEntry(r.rid, [r.tokens[-1] if prev is None else 0], [0]) for r in reqs]
+        handle = self.runner.launch_decode(entries, None if prev is None else prev[1])
+        self.scheduler.computed([(r, 1) for r in reqs])
+        return reqs, handle
+
+    def _resolve(self, inflight) -> list:
+        """Read a launched step's tokens back and accept them; a request that finished one step
+        earlier has produced one token too many, which is dropped (tensorline/batch_engine.py:500-508)."""
+        reqs, handle = inflight
+        toks = self.runner.read_tokens(handle)
+        now = time.perf_counter()
+        out = []
+        for req, tok in zip(reqs, toks):
+            if not req.done and self.scheduler.accept(req, tok, now):
+                out.append((req, tok))
+        self._sync_runner()
+        return out
+
+    def _can_continue(self) -> bool:
+        """Whether the step after the one in flight can be launched before that one is read back
+        (tensorline/batch_engine.py:510-521): same requests, all greedy, nobody near a limit, a page
+        for one more token each."""
+        reqs = self._inflight[0]
+        sch = self.scheduler
+        if sch.waiting or len(sch.running) != len(reqs) or any(a is not b for a, b in zip(sch.running, reqs)):
+            return False
+        for r in reqs:      # the pending token is appended when the step is read back; leave room for one more
+            if (r.done or r.params.temperature > 0 or r.num_generated + 2 > r.params.max_tokens
+                    or len(r.tokens) + 2 > sch.max_model_len):
+                return False
+        return all(self.cache.grow(r.rid, r.num_computed, r.num_computed + 1) for r in reqs)
+
+    def flush(self) -> list:
+        """Read back the step in flight, if any."""
+        if self._inflight is None:
+            return []
+        prev, self._inflight = self._inflight, None
+        return self._resolve(prev)
+
     # ------------------------------------------------------------------ one iteration
     def step(self) -> list:
-        """Schedule, run one batch, sample, finish.  Returns [(request, token)] for the tokens
-        produced in this step."""
+        """Schedule, run one batch, sample, finish.  Returns [(request, token)] for the tokens that
+        became known in this call (with overlap on, a decode step's tokens arrive one call later)."""
         sch = self.scheduler
         try:
+            if self._inflight is not None:
+                if self._can_continue():
+                    prev = self._inflight
+                    self._inflight = self._launch(prev[0], prev)
+                    self.overlapped_steps += 1
+                    return self._resolve(prev)
+                return self.flush()
             plan = sch.schedule()
             self._sync_runner()
             if not plan:
@@ -144,6 +198,9 @@ class Engine:
                 end = req.num_computed + n
                 want = [n - 1] if end == len(req.tokens) else []      # tensorline/batch_engine.py:376
                 entries.append(StepEntry(req.rid, req.tokens[req.num_computed:end], want))
+            if (self.overlap and all(r.params.temperature <= 0 for r, _ in plan) and self.runner.can_replay(entries)):
+                self._inflight = self._launch([r for r, _ in plan])      # its tokens are read at the next call
+                return []
             sampled = [req for (req, n), e in zip(plan, entries) if e.want]
             rows = [(r.params, r.seed, r.num_generated) for r in sampled]
             tokens = self.runner.step_and_sample(entries, self.sampler, rows)
@@ -156,6 +213,7 @@ class Engine:
             self._sync_runner()
             return out
         except Exception as e:                                       # tensorline/batch_engine.py:568-576
+            self._inflight = None
             sch.fail_all(e)
             self._sync_runner()
             raise
@@ -195,4 +253,5 @@ class Engine:
         return {"steps": s.steps, "preemptions": s.preemptions, "max_running_seen": s.max_running_seen,
                 "prompt_tokens_total": s.prompt_tokens_total, "prefix_hit_tokens": s.prefix_hit_tokens,
                 "requests_finished": dict(s.finished), "free_pages": self.cache.num_free_pages(),
-                "num_pages": self.cache.num_pages, "graph_replays": getattr(self.runner, "graph_replays", 0)}
+                "num_pages": self.cache.num_pages, "graph_replays": getattr(self.runner, "graph_replays", 0),
+                "overlapped_steps": self.overlapped_steps}

@@ -107,6 +107,8 @@ class ModelRunner:
         self._graphs: dict = {}
         self._graph_pool = None
         self._graphable = all(isinstance(c, KVCacheView) for c in self.caches.values())
+        self._token_hosts = [torch.zeros(cache.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._flip = 0
 
     def _wait_for_table_copy(self) -> None:
         if self._table_event is not None:
@@ -284,8 +286,31 @@ class ModelRunner:
         self._graphs[nb] = g
         return g
 
+    # ------------------------------------------------------------------ decode without waiting for the tokens
+    def can_replay(self, entries) -> bool:
+        return self._can_replay(list(entries))
+
     @torch.inference_mode()
-    def _run_graph(self, entries):
+    def launch_decode(self, entries, ids_from=None):
+        """Replay the decode graph for `entries` and start copying its greedy tokens to the host without
+        waiting (tensorline/batch_engine.py:478-498).  `ids_from`: the handle of the previous launch of
+        the same requests in the same order; its tokens, still on the device, are this step's input ids."""
+        entries = list(entries)
+        n = len(entries)
+        g = self._run_graph(entries, None if ids_from is None else ids_from.graph.tokens[:n])
+        self._flip ^= 1
+        host = self._token_hosts[self._flip][:n]
+        host.copy_(g.tokens[:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return DecodeHandle(g, n, host, ev)
+
+    def read_tokens(self, handle) -> list:
+        handle.event.synchronize()
+        return handle.host.tolist()
+
+    @torch.inference_mode()
+    def _run_graph(self, entries, dev_ids=None):
         n = len(entries)
         nb = self._bucket(n)
         g = self._graphs.get(nb) or self._capture(nb)
@@ -312,6 +337,8 @@ class ModelRunner:
         g.buf.copy_(g.hosts[turn], non_blocking=True)
         g.events[turn] = torch.cuda.Event()
         g.events[turn].record()
+        if dev_ids is not None:                              # the previous step's tokens, never seen by the host
+            g.buf[:n].copy_(dev_ids)
         self._sync_tables()
         g.graph.replay()
         ops.count_launches(g.launches)
@@ -319,6 +346,15 @@ class ModelRunner:
         for e in entries:
             self.positions[e.rid] += 1
         return g
+
+
+@dataclass
+class DecodeHandle:
+    """A decode step in flight: its graph, batch size, the pinned copy of its tokens and the event after it."""
+    graph: object
+    n: int
+    host: torch.Tensor
+    event: object
 
 
 @dataclass

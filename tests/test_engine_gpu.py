@@ -149,3 +149,28 @@ def test_seeded_sampling_does_not_depend_on_batching_or_preemption(tmp_path):
     assert len({tuple(t) for t in alone}) == 3 and all(len(t) == 12 for t in alone)
     greedy = engine(folder, num_blocks=40, **opts).generate([prompts[0]], params(12))[0].token_ids
     assert greedy != alone[0]
+
+
+def test_overlapped_decoding_equals_synchronous(tiny_a):
+    """tzar-beep/Tensorline's tests/test_cuda_graphs.py:62-101: launching step t+1 before reading step t
+    changes no token, finish reason or count, with stop tokens, limits and staggered arrivals."""
+    from tensorline_b200 import SamplingParams
+    folder, prompts, want = tiny_a
+    stop = {want[3][5]}
+    sp = [params(8), SamplingParams(max_tokens=3, ignore_eos=True), params(8), SamplingParams(max_tokens=8, stop_token_ids=stop)]
+    results = {}
+    for overlap in (False, True):
+        eng = engine(folder, overlap=overlap)
+        reqs = [eng.add_request(prompts[0], sp[0]), eng.add_request(prompts[1], sp[1])]
+        for _ in range(4):                               # the other two arrive while these decode
+            eng.step()
+        reqs += [eng.add_request(prompts[2], sp[2]), eng.add_request(prompts[3], sp[3])]
+        while any(not r.done for r in reqs):
+            eng.step()
+        results[overlap] = [(r.output_tokens, r.stats.finish_reason, r.stats.completion_tokens) for r in reqs]
+        st = eng.stats()
+        assert st["free_pages"] == st["num_pages"]
+        assert (st["overlapped_steps"] > 0) == overlap
+    assert results[True] == results[False]
+    assert results[True][0][0] == want[0] and results[True][1][0] == want[1][:3]
+    assert results[True][3][1] == "stop" and results[True][3][0] == want[3][:want[3].index(want[3][5])]
