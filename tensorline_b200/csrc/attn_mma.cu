@@ -18,6 +18,7 @@
 // shared-memory tiles that cp.async fills; rows of a tile are padded by 16 bytes, which keeps
 // ldmatrix free of bank conflicts for every head size.
 #include "common.cuh"
+#include <cuda.h>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -467,6 +468,200 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     }
 }
 
+#if HEAD_DIM % 64 == 0
+// ------------------------------------------------------------------------------------ decode, TMA variant
+// The same split-KV decode attention with K and V brought in by TMA: a page's part for one KV head is a
+// contiguous [page, d] slab of the cache, so one thread issues a few tensor copies per 64-key stage
+// (128-byte swizzle, no per-thread address arithmetic) and the 128 threads only wait on the stage's
+// mbarrier.  Taken for head sizes that are multiples of 64 and pages of at least 8 tokens (a page's box
+// then starts on a 1024-byte boundary of the swizzle pattern); everything after the loads is the code
+// of the kernel above, reading the swizzled tile instead of the padded one.
+constexpr int TMA_TILE_BYTES = BN * D * 2;                       // K or V of one stage
+constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
+constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
+constexpr int TMA_TAB_OFFSET = TMA_BAR_OFFSET + 64;
+constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM) ? 1 : 0;
+static_assert(TMA_MERGE_OK == 1, "the stage buffers must hold the merge area");
+constexpr long long TMA_WAIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ const bf16* swz_ptr(const unsigned char* tile, int key, int c) {
+    return reinterpret_cast<const bf16*>(tile + (c >> 3) * (BN * 128) + key * 128 + (((c & 7) ^ (key & 7)) << 4));
+}
+__device__ __forceinline__ bool mbar_try_wait_tma(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after about two seconds, records the fact and lets the block leave.
+__device__ __forceinline__ bool mbar_wait_tma(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait_tma(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_tma(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > TMA_WAIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, 20);
+            return false;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const AttnArgs A, int* status) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    bf16* sQ = reinterpret_cast<bf16*>(tiles + TMA_Q_OFFSET);              // [16][DP], padded rows
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TMA_BAR_OFFSET);  // [DEC_STAGES]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + DEC_STAGES);
+    int* stab = reinterpret_cast<int*>(tiles + TMA_TAB_OFFSET);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = A.nq / A.nkv, m_tiles = (g + 15) / 16;
+    const int split = blockIdx.x / m_tiles, mt = blockIdx.x % m_tiles;
+    const int kh = blockIdx.y, b = blockIdx.z;
+    const int pos = A.start_pos[b], len = pos + 1;
+    const int lo = A.window > 0 ? max(0, len - A.window) : 0;
+    const int base = (lo / BN) * BN;
+    const int k_begin = base + split * A.chunk;
+    if (k_begin >= len) return;
+    const int k_end = min(len, k_begin + A.chunk);
+    const int n_stage = (k_end - k_begin + BN - 1) / BN;
+    const int* gtab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int qrow = A.q_start[b];
+    const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
+    const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
+    for (int i = tid; i < n_stage * ppt; i += 128) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
+    if (tid == 0) {
+        for (int s_ = 0; s_ < DEC_STAGES; ++s_)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + s_)), "r"(1));
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int hg = mt * 16 + r;
+        const bool valid = hg < g;
+        const bf16* src = A.q;
+        if (valid) src = A.q + (size_t)qrow * A.q_stride + (size_t)(kh * g + hg) * D + c * 8;
+        cp_async16(sQ + r * DP + c * 8, src, valid);
+    }
+    cp_async_commit();
+    __syncthreads();                                       // table copy and barriers are visible
+
+    auto issue_stage = [&](int st) {                       // one thread: the stage's pages, K and V, D/64 boxes each
+        const int buf = st % DEC_STAGES;
+        unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
+        unsigned char* vt = kt + TMA_TILE_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(full + buf)), "r"(2 * TMA_TILE_BYTES) : "memory");
+        for (int pg = 0; pg < ppt; ++pg) {
+            const int row = (stab[st * ppt + pg] * A.nkv + kh) * A.page_size;
+#pragma unroll
+            for (int db = 0; db < D / 64; ++db) {
+                const uint32_t off = db * (BN * 128) + pg * A.page_size * 128;
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                             ::"r"(smem_u32(kt + off)), "l"(&map_k), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                             ::"r"(smem_u32(vt + off)), "l"(&map_v), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
+            }
+        }
+    };
+    if (tid == 0)
+        for (int st = 0; st < DEC_STAGES - 1 && st < n_stage; ++st) issue_stage(st);
+    cp_async_wait<0>();
+    __syncthreads();                                       // the queries are in
+    uint32_t qf[KBLK][4];
+#pragma unroll
+    for (int kb = 0; kb < KBLK; ++kb)
+        ldsm_x4(qf[kb], sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + kb * 16 + (lane >> 4) * 8);
+    const int pos_r[2] = {k_end - 1, k_end - 1};
+    const int lo_r[2] = {max(lo, k_begin), max(lo, k_begin)};
+    float o[D / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int st = 0; st < n_stage; ++st) {
+        __syncthreads();                                   // every warp is done with stage st-1: its buffer is free
+        if (tid == 0 && st + DEC_STAGES - 1 < n_stage) issue_stage(st + DEC_STAGES - 1);
+        const int buf = st % DEC_STAGES;
+        if (!mbar_wait_tma(full + buf, (st / DEC_STAGES) & 1, abort_flag, status)) break;
+        const int key0 = k_begin + st * BN + warp * 16;    // this warp's 16 keys of the stage
+        if (key0 >= k_end) continue;
+        const unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
+        const unsigned char* vt = kt + TMA_TILE_BYTES;
+        float s[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+#pragma unroll
+        for (int kb = 0; kb < KBLK; ++kb) {                // S = Q K^T on this warp's 16 keys
+            uint32_t bfr[4];
+            ldsm_x4(bfr, swz_ptr(kt, warp * 16 + (lane & 7) + (lane >> 4) * 8, kb * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s[0], qf[kb], bfr[0], bfr[1]);
+            mma_bf16(s[1], qf[kb], bfr[2], bfr[3]);
+        }
+        if (key0 + 16 <= k_end && key0 >= lo) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        else                                  softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        uint32_t a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]); a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]); a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int nb = 0; nb < D / 8; nb += 2) {            // O += P V
+            uint32_t bfr[4];
+            ldsm_x4_trans(bfr, swz_ptr(vt, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nb + (lane >> 4)));
+            mma_bf16(o[nb], a, bfr[0], bfr[1]);
+            mma_bf16(o[nb + 1], a, bfr[2], bfr[3]);
+        }
+    }
+    __syncthreads();                                       // the stage buffers become the merge area
+    if (*abort_flag) return;
+
+    float* mO = reinterpret_cast<float*>(tiles);           // [4][16][D]
+    float* mML = mO + 4 * 16 * D;                          // [4][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float lr = l[r];
+        lr += __shfl_xor_sync(0xffffffffu, lr, 1);
+        lr += __shfl_xor_sync(0xffffffffu, lr, 2);
+        const int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) { mML[(warp * 16 + row) * 2] = m[r]; mML[(warp * 16 + row) * 2 + 1] = lr; }
+#pragma unroll
+        for (int nb = 0; nb < D / 8; ++nb) {
+            float* dst = mO + (warp * 16 + row) * D + nb * 8 + (lane & 3) * 2;
+            dst[0] = o[nb][2 * r]; dst[1] = o[nb][2 * r + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * D; idx += 128) {
+        const int row = idx / D, col = idx - row * D;
+        const int hg = mt * 16 + row;
+        if (hg >= g) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mML[(w * 16 + row) * 2]);
+        float acc = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mML[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            acc += f * mO[(w * 16 + row) * D + col];
+            lt += f * mML[(w * 16 + row) * 2 + 1];
+        }
+        const int head = kh * g + hg;
+        if (A.splits == 1) {
+            A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+        } else {
+            const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
+            A.part_o[pi * D + col] = acc;
+            if (col == 0) { A.part_ml[pi * 2] = mm; A.part_ml[pi * 2 + 1] = lt; }
+        }
+    }
+}
+#endif  // HEAD_DIM % 64 == 0
+
 // grid (nq, B): merges the partials of the non-empty splits of one (request, head).
 __global__ void attn_combine_kernel(const AttnArgs A) {
     const int head = blockIdx.x, b = blockIdx.y;
@@ -565,6 +760,84 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     dim3 cgrid(nq, B);
     attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
     return tl_launch_status();
+}
+
+#if HEAD_DIM % 64 == 0
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+bool g_tma_attr_done = false;
+
+// The cache tensor [pages, nkv, page, D] as rows of D elements; a box is one page of one KV head, 64 wide.
+int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 101;
+}
+}  // namespace
+#endif
+
+// tl_attn_decode with K and V loaded by TMA.  Needs a head size that is a multiple of 64, pages of 8 to 64
+// tokens, and `total_pages` (first dimension of the cache tensors).  `status`: device int for a wait that
+// ran out (may be null).  Returns 2 if this build or these sizes do not take the TMA path.
+TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                 long long total_pages, const int* table, int max_pages, int page_size,
+                                 const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                 int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
+                                 int* status, cudaStream_t stream) {
+#if HEAD_DIM % 64 == 0
+    if (B <= 0) return 0;
+    if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
+    if (nq % nkv || chunk % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return 1;
+    if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+            qres != cudaDriverEntryPointSuccess) return 100;
+        g_encode = (EncodeTiledFn)fn;
+    }
+    const int tab_entries = chunk / page_size;
+    if (tab_entries > DECODE_MAX_TAB) return 1;
+    const int smem = TMA_TAB_OFFSET + tab_entries * 4 + 1024;
+    if (!g_tma_attr_done) {
+        cudaError_t ce = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
+        if (ce != cudaSuccess) return (int)ce;
+        g_tma_attr_done = true;
+    }
+    int e = set_attrs();                                   // the combine kernel's library state
+    if (e) return e;
+    CUtensorMap mk, mv;
+    const long long rows = total_pages * nkv * page_size;
+    if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
+    if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
+    AttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
+    A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
+    const int g = nq / nkv, m_tiles = (g + 15) / 16;
+    dim3 grid(splits * m_tiles, nkv, B);
+    if (grid.z > 65535) return 1;
+    attn_decode_tma_kernel<<<grid, 128, smem, stream>>>(mk, mv, A, status);
+    e = tl_launch_status();
+    if (e || splits == 1) return e;
+    dim3 cgrid(nq, B);
+    attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
+    return tl_launch_status();
+#else
+    return 2;
+#endif
 }
 
 // ------------------------------------------------------------------------------------ no allocation

@@ -178,6 +178,9 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
     (6, 2, 192, 32, [63, 64], [70, 1], None),
     (4, 4, 256, 64, [257, 0], [1, 150], 33),
     (7, 7, 64, 2, [30], [150], 50),
+    (28, 4, 128, 16, [1, 1000, 700, 63], [1, 1, 1, 1], None),
+    (8, 2, 64, 8, [500, 129], [1, 1], 200),
+    (3, 1, 256, 32, [333], [1], None),
 ]
 
 
@@ -250,8 +253,10 @@ def test_paged_attention(case, kernel):
                 po = torch.full((B, nq, splits, d), float("nan"), device="cuda")
                 pml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")
                 out.zero_()
-                ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml)
-                assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits", **BF16)
+                for tma in (False, True):             # K, V by cp.async, or by TMA where the sizes allow it
+                    out.zero_()
+                    ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml, tma=tma)
+                    assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits, tma {tma}", **BF16)
             out.zero_()
         ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale)
     assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))

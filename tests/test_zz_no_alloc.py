@@ -60,7 +60,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         po = torch.empty(B, nq, splits, d, device="cuda")
         pml = torch.empty(B, nq, splits, 2, device="cuda")
         ops_attention.decode(q, nq * d, want, kp, vp, table, ps, i32(list(range(B + 1))), i32(ctx_lens),
-                             i32(list(range(B))), B, nq, nkv, d, None, d ** -0.5, chunk, splits, po, pml)
+                             i32(list(range(B))), B, nq, nkv, d, None, d ** -0.5, chunk, splits, po, pml, tma=False)
         got = torch.zeros_like(want)
         rc, msg = _static_call(lib, q, got, kp, vp, table, ps, B, ctx_lens, nq, nkv, d, chunk, splits)
         assert rc == 0, msg
@@ -70,7 +70,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
     q, kp, vp, table, _ = _setup(2, [100, 30], nq, nkv, d, ps, 3)
     want, got = (torch.zeros(2, nq * d, dtype=torch.bfloat16, device="cuda") for _ in range(2))
     ops_attention.decode(q, nq * d, want, kp, vp, table, ps, i32([0, 1, 2]), i32([100, 30]), i32([0, 1]), 2, nq, nkv, d,
-                         None, d ** -0.5, 128, 1)
+                         None, d ** -0.5, 128, 1, tma=False)
     rc, msg = _static_call(lib, q, got, kp, vp, table, ps, 2, [100, 30], nq, nkv, d, 128, 1)
     assert rc == 0, msg
     assert_close(got, want, "static scratch, one range", **BF16)
