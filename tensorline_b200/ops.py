@@ -23,7 +23,7 @@ _SIGNATURES = {
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
-    "tl_argmax": [_P, _I, _I, _I, _P, _P],
+    "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
 }
 
@@ -196,12 +196,19 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Te
                               out.stride(0), M, N, K, _stream()), "gemm_f32")
 
 
+ARGMAX_SLICES = 32
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the largest logit of row r, the lowest index on a tie."""
     R, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("argmax: logits must be float32 with unit inner stride")
     _ints(out, "out")
-    _check(core().tl_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+    wide = V >= 8192                                     # wide rows are cut into slices, merged by a second kernel
+    partial = torch.empty(R * 2 * ARGMAX_SLICES, dtype=torch.int32, device=logits.device) if wide else None
+    _check(core().tl_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(out), _ptr(partial), _stream()), "argmax",
+           launches=2 if wide else 1)
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,

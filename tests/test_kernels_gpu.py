@@ -115,28 +115,33 @@ def test_rope_and_kv_write(adt, rot, d):
     assert int((kp != 0).any(dim=-1).sum()) == T * nkv                       # nothing else was written
 
 
-def test_argmax_lowest_index_wins():
+@pytest.mark.parametrize("V", [5003, 40007])            # one block per row; slices merged by a second kernel
+def test_argmax_lowest_index_wins(V):
     from tensorline_b200 import ops
-    logits = rnd(6, 5003, seed=10)
+    logits = rnd(6, V, seed=10)
     logits[2, 4000] = logits[2, 17] = 50.0
-    logits[3, 5002] = 60.0
+    logits[3, V - 1] = 60.0
     logits[4, 0] = 60.0
+    logits[5, V // 2 + 3] = logits[5, V - 5] = 70.0
     out = torch.empty(6, dtype=torch.int32, device="cuda")
     ops.argmax(logits.cuda(), out)
     want = logits.argmax(-1).tolist()
-    want[2] = 17
+    want[2], want[5] = 17, V // 2 + 3
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("V,R", [(1237, 64), (5003, 9), (40007, 24)])       # clusters of 1, 2 and 8 blocks a row
 @pytest.mark.parametrize("top_p", [1.0, 0.7, 0.2])
-def test_sampling_matches_reference_distribution(top_p):
+def test_sampling_matches_reference_distribution(top_p, V, R):
     """The picked token is the one the plain inverse-CDF picks for the same uniform number; the kept
     set is the reference's nucleus."""
     from tensorline_b200 import ops
-    V, R = 1237, 64
     logits = rnd(R, V, seed=11, scale=2.5)
+    logits[0, V - 3] = 9.0                                                  # most of row 0's mass at the far end
+    logits[1] *= 0.01                                                       # nearly flat: a nucleus of thousands
     temps = torch.full((R,), 0.8)
     temps[5] = 0.0                                                          # a greedy row among sampled ones
+    logits[5, V - 2] = logits[5, 3] = 11.0                                  # whose maximum is tied across slices
     g = torch.Generator().manual_seed(12)
     u = torch.rand(R, generator=g)
     out = torch.empty(R, dtype=torch.int32, device="cuda")
@@ -144,7 +149,7 @@ def test_sampling_matches_reference_distribution(top_p):
     got = out.tolist()
     for r in range(R):
         if temps[r] <= 0:
-            assert got[r] == int(logits[r].argmax())
+            assert got[r] == 3
             continue
         probs = plain.sampling_distribution(logits[r], float(temps[r]), top_p)
         assert probs[got[r]] > 0, f"row {r}: token {got[r]} is outside the nucleus"
