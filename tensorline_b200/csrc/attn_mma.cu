@@ -371,6 +371,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
     const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
 
+    // Positions and block tables were written before the step's first kernel; the queries and the newest keys
+    // and values come from the kernel just before this one.
+    grid_dependency_wait();
+    grid_dependency_trigger();
     for (int idx = tid; idx < 16 * CH; idx += 128) {
         const int r = idx / CH, c = idx - r * CH;
         const int hg = mt * 16 + r;
@@ -541,6 +545,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    grid_dependency_wait();                                // queries and the newest keys and values: the kernel before
+    grid_dependency_trigger();
     for (int idx = tid; idx < 16 * CH; idx += 128) {
         const int r = idx / CH, c = idx - r * CH;
         const int hg = mt * 16 + r;
@@ -670,6 +676,8 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
     const int base = (lo / BN) * BN;
     const int ns = min(A.splits, (len - base + A.chunk - 1) / A.chunk);
     const size_t p0 = ((size_t)b * A.nq + head) * A.splits;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     float mm = -INFINITY;
     for (int s = 0; s < ns; ++s) mm = fmaxf(mm, A.part_ml[(p0 + s) * 2]);
     float lt = 0.f;
@@ -754,12 +762,10 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     if (grid.z > 65535) return 1;
     const int tab_entries = chunk / page_size;            // of the longest range a block can have
     if (tab_entries > DECODE_MAX_TAB) return 1;
-    attn_decode_kernel<<<grid, 128, DECODE_TAB_OFFSET + tab_entries * 4, stream>>>(A);
-    e = tl_launch_status();
+    e = launch_after_wait(attn_decode_kernel, grid, dim3(128), DECODE_TAB_OFFSET + tab_entries * 4, stream, A);
     if (e || splits == 1) return e;
     dim3 cgrid(nq, B);
-    attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
-    return tl_launch_status();
+    return launch_after_wait(attn_combine_kernel, cgrid, dim3(D < 128 ? ((D + 31) / 32) * 32 : 128), 0, stream, A);
 }
 
 #if HEAD_DIM % 64 == 0
@@ -829,12 +835,10 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
-    attn_decode_tma_kernel<<<grid, 128, smem, stream>>>(mk, mv, A, status);
-    e = tl_launch_status();
+    e = launch_after_wait(attn_decode_tma_kernel, grid, dim3(128), (size_t)smem, stream, mk, mv, A, status);
     if (e || splits == 1) return e;
     dim3 cgrid(nq, B);
-    attn_combine_kernel<<<cgrid, D < 128 ? ((D + 31) / 32) * 32 : 128, 0, stream>>>(A);
-    return tl_launch_status();
+    return launch_after_wait(attn_combine_kernel, cgrid, dim3(D < 128 ? ((D + 31) / 32) * 32 : 128), 0, stream, A);
 #else
     return 2;
 #endif

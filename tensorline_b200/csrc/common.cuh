@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 typedef __nv_bfloat16 bf16;
 
@@ -69,3 +70,39 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 static inline int tl_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
+// the kernel before it in the stream is still running; its blocks run their set-up and then stop in
+// grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched
+// this way calls grid_dependency_wait() before its first access to global memory that another kernel writes
+// or reads, and grid_dependency_trigger() right after, which lets the kernel after it be placed in turn (one
+// kernel ahead at most).  After a kernel that never triggers (a library's), the wait is an ordinary stream
+// dependency.  TENSORLINE_B200_PDL=0 launches everything the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool tl_dependent_launch_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("TENSORLINE_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_after_wait(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tl_dependent_launch_enabled() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

@@ -13,6 +13,8 @@ template <typename TW>
 __global__ void embed_kernel(float* __restrict__ x, const TW* __restrict__ table,
                              const int* __restrict__ ids, int H) {
     const int t = blockIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     const TW* row = table + (size_t)ids[t] * H;
     float* out = x + (size_t)t * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f<TW>(row[i]);
@@ -22,9 +24,9 @@ TL_EXPORT int tl_embed(void* x, const void* table, int table_dtype, const int* i
                        cudaStream_t stream) {
     if (T <= 0) return 0;
     if (table_dtype == TL_F32)
-        embed_kernel<float><<<T, 256, 0, stream>>>((float*)x, (const float*)table, ids, H);
+        launch_after_wait(embed_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)x, (const float*)table, ids, H);
     else
-        embed_kernel<bf16><<<T, 256, 0, stream>>>((float*)x, (const bf16*)table, ids, H);
+        launch_after_wait(embed_kernel<bf16>, dim3(T), dim3(256), 0, stream, (float*)x, (const bf16*)table, ids, H);
     return tl_launch_status();
 }
 
@@ -92,15 +94,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
                                        const int* __restrict__ rows, int H, float eps, int write_x) {
     __shared__ float red[33];
     const int i = blockIdx.x, nvec = H >> 2;
-    const size_t src = (size_t)(rows ? rows[i] : i) * H;
     float v[NV][4], wv[NV][4];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {                       // the weights are nobody's output: read them before the wait
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) Vec4<TW>::load(w + 4 * c, wv[k]);
+    }
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
-        if (c < nvec) {
-            Vec4<float>::load(x + src + 4 * c, v[k]);
-            Vec4<TW>::load(w + 4 * c, wv[k]);
-        }
+        if (c < nvec) Vec4<float>::load(x + src + 4 * c, v[k]);
     }
     if (r) {
 #pragma unroll
@@ -142,7 +148,7 @@ static void launch_add_rmsnorm(void* x, const void* r, const void* w, void* out,
     const bool vec = (H & 3) == 0 && nvec <= 8192 &&
                      ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out) & 15) == 0);
 #define VLAUNCH(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
-        add_rmsnorm_vec_kernel<TA, TW, NV><<<R, th, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x); }
+        launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x); }
     if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x);
     else if (nvec <= 1024) VLAUNCH(1)
     else if (nvec <= 2048) VLAUNCH(2)
@@ -181,6 +187,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
 // 8 values (16 bytes of bfloat16) per thread and iteration: requires I % 8 == 0.
 __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t total8) {
     const int i8 = I >> 3;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / i8;
@@ -208,9 +216,8 @@ TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I
     if (act_dtype == TL_BF16 && (I & 7) == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
         const size_t total8 = total / 8;
         const size_t want = (total8 + threads - 1) / threads;
-        silu_mul_vec8_kernel<<<(int)(want < 148 * 32 ? want : 148 * 32), threads, 0, stream>>>(
-            (const bf16*)gu, (bf16*)out, I, total8);
-        return tl_launch_status();
+        return launch_after_wait(silu_mul_vec8_kernel, dim3((unsigned)(want < 148 * 32 ? want : 148 * 32)), dim3(threads), 0, stream,
+                                 (const bf16*)gu, (bf16*)out, I, total8);
     }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (act_dtype == TL_F32)

@@ -145,9 +145,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
-        for (int i = 0; i < n_kt; ++i) {
+        // The weights are nobody's output: the first ring of weight tiles is requested before the wait for the
+        // kernel that writes the activations, so the stream from memory is already running when that kernel ends.
+        const int ahead = n_kt < STAGES ? n_kt : STAGES;
+        for (int i = 0; i < ahead; ++i) {
+            mbar_expect_tx(full_bar + i, STAGE_BYTES);
+            unsigned char* st = tiles + i * STAGE_BYTES;
+            if (G.swap) tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
+            else        tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
+        }
+        grid_dependency_wait();
+        grid_dependency_trigger();
+        for (int i = 0; i < ahead; ++i) {
+            unsigned char* st = tiles + i * STAGE_BYTES;
+            if (G.swap) tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
+            else        tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
+        }
+        for (int i = ahead; i < n_kt; ++i) {
             const int s = i % STAGES;
-            if (i >= STAGES && !mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1)) break;
+            if (!mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1)) break;
             mbar_expect_tx(full_bar + s, STAGE_BYTES);
             unsigned char* st = tiles + s * STAGE_BYTES;
             tma_load_2d(st, &map_a, full_bar + s, (kt_begin + i) * BK, a0);
@@ -157,6 +173,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------------------------------------------------------- MMA issuer
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         bool ok = true;
+        grid_dependency_wait();                          // the bounded waits below start counting once the copies can land
         for (int i = 0; i < n_kt && ok; ++i) {
             const int s = i % STAGES;
             ok = mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, G.status, 2);
@@ -172,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (ok) umma_commit(done_bar);                   // the accumulator is complete
     } else if (warp >= 2) {
         // ---------------------------------------------------------------- epilogue: 4 warps, 32 lanes of TMEM each
+        grid_dependency_wait();                          // the output may still be read by the kernel before
         if (mbar_wait(done_bar, 0, abort_flag, G.status, 3)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3;                // the TMEM lanes a warp may read: 32 * (warp % 4)
@@ -271,6 +289,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int out_f32,
                                      int S, int R, int C, int ldo) {
     const size_t total = (size_t)R * C;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < S; ++s) acc += partial[(size_t)s * total + idx];
@@ -316,8 +336,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, SMEM, stream>>>(ma, mb, G);
-    return tl_launch_status();
+    return launch_after_wait(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), SMEM, stream, ma, mb, G);
 }
 
 }  // namespace
@@ -362,6 +381,5 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     if (e || splits == 1 || G.counters != nullptr) return e;
     const size_t total = (size_t)T * N;
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(partial, y, out_f32, splits, T, N, ldo);
-    return tl_launch_status();
+    return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (void*)y, out_f32, splits, T, N, ldo);
 }

@@ -72,6 +72,8 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
         const int page = table[(size_t)req_slot[t] * max_pages + p / page_size];
         page_base = ((size_t)page * nkv * page_size + (p % page_size)) * d;
     }
+    grid_dependency_wait();                              // angles and the page are ready when the projection ends
+    grid_dependency_trigger();
     __syncthreads();
     bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
     for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
@@ -134,12 +136,10 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
         const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
         const size_t smem = (size_t)d * sizeof(float);
         if (bias_dtype == TL_F32)
-            rope_kv_vec_kernel<float><<<T, threads, smem, stream>>>((bf16*)qkv, (const float*)bias, pos, req_slot, table,
-                max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
-        else
-            rope_kv_vec_kernel<bf16><<<T, threads, smem, stream>>>((bf16*)qkv, (const bf16*)bias, pos, req_slot, table,
-                max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
-        return tl_launch_status();
+            return launch_after_wait(rope_kv_vec_kernel<float>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const float*)bias,
+                pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
+        return launch_after_wait(rope_kv_vec_kernel<bf16>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const bf16*)bias,
+            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
     }
     dim3 grid(T, heads);
     const int half = d / 2;

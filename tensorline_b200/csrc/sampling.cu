@@ -72,6 +72,8 @@ argmax_slice_kernel(const float* __restrict__ logits, int ld, int V, float* __re
     const float* row = logits + (size_t)r * ld;
     float best = -INFINITY;
     int idx = 0x7fffffff;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
         const float v = row[i];
         if (v > best || (v == best && i < idx)) { best = v; idx = i; }
@@ -100,6 +102,8 @@ argmax_slice_kernel(const float* __restrict__ logits, int ld, int V, float* __re
 
 __global__ void argmax_merge_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out) {
     const int r = blockIdx.x, lane = threadIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
     float best = pval[r * ARGMAX_SLICES + lane];
     int idx = pidx[r * ARGMAX_SLICES + lane];
 #pragma unroll
@@ -121,11 +125,9 @@ TL_EXPORT int tl_argmax(const float* logits, int ld, int R, int V, int* out, voi
     }
     float* pval = (float*)partial;
     int* pidx = (int*)partial + (size_t)R * ARGMAX_SLICES;
-    argmax_slice_kernel<<<dim3(ARGMAX_SLICES, R), 256, 0, stream>>>(logits, ld, V, pval, pidx);
-    int e = tl_launch_status();
+    const int e = launch_after_wait(argmax_slice_kernel, dim3(ARGMAX_SLICES, R), dim3(256), 0, stream, logits, ld, V, pval, pidx);
     if (e) return e;
-    argmax_merge_kernel<<<R, 32, 0, stream>>>(pval, pidx, out);
-    return tl_launch_status();
+    return launch_after_wait(argmax_merge_kernel, dim3(R), dim3(32), 0, stream, (const float*)pval, (const int*)pidx, out);
 }
 
 #define DRAW_THREADS 512
