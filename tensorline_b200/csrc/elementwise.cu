@@ -88,10 +88,14 @@ template <> struct Vec4<bf16> {
     }
 };
 
+// `partial` (instead of r): the addend is still in pieces, [splits][rows of x][H] float, as a split-K product
+// leaves them; they are summed in split order and rounded to the activation type first, which is what a
+// separate reduction pass would have handed over as r.
 template <typename TA, typename TW, int NV>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ r,
                                        const TW* __restrict__ w, TA* __restrict__ out,
-                                       const int* __restrict__ rows, int H, float eps, int write_x) {
+                                       const int* __restrict__ rows, int H, float eps, int write_x,
+                                       const float* __restrict__ partial, int splits, size_t plane) {
     __shared__ float red[33];
     const int i = blockIdx.x, nvec = H >> 2;
     float v[NV][4], wv[NV][4];
@@ -108,7 +112,24 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
         const int c = threadIdx.x + k * blockDim.x;
         if (c < nvec) Vec4<float>::load(x + src + 4 * c, v[k]);
     }
-    if (r) {
+    if (partial) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int sp = 0; sp < splits; ++sp) {
+                    float pv[4];
+                    Vec4<float>::load(partial + sp * plane + src + 4 * c, pv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[e] += pv[e];
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[k][e] = v[k][e] + to_f<TA>(from_f<TA>(acc[e]));
+                if (write_x) Vec4<float>::store(x + src + 4 * c, v[k]);
+            }
+        }
+    } else if (r) {
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int c = threadIdx.x + k * blockDim.x;
@@ -142,32 +163,36 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
 }
 
 template <typename TA, typename TW>
-static void launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, const int* rows, int R, int H,
-                               float eps, int write_x, cudaStream_t stream) {
+static int launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, const int* rows, int R, int H,
+                              float eps, int write_x, const float* partial, int splits, size_t plane, cudaStream_t stream) {
     const int nvec = H >> 2;
     const bool vec = (H & 3) == 0 && nvec <= 8192 &&
-                     ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out) & 15) == 0);
+                     ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out | (uintptr_t)partial) & 15) == 0);
+    if (partial && !vec) return 1;                       // pieces only on the vector path; the caller sums them first
 #define VLAUNCH(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
-        launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x); }
+        launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); }
     if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x);
     else if (nvec <= 1024) VLAUNCH(1)
     else if (nvec <= 2048) VLAUNCH(2)
     else if (nvec <= 4096) VLAUNCH(4)
     else VLAUNCH(8)
 #undef VLAUNCH
+    return 0;
 }
 
 TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype, void* out, int act_dtype,
-                             const int* rows, int R, int H, float eps, int write_x, cudaStream_t stream) {
+                             const int* rows, int R, int H, float eps, int write_x, const float* partial, int splits,
+                             long long plane, cudaStream_t stream) {
     if (R <= 0) return 0;
+    int e;
     if (act_dtype == TL_F32) {
-        if (w_dtype == TL_F32) launch_add_rmsnorm<float, float>(x, r, w, out, rows, R, H, eps, write_x, stream);
-        else launch_add_rmsnorm<float, bf16>(x, r, w, out, rows, R, H, eps, write_x, stream);
+        if (w_dtype == TL_F32) e = launch_add_rmsnorm<float, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
+        else e = launch_add_rmsnorm<float, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
     } else {
-        if (w_dtype == TL_F32) launch_add_rmsnorm<bf16, float>(x, r, w, out, rows, R, H, eps, write_x, stream);
-        else launch_add_rmsnorm<bf16, bf16>(x, r, w, out, rows, R, H, eps, write_x, stream);
+        if (w_dtype == TL_F32) e = launch_add_rmsnorm<bf16, float>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
+        else e = launch_add_rmsnorm<bf16, bf16>(x, r, w, out, rows, R, H, eps, write_x, partial, splits, (size_t)plane, stream);
     }
-    return tl_launch_status();
+    return e ? e : tl_launch_status();
 }
 
 // ------------------------------------------------------------------ SwiGLU activation

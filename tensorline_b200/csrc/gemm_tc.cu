@@ -364,6 +364,7 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     if (splits > k_tiles) splits = k_tiles;
     const int per = (k_tiles + splits - 1) / splits;
     splits = (k_tiles + per - 1) / per;                                                  // no empty split
+    if (y == nullptr && splits < 2) return 1;
     GemmArgs G{};
     G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
@@ -378,8 +379,17 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
         case 256: e = launch<256, 4>(ma, mb, G, grid, stream); break;
         default: return 1;
     }
-    if (e || splits == 1 || G.counters != nullptr) return e;
+    if (e || splits == 1 || G.counters != nullptr || y == nullptr) return e;      // y null: the caller sums the pieces
     const size_t total = (size_t)T * N;
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (void*)y, out_f32, splits, T, N, ldo);
+}
+
+// out[T, ldo] = the sum of the S pieces partial[S][T][N] in split order, converted.
+TL_EXPORT int tl_splitk_reduce(const float* partial, void* y, int out_f32, int splits, int T, int N, int ldo,
+                               cudaStream_t stream) {
+    const size_t total = (size_t)T * N;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partial, y, out_f32, splits, T, N, ldo);
 }

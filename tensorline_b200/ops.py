@@ -18,7 +18,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
-    "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
+    "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_silu_mul": [_P, _P, _I, _I, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
@@ -111,9 +111,11 @@ def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
 
 
 def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, eps: float,
-                rows: torch.Tensor | None = None, write_x: bool = True) -> None:
+                rows: torch.Tensor | None = None, write_x: bool = True, pieces: torch.Tensor | None = None) -> None:
     """x += r (if r), out = cast(x * rstd) * w.  x float32 [*, H]; r, out of the activation
-    type; `rows` picks the rows (x is then left alone)."""
+    type; `rows` picks the rows (x is then left alone).  `pieces` [S, rows of x, H] float32 instead
+    of r: the addend as a split-K product left it; summed in split order and rounded to the
+    activation type inside the kernel (needs H % 4 == 0 and H <= 32768)."""
     H = x.shape[-1]
     R = out.shape[0]
     if x.dtype != torch.float32 or out.shape[-1] != H or w.numel() != H:
@@ -123,6 +125,14 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
     _contig(x, "x"); _contig(out, "out"); _contig(w, "w")
     if r is not None:
         _contig(r, "r")
+    splits = plane = 0
+    if pieces is not None:
+        if r is not None or pieces.dtype != torch.float32 or pieces.dim() != 3 or pieces.shape[1:] != x.shape:
+            raise KernelError("add_rmsnorm: pieces must be float32 [S, rows of x, H] and stand instead of r")
+        if H % 4 or H > 32768:
+            raise KernelError("add_rmsnorm: pieces need a width that is a multiple of 4 and at most 32768")
+        _contig(pieces, "pieces")
+        splits, plane = pieces.shape[0], x.numel()
     if rows is not None:
         _ints(rows, "rows")
         if rows.numel() != R:
@@ -131,7 +141,8 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
     elif x.shape[0] != R:
         raise KernelError("add_rmsnorm: out must have x's rows")
     _check(core().tl_add_rmsnorm(_ptr(x), _ptr(r), _ptr(w), dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype),
-                                 _ptr(rows), R, H, float(eps), int(write_x), _stream()), "add_rmsnorm")
+                                 _ptr(rows), R, H, float(eps), int(write_x), _ptr(pieces), splits, plane, _stream()),
+           "add_rmsnorm")
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:

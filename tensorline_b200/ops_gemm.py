@@ -30,6 +30,8 @@ def lib():
         l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
         l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P]
         l.tl_gemm_tc.restype = ctypes.c_int
+        l.tl_splitk_reduce.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
+        l.tl_splitk_reduce.restype = ctypes.c_int
         _lib = l
     return _lib
 
@@ -70,7 +72,9 @@ def plan(T: int, N: int, K: int) -> tuple:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
-            splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False) -> torch.Tensor:
+            splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False, pieces: bool = False):
+    """x [T, K] times w [N, K]^T.  `pieces`: when the plan splits K, return the float32 pieces
+    [S, T, N] unsummed (for a consumer that adds them up itself) instead of the product."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: bfloat16 operands only")
     T, K = x.shape
@@ -85,13 +89,28 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     swap = p_swap if swap is None else int(swap)
     bn = p_bn if bn is None else bn
     splits = p_splits if splits is None else splits
-    if out is None:
+    k_tiles = -(-K // 64)
+    splits = -(-k_tiles // -(-k_tiles // min(splits, k_tiles)))          # as the kernel rounds it: no empty split
+    pieces = pieces and splits > 1 and not fused_reduce
+    if pieces:
+        out = None
+    elif out is None:
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     elif out.shape != (T, N) or out.dtype != out_dtype or out.stride(1) != 1:
         raise KernelError("gemm_tc: out must be [T, N] of the output type with unit inner stride")
     partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     st = status_word(x.device)
-    _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K, swap, bn,
-                            splits, _ptr(partial), _ptr(st), (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS,
-                            _stream()), "gemm_tc", launches=1 if (splits == 1 or fused_reduce) else 2)
+    _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), N if pieces else out.stride(0),
+                            T, N, K, swap, bn, splits, _ptr(partial), _ptr(st),
+                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, _stream()),
+           "gemm_tc", launches=1 if (splits == 1 or fused_reduce or pieces) else 2)
+    return partial if pieces else out
+
+
+def sum_pieces(pieces: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """[S, T, N] float32 pieces of a split-K product -> their sum in split order, [T, N]."""
+    S, T, N = pieces.shape
+    out = torch.empty((T, N), dtype=out_dtype, device=pieces.device)
+    _check(lib().tl_splitk_reduce(_ptr(pieces), _ptr(out), int(out_dtype == torch.float32), S, T, N, N, _stream()),
+           "splitk_reduce")
     return out

@@ -68,7 +68,7 @@ class PagedAttention(Part):
                           nq, nkv, d, cache.k, cache.v, write_kv=cache.owner)
         o = torch.empty((T, nq * d), dtype=h.dtype, device=h.device)
         self.attend(qkv, o, ctx, cache, table)
-        return matmul(o, self.w_o)
+        return matmul(o, self.w_o, may_defer=True)             # the block's next norm adds it up
 
     def attend(self, qkv, o, ctx, cache, table):
         from . import attention_kernels

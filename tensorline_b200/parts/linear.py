@@ -17,7 +17,7 @@ import torch
 from .. import ops
 
 TC_MAX_TOKENS = 16                 # the hand-written kernel wins up to this many tokens ...
-TC_MIN_WEIGHT_ELEMENTS = 48 << 20  # ... against matrices of at least this many elements
+TC_MIN_WEIGHT_ELEMENTS = int(os.environ.get("TENSORLINE_B200_TC_MIN_ELEMENTS", 8 << 20))   # ... against matrices of at least this many elements
 
 
 TC_ENABLED = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: library products only (for A/B timing)
@@ -27,8 +27,28 @@ def use_tc(tokens: int, n: int, k: int) -> bool:
     return TC_ENABLED and tokens <= TC_MAX_TOKENS and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0
 
 
-def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """x [T, K] (float32 or bfloat16) times w [N, K]^T -> [T, N]."""
+class SplitSum:
+    """A product whose split-K pieces [S, T, N] (float32) have not been added up yet.  A consumer that
+    reads its input once anyway (the residual add + norm) sums them on the way and saves the pass that
+    would; anyone else calls `resolve`."""
+
+    def __init__(self, pieces: torch.Tensor, dtype: torch.dtype):
+        self.pieces, self.dtype = pieces, dtype
+        self.shape = pieces.shape[1:]
+
+    def sum(self) -> torch.Tensor:
+        from .. import ops_gemm
+        return ops_gemm.sum_pieces(self.pieces, self.dtype)
+
+
+def resolve(t):
+    """A tensor from what a projection returned."""
+    return t.sum() if isinstance(t, SplitSum) else t
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, may_defer: bool = False):
+    """x [T, K] (float32 or bfloat16) times w [N, K]^T -> [T, N].  `may_defer`: the caller hands the
+    result to a consumer that takes a `SplitSum`."""
     if x.dtype == torch.float32:
         out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
         ops.gemm_f32(x, w, out)
@@ -37,7 +57,8 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         raise ops.KernelError("matmul called with a CPU tensor: this engine has no CPU path")
     if use_tc(x.shape[0], w.shape[0], w.shape[1]) and x.is_contiguous():
         from .. import ops_gemm
-        return ops_gemm.gemm_tc(x, w, out_dtype or x.dtype)
+        y = ops_gemm.gemm_tc(x, w, out_dtype or x.dtype, pieces=may_defer)
+        return SplitSum(y, out_dtype or x.dtype) if y.dim() == 3 else y
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.mm(x, w.t())

@@ -36,4 +36,4 @@ class GatedMLP(Part):
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], self.intermediate), dtype=h.dtype, device=h.device)
         ops.silu_mul(gu, m)
-        return matmul(m, self.w_down)
+        return matmul(m, self.w_down, may_defer=True)          # the next norm adds it up

@@ -5,6 +5,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_norm
+from .linear import SplitSum
 
 
 @register_norm("rms_norm")
@@ -23,5 +24,10 @@ class RMSNorm(Part):
     def add_norm(self, x, pending, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+        if isinstance(pending, SplitSum):                # a split-K product: its pieces are summed inside the kernel
+            if pending.dtype == h.dtype and self.dim % 4 == 0 and self.dim <= 32768:
+                ops.add_rmsnorm(x, None, self.weight, h, self.eps, rows=rows, pieces=pending.pieces)
+                return h
+            pending = pending.sum()
         ops.add_rmsnorm(x, pending, self.weight, h, self.eps, rows=rows)
         return h

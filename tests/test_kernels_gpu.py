@@ -300,6 +300,36 @@ def test_tcgen05_matrix_product(case, fused):
     assert int(ops_gemm.status_word(x.device)[1:].abs().sum()) == 0          # arrival counters are back at zero
 
 
+@pytest.mark.parametrize("rows", [None, [3, 0, 3]])
+def test_split_product_summed_inside_the_norm(rows):
+    """The pieces of a split-K product handed to the residual add + norm give bit for bit what the
+    separate summing pass followed by the norm gives; and the norm part takes a `SplitSum`."""
+    from tensorline_b200 import ops, ops_gemm
+    from tensorline_b200.parts.linear import SplitSum, resolve
+    T, N, K, eps = 5, 264, 2056, 1e-5
+    a = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    w = rnd(N, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()
+    pieces = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4, pieces=True)
+    assert pieces.shape == (4, T, N) and pieces.dtype == torch.float32
+    whole = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4)
+    assert torch.equal(resolve(SplitSum(pieces, torch.bfloat16)), whole)
+    assert_close(whole, a.double() @ w.double().T, "product", rtol=1e-2, atol=1e-2)
+    x = rnd(T, N, seed=3, scale=2.0).cuda()
+    nw = (1 + rnd(N, seed=4, scale=0.3)).to(torch.bfloat16).cuda()
+    R = T if rows is None else len(rows)
+    sel = None if rows is None else i32(rows)
+    x1, x2 = x.clone(), x.clone()
+    o1 = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+    o2 = torch.empty_like(o1)
+    ops.add_rmsnorm(x1, whole, nw, o1, eps, rows=sel)
+    ops.add_rmsnorm(x2, None, nw, o2, eps, rows=sel, pieces=pieces)
+    assert torch.equal(o1, o2) and torch.equal(x1, x2)
+    if rows is None:
+        assert not torch.equal(x1, x)                                          # the sum went into the residual stream
+    with pytest.raises(ops.KernelError, match="pieces"):
+        ops.add_rmsnorm(x2, whole, nw, o2, eps, rows=sel, pieces=pieces)
+
+
 def test_tcgen05_matrix_product_refuses_unaligned_k():
     from tensorline_b200 import ops, ops_gemm
     x = torch.zeros(4, 36, dtype=torch.bfloat16, device="cuda")
