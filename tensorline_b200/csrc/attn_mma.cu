@@ -676,23 +676,62 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
     const int base = (lo / BN) * BN;
     const int ns = min(A.splits, (len - base + A.chunk - 1) / A.chunk);
     const size_t p0 = ((size_t)b * A.nq + head) * A.splits;
+    __shared__ float wgt[128];                             // a split's weight exp2(m_s - m); at most 128 splits
+    __shared__ float inv_total;
     grid_dependency_wait();
     grid_dependency_trigger();
-    float mm = -INFINITY;
-    for (int s = 0; s < ns; ++s) mm = fmaxf(mm, A.part_ml[(p0 + s) * 2]);
-    float lt = 0.f;
-    for (int s = 0; s < ns; ++s) {
-        const float ms = A.part_ml[(p0 + s) * 2];
-        lt += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_ml[(p0 + s) * 2 + 1];
-    }
-    const float inv = lt > 0.f ? 1.0f / lt : 0.f;
     const int qrow = A.q_start[b];
+    if (ns > 128) {                                        // more splits than the weight table holds: one by one
+        float mm = -INFINITY;
+        for (int sp = 0; sp < ns; ++sp) mm = fmaxf(mm, A.part_ml[(p0 + sp) * 2]);
+        float lt = 0.f;
+        for (int sp = 0; sp < ns; ++sp) {
+            const float ms = A.part_ml[(p0 + sp) * 2];
+            lt += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_ml[(p0 + sp) * 2 + 1];
+        }
+        const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+        for (int col = threadIdx.x; col < D; col += blockDim.x) {
+            float acc = 0.f;
+            for (int sp = 0; sp < ns; ++sp) {
+                const float ms = A.part_ml[(p0 + sp) * 2];
+                acc += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_o[(p0 + sp) * D + col];
+            }
+            A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(acc * inv);
+        }
+        return;
+    }
+    if (threadIdx.x < 32) {                                // all (m, l) pairs are requested at once: up to four a lane
+        const int lane = threadIdx.x;
+        float ms[4], ls[4];
+        float mm = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int sp = lane + 32 * k;
+            ms[k] = -INFINITY; ls[k] = 0.f;
+            if (sp < ns) {
+                const float2 ml = *reinterpret_cast<const float2*>(A.part_ml + (p0 + sp) * 2);
+                ms[k] = ml.x; ls[k] = ml.y;
+            }
+            mm = fmaxf(mm, ms[k]);
+        }
+        mm = warp_max(mm);
+        float lt = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int sp = lane + 32 * k;
+            const float f = ms[k] == -INFINITY ? 0.f : exp2f(ms[k] - mm);
+            if (sp < ns) wgt[sp] = f;
+            lt += f * ls[k];
+        }
+        lt = warp_sum(lt);
+        if (lane == 0) inv_total = lt > 0.f ? 1.0f / lt : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_total;
     for (int col = threadIdx.x; col < D; col += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < ns; ++s) {
-            const float ms = A.part_ml[(p0 + s) * 2];
-            acc += (ms == -INFINITY ? 0.f : exp2f(ms - mm)) * A.part_o[(p0 + s) * D + col];
-        }
+#pragma unroll 8
+        for (int sp = 0; sp < ns; ++sp) acc += wgt[sp] * A.part_o[(p0 + sp) * D + col];
         A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(acc * inv);
     }
 }

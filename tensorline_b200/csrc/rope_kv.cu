@@ -57,7 +57,11 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
                                    const int* __restrict__ pos, const int* __restrict__ req_slot,
                                    const int* __restrict__ table, int max_pages, int page_size,
                                    const float* __restrict__ inv_freq, int nq, int nkv, int d,
-                                   bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int heads) {
+                                   bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int heads,
+                                   const float* __restrict__ pieces, int splits, size_t plane) {
+    // `pieces` [splits][T][(nq + 2 nkv) d] float: the projection as a split-K product left it.  The pieces are
+    // summed in split order and rounded to bfloat16 first, as the separate summing pass would have stored them
+    // in qkv; q still goes to qkv, which is then output only.
     extern __shared__ float cs[];                                // cos[half], sin[half]
     const int t = blockIdx.x;
     const int p = pos[t];
@@ -78,15 +82,32 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
     bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
     for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
         const int hh = item / per_head, i0 = (item - hh * per_head) * 8;
-        const uint4 av = *reinterpret_cast<const uint4*>(row + hh * d + i0);
-        const uint4 bv = *reinterpret_cast<const uint4*>(row + hh * d + half + i0);
-        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
         float a[8], b[8];
+        if (pieces) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            a[2 * k] = __low2float(a2[k]); a[2 * k + 1] = __high2float(a2[k]);
-            b[2 * k] = __low2float(b2[k]); b[2 * k + 1] = __high2float(b2[k]);
+            for (int k = 0; k < 8; ++k) { a[k] = 0.f; b[k] = 0.f; }
+            const float* src = pieces + (size_t)t * (nq + 2 * nkv) * d + hh * d + i0;
+            for (int sp = 0; sp < splits; ++sp, src += plane) {
+                const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
+                const float4 b0 = *reinterpret_cast<const float4*>(src + half), b1 = *reinterpret_cast<const float4*>(src + half + 4);
+                a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w; a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+                b[0] += b0.x; b[1] += b0.y; b[2] += b0.z; b[3] += b0.w; b[4] += b1.x; b[5] += b1.y; b[6] += b1.z; b[7] += b1.w;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                a[k] = __bfloat162float(__float2bfloat16_rn(a[k]));
+                b[k] = __bfloat162float(__float2bfloat16_rn(b[k]));
+            }
+        } else {
+            const uint4 av = *reinterpret_cast<const uint4*>(row + hh * d + i0);
+            const uint4 bv = *reinterpret_cast<const uint4*>(row + hh * d + half + i0);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a[2 * k] = __low2float(a2[k]); a[2 * k + 1] = __high2float(a2[k]);
+                b[2 * k] = __low2float(b2[k]); b[2 * k + 1] = __high2float(b2[k]);
+            }
         }
         if (bias) {
 #pragma unroll
@@ -125,21 +146,25 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
 TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int bias_dtype,
                                const int* pos, const int* req_slot, const int* table, int max_pages,
                                int page_size, const float* inv_freq, int rot, int nq, int nkv, int d,
-                               void* k_pages, void* v_pages, int write_kv, int T, cudaStream_t stream) {
+                               void* k_pages, void* v_pages, int write_kv, int T, const float* pieces, int splits,
+                               long long plane, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
     const int heads = write_kv ? nq + 2 * nkv : nq;
     if (heads > 65535) return 1;
-    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0);
+    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)pieces) & 15) == 0);
+    if (pieces && !(act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned)) return 1;   // pieces: the fast path only
     if (act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned) {
         const int items = heads * (d / 16);
         const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
         const size_t smem = (size_t)d * sizeof(float);
         if (bias_dtype == TL_F32)
             return launch_after_wait(rope_kv_vec_kernel<float>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const float*)bias,
-                pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
+                pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads,
+                pieces, splits, (size_t)plane);
         return launch_after_wait(rope_kv_vec_kernel<bf16>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const bf16*)bias,
-            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads);
+            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads,
+            pieces, splits, (size_t)plane);
     }
     dim3 grid(T, heads);
     const int half = d / 2;

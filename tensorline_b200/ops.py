@@ -20,7 +20,7 @@ _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_silu_mul": [_P, _P, _I, _I, _I, _P],
-    "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P],
+    "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -156,9 +156,19 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
 
 def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tensor, req_slot: torch.Tensor,
                   table: torch.Tensor, page_size: int, inv_freq: torch.Tensor, rot: int, nq: int, nkv: int,
-                  d: int, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True) -> None:
-    """Bias, rotary encoding of q and k in place, and the write of k, v into their pages."""
+                  d: int, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True,
+                  pieces: torch.Tensor | None = None) -> None:
+    """Bias, rotary encoding of q and k in place, and the write of k, v into their pages.
+    `pieces` [S, T, width] float32: the projection as a split-K product left it; the kernel sums them
+    (bfloat16, full rotary, d % 16 == 0 only) and qkv is output only (its q columns are written)."""
     T = qkv.shape[0]
+    splits = plane = 0
+    if pieces is not None:
+        if (pieces.dtype != torch.float32 or pieces.dim() != 3 or pieces.shape[1:] != qkv.shape
+                or qkv.dtype != torch.bfloat16 or rot != d or d % 16):
+            raise KernelError("rope_kv_write: pieces must be float32 [S, T, width] for bfloat16 qkv, full rotary, d % 16 == 0")
+        _contig(pieces, "pieces")
+        splits, plane = pieces.shape[0], qkv.numel()
     if qkv.shape[1] != (nq + 2 * nkv) * d:
         raise KernelError("rope_kv_write: qkv must be [T, (nq + 2 nkv) d]")
     _contig(qkv, "qkv"); _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
@@ -172,8 +182,8 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
     _check(core().tl_rope_kv_write(
         _ptr(qkv), dtype_code(qkv.dtype), _ptr(bias), dtype_code(bias.dtype) if bias is not None else 0,
         _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(inv_freq), rot, nq, nkv, d,
-        _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T, _stream()),
-        "rope_kv_write")
+        _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T,
+        _ptr(pieces), splits, plane, _stream()), "rope_kv_write")
 
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

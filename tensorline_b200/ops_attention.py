@@ -94,15 +94,15 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     A block streams its range of keys tile by tile (64 keys), and a tile costs it about a microsecond
     whatever else runs, so a request's keys are cut into ranges until the blocks fill the GPU's resident
     slots once (a second, partly filled round would double the time) - but not finer than four tiles a
-    range (two when that leaves fewer than 64 blocks), below which the merge of the partials costs more
-    than the shorter ranges save.  Measured at 7B sizes, context 4,065: batch 1 -> 16 ranges, 8 -> 8, 64 -> 1."""
+    range (two when that leaves 64 blocks or fewer), below which the merge of the partials costs more
+    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 4 -> 16, 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1."""
     m_tiles = -(-group // 16)
     tiles = max(1, -(-span // KEY_TILE))
     base = max(1, batch * nkv * m_tiles)
     resident = NUM_SMS * decode_blocks_per_sm(head_dim)
     fill = max(1, resident // base)
     splits = min(fill, max(1, tiles // 4), max_splits)
-    if base * splits < 64:
+    if base * splits <= 64:
         splits = min(fill, max(1, tiles // 2), max_splits)
     chunk = -(-tiles // splits) * KEY_TILE
     splits = -(-tiles * KEY_TILE // chunk)

@@ -18,7 +18,7 @@ import torch
 from .. import ops
 from ..cache import PagedKV
 from .base import MIXERS, POSITION_ENCODINGS, Part, PartSpec, Runtime, TensorSpec, register_mixer
-from .linear import matmul
+from .linear import SplitSum, matmul
 
 
 @register_mixer("paged_attention")
@@ -61,11 +61,15 @@ class PagedAttention(Part):
     def forward(self, h, ctx, cache):
         nq, nkv, d = self.nq, self.nkv, self.d
         T = h.shape[0]
-        qkv = matmul(h, self.w_qkv)
         inv_freq, rot = self.position.rotary()
+        qkv = matmul(h, self.w_qkv, may_defer=rot == d and d % 16 == 0)
+        pieces = None
+        if isinstance(qkv, SplitSum):                    # a split-K product: the rotary kernel sums its pieces
+            pieces = qkv.pieces
+            qkv = torch.empty(qkv.shape, dtype=h.dtype, device=h.device)
         table = ctx.tables[cache.group]
         ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
-                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner)
+                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces)
         o = torch.empty((T, nq * d), dtype=h.dtype, device=h.device)
         self.attend(qkv, o, ctx, cache, table)
         return matmul(o, self.w_o, may_defer=True)             # the block's next norm adds it up

@@ -115,6 +115,34 @@ def test_rope_and_kv_write(adt, rot, d):
     assert int((kp != 0).any(dim=-1).sum()) == T * nkv                       # nothing else was written
 
 
+def test_rope_sums_the_pieces_of_a_split_product():
+    """Handed the unsummed float32 pieces of the projection, the rotary kernel gives bit for bit what it
+    gives from their bfloat16 sum: q in the qkv buffer, k and v in the pages."""
+    from tensorline_b200 import ops
+    nq, nkv, d, ps, S = 5, 2, 32, 8, 3
+    pos, slots = [0, 7, 8, 300], [1, 0, 0, 1]
+    T, W = len(pos), (5 + 2 * 2) * 32
+    pieces = rnd(S, T, W, seed=21).cuda()
+    whole = (pieces[0] + pieces[1] + pieces[2]).to(torch.bfloat16)
+    bias = rnd(W, seed=22, scale=0.5, dtype=torch.bfloat16).cuda()
+    table = torch.randperm(90, generator=torch.Generator().manual_seed(4))[:80].reshape(2, 40).to(torch.int32).cuda()
+    inv_freq = (10000.0 ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).float().cuda()
+    outs = []
+    for use_pieces in (False, True):
+        kp = torch.zeros(91, nkv, ps, d, dtype=torch.bfloat16, device="cuda")
+        vp = torch.zeros_like(kp)
+        qkv = torch.full((T, W), 7.0, dtype=torch.bfloat16, device="cuda") if use_pieces else whole.clone()
+        ops.rope_kv_write(qkv, bias, i32(pos), i32(slots), table, ps, inv_freq, d, nq, nkv, d, kp, vp,
+                          pieces=pieces if use_pieces else None)
+        outs.append((qkv[:, :nq * d].clone(), kp, vp))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert float(outs[0][1].abs().sum()) > 0
+    with pytest.raises(ops.KernelError, match="pieces"):
+        ops.rope_kv_write(whole.float(), bias.float(), i32(pos), i32(slots), table, ps, inv_freq, d, nq, nkv, d,
+                          outs[0][1].float(), outs[0][2].float(), pieces=pieces)
+
+
 @pytest.mark.parametrize("V", [5003, 40007])            # one block per row; slices merged by a second kernel
 def test_argmax_lowest_index_wins(V):
     from tensorline_b200 import ops
