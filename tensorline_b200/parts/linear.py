@@ -3,8 +3,8 @@
 The 32-bit engine uses the exact-order FFMA kernel of this package.  The bfloat16 engine has two
 routes, both with float32 accumulation:
   * the hand-written tcgen05 / TMA kernel (`csrc/gemm_tc.cu`) for steps of few tokens against large
-    matrices, where it streams the weights faster than the library (measured on the 7B shapes: gate|up,
-    down and the output head at up to 16 tokens);
+    matrices, where it streams the weights faster than the library and chains with the kernels around
+    it (measured on the 7B shapes: every projection and the output head at up to 64 tokens);
   * the library product (cuBLAS through torch) everywhere else, as tzar-beep/Tensorline's engine does
     for every projection (tensorline/paged.py:248-250, :275-276, :287).
 """
@@ -16,7 +16,7 @@ import torch
 
 from .. import ops
 
-TC_MAX_TOKENS = 16                 # the hand-written kernel wins up to this many tokens ...
+TC_MAX_TOKENS = int(os.environ.get("TENSORLINE_B200_TC_MAX_TOKENS", 64))     # the hand-written kernel wins up to this many tokens ...
 TC_MIN_WEIGHT_ELEMENTS = int(os.environ.get("TENSORLINE_B200_TC_MIN_ELEMENTS", 8 << 20))   # ... against matrices of at least this many elements
 
 
