@@ -196,21 +196,24 @@ TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype,
 }
 
 // ------------------------------------------------------------------ SwiGLU activation
-// gu is [T, 2*I]: gate in columns [0, I), up in [I, 2I).  out is [T, I].
+// gu is [T, 2*I], out [T, I].  Gate and up columns alternate in blocks of `blk` columns: out column c has its
+// gate at (c / blk) * 2 blk + c % blk and its up value blk columns further.  blk = I is the plain layout
+// (gate in [0, I), up in [I, 2I)); blk = 64 is what a product against interleaved weight rows leaves.
 template <typename TA>
-__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, int blk, size_t total) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int c = (int)(idx - t * I);
-        const float g = to_f<TA>(gu[t * 2 * I + c]);
-        const float u = to_f<TA>(gu[t * 2 * I + I + c]);
+        const int gc = (c / blk) * 2 * blk + c % blk;
+        const float g = to_f<TA>(gu[t * 2 * I + gc]);
+        const float u = to_f<TA>(gu[t * 2 * I + gc + blk]);
         out[idx] = from_f<TA>((g / (1.0f + expf(-g))) * u);
     }
 }
 
-// 8 values (16 bytes of bfloat16) per thread and iteration: requires I % 8 == 0.
-__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, size_t total8) {
+// 8 values (16 bytes of bfloat16) per thread and iteration: requires I % 8 == 0 and blk % 8 == 0.
+__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk, size_t total8) {
     const int i8 = I >> 3;
     grid_dependency_wait();
     grid_dependency_trigger();
@@ -218,8 +221,9 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / i8;
         const int c = (int)(idx - t * i8) * 8;
-        const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + c);
-        const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + c);
+        const int gc = (c / blk) * 2 * blk + c % blk;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + gc);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + gc + blk);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
         uint4 ov;
@@ -234,20 +238,21 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, cudaStream_t stream) {
+TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, int blk, cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
+    if (blk <= 0 || I % blk) return 1;
     const int threads = 256;
-    if (act_dtype == TL_BF16 && (I & 7) == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
+    if (act_dtype == TL_BF16 && (I & 7) == 0 && (blk & 7) == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
         const size_t total8 = total / 8;
         const size_t want = (total8 + threads - 1) / threads;
         return launch_after_wait(silu_mul_vec8_kernel, dim3((unsigned)(want < 148 * 32 ? want : 148 * 32)), dim3(threads), 0, stream,
-                                 (const bf16*)gu, (bf16*)out, I, total8);
+                                 (const bf16*)gu, (bf16*)out, I, blk, total8);
     }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (act_dtype == TL_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total);
     else
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, blk, total);
     return tl_launch_status();
 }

@@ -104,6 +104,8 @@ struct GemmArgs {
     int out_f32;
     int* status;
     int* counters;        // one per output tile, zero between calls: the last block of a tile to finish sums the partials
+    int gated;            // swap, one split: rows 0..63 of every 128-row tile of A are gate features, rows 64..127 the
+                          // up features of the same 64 columns; out[b, 64 tile + j] = silu(gate) * up, [RB, RA / 2]
 };
 
 template <int BN, int STAGES>
@@ -199,7 +201,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
-                if (a >= G.RA) continue;
+                if (a >= G.RA && !G.gated) continue;
+                if (G.gated) {
+                    // The up half (TMEM lanes 64..127) hands its values over through shared memory (the tile ring is
+                    // idle by now); the gate half rounds both to bfloat16 as a stored gate|up product would have
+                    // been, and writes silu(gate) * up.
+                    float* hand = reinterpret_cast<float*>(tiles);                   // [16 tokens][64 features]
+                    const int f = (quarter & 1) * 32 + lane;
+                    if (quarter >= 2) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) hand[j * 64 + f] = __uint_as_float(r[j]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (quarter < 2) {
+                        const int col = blockIdx.x * 64 + f;                       // feature of the output
+                        if (col < (G.RA >> 1)) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int b = b0 + c0 + j;
+                                if (b < G.RB) {
+                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
+                                    const float u = __bfloat162float(__float2bfloat16_rn(hand[j * 64 + f]));
+                                    ((bf16*)G.out)[(size_t)b * G.ldo + col] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+                                }
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");                   // `hand` is free for the next 16 tokens
+                    continue;
+                }
                 if (gridDim.z > 1) {                     // float partial, laid out like the output
                     float* part = G.partial + (size_t)split * (size_t)G.RA * G.RB;
 #pragma unroll
@@ -345,10 +375,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
 // bn: columns of the other side per tile (16, 32, 64, 128 or 256).  splits > 1 needs `partial`
 // (splits * T * N floats); with `counters` (n_counters zeroed ints, at least one per tile, left zeroed) the
 // last block of a tile sums the partials inside the same launch, else a second kernel does.  `status` (device int, zero before
-// the call) receives a non-zero code if a wait inside the kernel ran out.
+// the call) receives a non-zero code if a wait inside the kernel ran out.  `gated` (swap = 1, one split, N % 128 == 0, bfloat16 out):
+// w holds gate and up rows interleaved in blocks of 64 and y [T, N / 2] receives silu(gate) * up.
 TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
                          int bn, int splits, float* partial, int* status, int* counters, int n_counters,
-                         cudaStream_t stream) {
+                         int gated, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
     if (splits < 1 || (splits > 1 && partial == nullptr)) return 1;
@@ -365,7 +396,9 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     const int per = (k_tiles + splits - 1) / splits;
     splits = (k_tiles + per - 1) / per;                                                  // no empty split
     if (y == nullptr && splits < 2) return 1;
+    if (gated && (!swap || splits != 1 || out_f32 || (N & 127) || y == nullptr)) return 1;   // whole 64 + 64 tiles, one split
     GemmArgs G{};
+    G.gated = gated;
     G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
     dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);

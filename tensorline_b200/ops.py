@@ -19,7 +19,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
-    "tl_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
@@ -145,13 +145,18 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
            "add_rmsnorm")
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gu[:, :I]) * gu[:, I:]."""
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None) -> None:
+    """out = silu(gate) * up from gu [T, 2I].  block None: gate = gu[:, :I], up = gu[:, I:]; else gate
+    and up columns alternate in blocks of `block` columns (gate first), as a product against weight rows
+    interleaved that way leaves them."""
     T, I = out.shape
     if gu.shape != (T, 2 * I) or gu.dtype != out.dtype:
         raise KernelError("silu_mul: gu must be [T, 2I] of out's type")
+    blk = I if block is None else int(block)
+    if blk <= 0 or I % blk:
+        raise KernelError(f"silu_mul: the block of {blk} columns must divide I = {I}")
     _contig(gu, "gu"); _contig(out, "out")
-    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, _stream()), "silu_mul")
+    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, blk, _stream()), "silu_mul")
 
 
 def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tensor, req_slot: torch.Tensor,

@@ -28,7 +28,7 @@ def lib():
     global _lib
     if _lib is None:
         l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
-        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P]
+        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]
         l.tl_gemm_tc.restype = ctypes.c_int
         l.tl_splitk_reduce.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
         l.tl_splitk_reduce.restype = ctypes.c_int
@@ -72,9 +72,13 @@ def plan(T: int, N: int, K: int) -> tuple:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
-            splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False, pieces: bool = False):
+            splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False, pieces: bool = False,
+            gated: bool = False):
     """x [T, K] times w [N, K]^T.  `pieces`: when the plan splits K, return the float32 pieces
-    [S, T, N] unsummed (for a consumer that adds them up itself) instead of the product."""
+    [S, T, N] unsummed (for a consumer that adds them up itself) instead of the product.
+    `gated`: w holds gate and up rows interleaved in blocks of 64 (N % 128 == 0); the result is
+    silu(gate) * up, [T, N / 2] bfloat16, formed in the epilogue (few tokens, one split only:
+    check `can_gate` first)."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: bfloat16 operands only")
     T, K = x.shape
@@ -92,7 +96,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     k_tiles = -(-K // 64)
     splits = -(-k_tiles // -(-k_tiles // min(splits, k_tiles)))          # as the kernel rounds it: no empty split
     pieces = pieces and splits > 1 and not fused_reduce
-    if pieces:
+    if gated:
+        if not swap or splits != 1 or N % 128 or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: the gated epilogue needs the few-token order, one split, N % 128 == 0, bfloat16")
+        if out is None:
+            out = torch.empty((T, N // 2), dtype=out_dtype, device=x.device)
+        elif out.shape != (T, N // 2) or out.dtype != out_dtype or out.stride(1) != 1:
+            raise KernelError("gemm_tc: out must be [T, N / 2] bfloat16 for the gated epilogue")
+    elif pieces:
         out = None
     elif out is None:
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
@@ -102,9 +113,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     st = status_word(x.device)
     _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), N if pieces else out.stride(0),
                             T, N, K, swap, bn, splits, _ptr(partial), _ptr(st),
-                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, _stream()),
+                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, int(gated), _stream()),
            "gemm_tc", launches=1 if (splits == 1 or fused_reduce or pieces) else 2)
     return partial if pieces else out
+
+
+def can_gate(T: int, N: int, K: int) -> bool:
+    """Whether the plan for these sizes allows the gated epilogue."""
+    swap, _, splits = plan(T, N, K)
+    return bool(swap) and splits == 1 and N % 128 == 0
 
 
 def sum_pieces(pieces: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

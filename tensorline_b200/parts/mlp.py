@@ -2,7 +2,8 @@
 
 tzar-beep/Tensorline calls the installed package's module for this (tensorline/paged.py:276;
 shapes tensorline/manager.py:53-54).  Here gate and up are one product against the stacked
-[2I, H] matrix, the activation is a kernel of its own in float32, then the down product.
+[2I, H] matrix, the activation in float32 (a kernel of its own, or the epilogue of the tcgen05
+product for steps of few tokens), then the down product.
 """
 from __future__ import annotations
 
@@ -10,7 +11,9 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_feed_forward
-from .linear import matmul
+from .linear import matmul, use_tc
+
+GATE_BLOCK = 64
 
 
 @register_feed_forward("gated_mlp")
@@ -29,11 +32,25 @@ class GatedMLP(Part):
 
     def bind(self, weights, prefix):
         g, u = weights[f"{prefix}.gate_proj.weight"], weights[f"{prefix}.up_proj.weight"]
-        self.w_gate_up = self._compute_copy(torch.cat((g, u), dim=0))
+        I, H = self.intermediate, self.hidden
+        # bfloat16 engine, I % 64 == 0: gate and up rows alternate in blocks of 64, so that a 128-row tile of
+        # the tcgen05 product holds both halves of 64 output columns and its epilogue can apply the activation
+        self.block = GATE_BLOCK if (self.rt.act_dtype == torch.bfloat16 and I % GATE_BLOCK == 0) else None
+        if self.block:
+            gu = torch.stack((g.view(I // GATE_BLOCK, GATE_BLOCK, H), u.view(I // GATE_BLOCK, GATE_BLOCK, H)), dim=1)
+            self.w_gate_up = self._compute_copy(gu.reshape(2 * I, H))
+        else:
+            self.w_gate_up = self._compute_copy(torch.cat((g, u), dim=0))
         self.w_down = self._compute_copy(weights[f"{prefix}.down_proj.weight"])
 
     def forward(self, h, ctx):
+        I = self.intermediate
+        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
+            from .. import ops_gemm
+            if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
+                m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=True)
+                return matmul(m, self.w_down, may_defer=True)
         gu = matmul(h, self.w_gate_up)
-        m = torch.empty((h.shape[0], self.intermediate), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, m)
+        m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)
+        ops.silu_mul(gu, m, block=self.block)
         return matmul(m, self.w_down, may_defer=True)          # the next norm adds it up

@@ -70,6 +70,46 @@ def test_silu_mul(adt, I):
     assert_close(out, g / (1 + torch.exp(-g)) * u, "silu*up", **tol(adt))
 
 
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("I,block", [(48, 8), (192, 64), (35, 5)])
+def test_silu_mul_interleaved(adt, I, block):
+    """Gate and up columns alternating in blocks give what the plain layout gives."""
+    from tensorline_b200 import ops
+    T = 3
+    gu = rnd(T, 2 * I, seed=6, scale=3.0, dtype=adt)
+    mixed = torch.stack((gu[:, :I].view(T, I // block, block), gu[:, I:].view(T, I // block, block)), dim=2).reshape(T, 2 * I)
+    a = torch.empty(T, I, dtype=adt, device="cuda")
+    b = torch.empty_like(a)
+    ops.silu_mul(gu.cuda(), a)
+    ops.silu_mul(mixed.contiguous().cuda(), b, block=block)
+    assert torch.equal(a, b)
+    with pytest.raises(ops.KernelError, match="divide"):
+        ops.silu_mul(gu.cuda(), a, block=I - 1)
+
+
+@pytest.mark.parametrize("T", [1, 8, 37])
+def test_tcgen05_product_with_the_activation_in_its_epilogue(T):
+    """Against interleaved gate / up rows the gated epilogue gives bit for bit what the product, stored in
+    bfloat16, followed by the activation kernel gives."""
+    from tensorline_b200 import ops, ops_gemm
+    I, K = 320, 520
+    x = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    w = rnd(2 * I, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()          # rows already in blocks of 64 + 64
+    assert not ops_gemm.can_gate(T, 2 * I + 64, K) and not ops_gemm.can_gate(300, 2 * I, K)
+    kw = dict(swap=1, bn=16 if T <= 16 else 64, splits=1)
+    gu = ops_gemm.gemm_tc(x, w, **kw)
+    want = torch.empty(T, I, dtype=torch.bfloat16, device="cuda")
+    ops.silu_mul(gu, want, block=64)
+    got = ops_gemm.gemm_tc(x, w, gated=True, **kw)
+    ops_gemm.check_status()
+    assert got.shape == (T, I) and torch.equal(got, want)
+    full = (x.double() @ w.double().T).view(T, I // 64, 2, 64)
+    g, u = full[:, :, 0].reshape(T, I), full[:, :, 1].reshape(T, I)
+    assert_close(got, g / (1 + torch.exp(-g)) * u, "silu(gate) * up", rtol=3e-2, atol=3e-2)
+    with pytest.raises(ops.KernelError, match="gated"):
+        ops_gemm.gemm_tc(x, w, gated=True, swap=1, bn=16, splits=2)
+
+
 @pytest.mark.parametrize("wdt", DT)
 def test_gemm_f32_exact_order(wdt):
     from tensorline_b200 import ops
