@@ -16,6 +16,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -111,6 +112,12 @@ def build_library(name: str, sources, defines: dict | None = None, extra_flags=(
         tmp.unlink(missing_ok=True)
         raise KernelBuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp, path)                               # atomic: concurrent builders agree
+    for old in path.parent.glob(f"lib{name}_*.so"):     # builds of this library from earlier sources
+        if old != path and re.fullmatch(rf"lib{re.escape(name)}_[0-9a-f]{{16}}\.so", old.name):
+            try:
+                old.unlink()
+            except OSError:
+                pass                                    # another process may still have it mapped, or it is not ours
     if verbose:
         print(f"[tensorline_b200] built {path.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return path
