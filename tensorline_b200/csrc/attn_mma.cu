@@ -483,7 +483,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 constexpr int TMA_TILE_BYTES = BN * D * 2;                       // K or V of one stage
 constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
 constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
-constexpr int TMA_TAB_OFFSET = TMA_BAR_OFFSET + 64;
+constexpr int TMA_TAB_OFFSET = TMA_BAR_OFFSET + 128;             // room for 2 * DEC_STAGES barriers and a flag
+constexpr int TMA_DEC_THREADS = 160;                             // four compute warps and the copy warp
+static_assert(2 * DEC_STAGES * 8 + 8 <= 128, "the barrier area holds at most 7 stages");
 constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM) ? 1 : 0;
 static_assert(TMA_MERGE_OK == 1, "the stage buffers must hold the merge area");
 constexpr long long TMA_WAIT_CYCLES = 4000000000LL;
@@ -514,14 +516,15 @@ __device__ __forceinline__ bool mbar_wait_tma(uint64_t* bar, uint32_t parity, vo
     }
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(TMA_DEC_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const AttnArgs A, int* status) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     bf16* sQ = reinterpret_cast<bf16*>(tiles + TMA_Q_OFFSET);              // [16][DP], padded rows
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TMA_BAR_OFFSET);  // [DEC_STAGES]
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + DEC_STAGES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TMA_BAR_OFFSET);  // [DEC_STAGES]: the stage's copies have landed
+    uint64_t* empty = full + DEC_STAGES;                                   // [DEC_STAGES]: the four compute warps are done with it
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DEC_STAGES);
     int* stab = reinterpret_cast<int*>(tiles + TMA_TAB_OFFSET);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = A.nq / A.nkv, m_tiles = (g + 15) / 16;
@@ -538,24 +541,32 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int qrow = A.q_start[b];
     const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
     const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
-    for (int i = tid; i < n_stage * ppt; i += 128) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
+    for (int i = tid; i < n_stage * ppt; i += TMA_DEC_THREADS) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
     if (tid == 0) {
-        for (int s_ = 0; s_ < DEC_STAGES; ++s_)
+        for (int s_ = 0; s_ < DEC_STAGES; ++s_) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + s_)), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(empty + s_)), "r"(4));
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid == 128) {                                      // the copy thread fetches the two descriptors meanwhile
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
     grid_dependency_wait();                                // queries and the newest keys and values: the kernel before
     grid_dependency_trigger();
-    for (int idx = tid; idx < 16 * CH; idx += 128) {
-        const int r = idx / CH, c = idx - r * CH;
-        const int hg = mt * 16 + r;
-        const bool valid = hg < g;
-        const bf16* src = A.q;
-        if (valid) src = A.q + (size_t)qrow * A.q_stride + (size_t)(kh * g + hg) * D + c * 8;
-        cp_async16(sQ + r * DP + c * 8, src, valid);
+    if (warp < 4) {
+        for (int idx = tid; idx < 16 * CH; idx += 128) {
+            const int r = idx / CH, c = idx - r * CH;
+            const int hg = mt * 16 + r;
+            const bool valid = hg < g;
+            const bf16* src = A.q;
+            if (valid) src = A.q + (size_t)qrow * A.q_stride + (size_t)(kh * g + hg) * D + c * 8;
+            cp_async16(sQ + r * DP + c * 8, src, valid);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
     __syncthreads();                                       // table copy and barriers are visible
 
     auto issue_stage = [&](int st) {                       // one thread: the stage's pages, K and V, D/64 boxes each
@@ -575,10 +586,21 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
     };
-    if (tid == 0)
-        for (int st = 0; st < DEC_STAGES - 1 && st < n_stage; ++st) issue_stage(st);
+    if (warp == 4) {
+        // ------------------------------------------------------------ the copy warp: one thread keeps the ring full
+        if (lane == 0) {
+            for (int st = 0; st < n_stage; ++st) {
+                if (st >= DEC_STAGES &&
+                    !mbar_wait_tma(empty + st % DEC_STAGES, ((st / DEC_STAGES) - 1) & 1, abort_flag, status)) break;
+                issue_stage(st);
+            }
+        }
+        __syncthreads();                                   // meets the compute warps after their last stage
+        __syncthreads();                                   // and after they have laid out their partial results
+        return;
+    }
     cp_async_wait<0>();
-    __syncthreads();                                       // the queries are in
+    asm volatile("bar.sync 1, 128;" ::: "memory");         // the queries are in (the four compute warps only)
     uint32_t qf[KBLK][4];
 #pragma unroll
     for (int kb = 0; kb < KBLK; ++kb)
@@ -591,12 +613,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int st = 0; st < n_stage; ++st) {
-        __syncthreads();                                   // every warp is done with stage st-1: its buffer is free
-        if (tid == 0 && st + DEC_STAGES - 1 < n_stage) issue_stage(st + DEC_STAGES - 1);
         const int buf = st % DEC_STAGES;
         if (!mbar_wait_tma(full + buf, (st / DEC_STAGES) & 1, abort_flag, status)) break;
         const int key0 = k_begin + st * BN + warp * 16;    // this warp's 16 keys of the stage
-        if (key0 >= k_end) continue;
+        if (key0 >= k_end) {                               // none of them exist: hand the buffer back at once
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + buf)) : "memory");
+            continue;
+        }
         const unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
         const unsigned char* vt = kt + TMA_TILE_BYTES;
         float s[2][4];
@@ -621,9 +644,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mma_bf16(o[nb], a, bfr[0], bfr[1]);
             mma_bf16(o[nb + 1], a, bfr[2], bfr[3]);
         }
+        __syncwarp();                                      // every lane has read the stage
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + buf)) : "memory");
     }
     __syncthreads();                                       // the stage buffers become the merge area
-    if (*abort_flag) return;
+    if (*abort_flag) { __syncthreads(); return; }
 
     float* mO = reinterpret_cast<float*>(tiles);           // [4][16][D]
     float* mML = mO + 4 * 16 * D;                          // [4][16][2]
@@ -874,7 +899,7 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
-    e = launch_after_wait(attn_decode_tma_kernel, grid, dim3(128), (size_t)smem, stream, mk, mv, A, status);
+    e = launch_after_wait(attn_decode_tma_kernel, grid, dim3(TMA_DEC_THREADS), (size_t)smem, stream, mk, mv, A, status);
     if (e || splits == 1) return e;
     dim3 cgrid(nq, B);
     return launch_after_wait(attn_combine_kernel, cgrid, dim3(D < 128 ? ((D + 31) / 32) * 32 : 128), 0, stream, A);
