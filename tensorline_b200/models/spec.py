@@ -42,6 +42,7 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm"
     head_prefix: str = "lm_head"
     embedding_position: PartSpec | None = None        # an encoding added to the embedded tokens, if any
+    embedding_position_prefix: str = "model.embed_positions"     # where its tensors live, if it has any
     eos_token_id: int | None = None
     max_position_embeddings: int | None = None
 
@@ -67,6 +68,8 @@ class Model:
     # ---- weights
     def expected_tensors(self) -> dict:
         out = dict(self.embedding.expected_tensors(self.spec.embedding_prefix))
+        if self.embedding_position is not None:
+            out.update(self.embedding_position.expected_tensors(self.spec.embedding_position_prefix))
         for block, layer in zip(self.blocks, self.spec.layers):
             out.update(block.expected_tensors(layer.prefix))
         out.update(self.final_norm.expected_tensors(self.spec.final_norm_prefix))
@@ -75,6 +78,8 @@ class Model:
 
     def bind(self, weights: dict) -> None:
         self.embedding.bind(weights, self.spec.embedding_prefix)
+        if self.embedding_position is not None:
+            self.embedding_position.bind(weights, self.spec.embedding_position_prefix)
         for block, layer in zip(self.blocks, self.spec.layers):
             block.bind(weights, layer.prefix)
         self.final_norm.bind(weights, self.spec.final_norm_prefix)
