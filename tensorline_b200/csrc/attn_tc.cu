@@ -19,6 +19,7 @@
 // accumulator in float, P in bfloat16 for P V.  Every mbarrier wait is bounded; on a time-out the block
 // records a code in `status` and leaves.
 #include "common.cuh"
+#include <cuda.h>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -416,6 +417,338 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     }
 }
 
+#if HEAD_DIM <= 128
+// ------------------------------------------------------------------------------------------------
+// Two query tiles per block (head sizes 64 and 128, pages of 8 to 64 tokens).
+//
+// Time stamps per role in the kernel above showed every role at about 1,700 cycles a key tile: the softmax
+// warps alone on their schedulers (64 exponentials a row on the special-function unit, then packing and
+// stores), the copy warps issuing a thousand cp.async each, and the one MMA thread, which needs about 90
+// cycles to issue a tcgen05.mma whatever its size - more than these small products take to run (47 cycles for
+// S with 64 keys, 63 for P V; two issuing threads reach the tensor core's rate).  Here a block takes 256
+// query rows as two tiles that share every K and V tile: eight softmax warps, two per scheduler; four MMA
+// issuers (S and P V of each tile); K and V as TMA boxes (one page of one KV head, 64 elements wide, 128-byte
+// swizzle) issued by one thread each.  Measured: 2,070 cycles a key tile for both query tiles, of which the
+// exponentials of 2 x 128 x 64 scores are 1,024 on the special-function unit.  Tensor memory: S[tile][2] at
+// columns 0..255, O[tile] behind them.
+constexpr int QT = 2;
+constexpr int THREADS2 = 448;           // warps 0..7: softmax (tile = warp / 4); 8..11: MMA issue; 12: K copies; 13: V copies
+constexpr int SMEM2_TILES = QT * Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + QT * 2 * P_BYTES;
+constexpr int SMEM2_BYTES = SMEM2_TILES + 1024 + 256;
+constexpr uint32_t TMEM2_COLS = 512;
+constexpr uint32_t S2_COL = 0, O2_COL = QT * 2 * BN;
+static_assert(O2_COL + QT * D <= 512, "S and O of both tiles must fit the tensor memory");
+static_assert(SMEM2_BYTES <= 227 * 1024, "shared memory");
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs A) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sQ = smem_addr(base), sK = sQ + QT * Q_BYTES, sV = sK + 2 * K_BYTES, sP = sV + 2 * V_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + SMEM2_TILES);
+    uint64_t* bar_s = bars;          // [tile * 2 + slot] S is complete (commit)
+    uint64_t* bar_p = bars + 4;      // [tile * 2 + slot] the tile's 128 rows have written P
+    uint64_t* bar_o = bars + 8;      // [tile * 2 + slot] O += P V is complete (commit): that P slot is free, O is at rest
+    uint64_t* bar_k = bars + 12;     // [slot] K has landed (TMA bytes)
+    uint64_t* bar_v = bars + 14;     // [slot] V has landed
+    uint64_t* bar_kfree = bars + 16; // [slot] both S issuers are done with this K slot (a commit, or a plain arrival)
+    uint64_t* bar_vfree = bars + 18; // [slot] both P V issuers are done with this V slot
+    uint64_t* bar_q = bars + 20;     // both Q tiles are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kh = blockIdx.y, g = A.nq / A.nkv;
+
+    int tile = gridDim.x - 1 - blockIdx.x, b = 0;          // longest tiles (late rows of a request) first
+    for (; b < A.B; ++b) {
+        const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + QT * BM - 1) / (QT * BM);
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (b >= A.B) return;
+    const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
+    const int rows_total = qlen * g;
+    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    // the two tiles: rows, and the range of key tiles each of them reads
+    int row0[QT], kt_first[QT], kt_last[QT];
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        row0[t] = (tile * QT + t) * BM;
+        if (row0[t] < rows_total) {
+            const int row_end = min(row0[t] + BM, rows_total);
+            const int pos_first = sp + row0[t] / g, pos_last = sp + (row_end - 1) / g;
+            const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
+            kt_first[t] = key_lo / BN; kt_last[t] = pos_last / BN;
+        } else {                                           // no rows: reads nothing
+            kt_first[t] = 1; kt_last[t] = 0;
+        }
+    }
+    // tile 1 holds the later rows: its range starts and ends no earlier than tile 0's
+    const int kt_lo = kt_first[0], kt_hi = max(kt_last[0], kt_last[1]), n_kt = kt_hi - kt_lo + 1;
+    auto reads = [&](int t, int j) { return kt_lo + j >= kt_first[t] && kt_lo + j <= kt_last[t]; };
+
+    if (tid == 0) {
+        for (int i = 0; i < 4; ++i) { mbar_init(bar_s + i, 1); mbar_init(bar_p + i, 128); mbar_init(bar_o + i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_k + i, 1); mbar_init(bar_v + i, 1); mbar_init(bar_kfree + i, 2); mbar_init(bar_vfree + i, 2); }
+        mbar_init(bar_q, 64);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TMEM2_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------ softmax and epilogue: thread = row of tile t
+        const int t = warp >> 2, r = tid & 127;
+        const int R = row0[t] + r;
+        const int pos_r = R < rows_total ? sp + R / g : -1; // -1: no key is visible
+        const int lo_r = A.window > 0 ? max(0, pos_r - A.window + 1) : 0;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int n_mine = kt_last[t] - kt_first[t] + 1;   // <= 0: this tile has no rows
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+
+        for (int i = 0; i < n_mine && ok; ++i) {
+            const int sl = i & 1, kt = kt_first[t] + i, bi = t * 2 + sl;
+            ok = mbar_wait(bar_s + bi, (i >> 1) & 1, abort_flag, A.status, 1);           // S(i) is ready
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t s_addr = lane_addr + S2_COL + bi * BN;
+            const int key0 = kt * BN;
+            float s[BN];
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32)
+                tmem_ld32(s_addr + c0, reinterpret_cast<float(&)[32]>(s[c0]));
+            tmem_ld_wait();                                 // all parts in flight, one wait
+            if (!(key0 + BN - 1 <= pos_r && key0 >= lo_r)) {   // not every key of the tile is visible to this row
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int j = key0 + c;
+                    if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * A.scale_log2;
+            const bool raise = mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY);
+            const float m_new = raise ? fmaxf(mx, m_ref) : m_ref;
+            const bool fix_o = raise && i > 0 && m_ref != -INFINITY;        // O holds earlier tiles of this row
+            if (__any_sync(0xffffffffu, fix_o)) {
+                ok = mbar_wait(bar_o + t * 2 + ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, A.status, 2);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float alpha = fix_o ? fast_exp2(m_ref - m_new) : 1.0f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(lane_addr + O2_COL + t * D + c0, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] *= alpha;
+                    tmem_st32(lane_addr + O2_COL + t * D + c0, o);
+                }
+            }
+            m_ref = m_new;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            if (i >= 2) {                                   // the P slot is free once P(i-2) V(i-2) is complete
+                ok = mbar_wait(bar_o + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 3);
+                if (!ok) break;
+            }
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j8 = 0; j8 < BN / 8; ++j8) {
+                float p[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    p[e] = fast_exp2(fmaf(s[j8 * 8 + e], A.scale_log2, -m_use));
+                    l4[e & 3] += p[e];
+                }
+                const uint32_t dst = sP + bi * P_BYTES + swz(BM, r, j8);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
+                             "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
+            }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            fence_async_proxy();                            // generic-proxy writes of P before the MMA reads them
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar_p + bi);
+        }
+        // ------------------------------------------------------------ epilogue: the tile's last P V has finished
+        if (ok && n_mine > 0 &&
+            mbar_wait(bar_o + t * 2 + ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag, A.status, 4)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = nullptr;
+            if (R < rows_total) dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float o[32];
+                tmem_ld32(lane_addr + O2_COL + t * D + c0, o);
+                tmem_ld_wait();
+                if (dst) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(o[c] * inv, o[c + 1] * inv); v.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
+                        v.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv); v.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = v;
+                    }
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------------------------------------ MMA issuers: one thread each in warps 8..11.
+        // A thread needs about 90 cycles to issue one tcgen05.mma whatever its size, more than these products take
+        // to run (47 cycles for S with 64 keys, 63 for P V), so one issuer would be the bottleneck (measured: two
+        // issuers run at the tensor core's rate).  Warps 8, 9 issue S = Q_t K^T for tile t = 0, 1; warps 10, 11
+        // issue O_t += P V.  Every issuer walks all key tiles, also those its query tile does not read, and
+        // hands each K (V) slot back with one of the two arrivals its barrier counts.
+        if (lane == 0) {
+            const int t = warp & 1;
+            bool ok = true;
+            if (warp < 10) {
+                constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                ok = mbar_wait(bar_q, 0, abort_flag, A.status, 11, true);
+                int i = 0;                                  // products issued for this tile
+                for (int j = 0; j < n_kt && ok; ++j) {
+                    const int sl = j & 1;
+                    ok = mbar_wait(bar_k + sl, (j >> 1) & 1, abort_flag, A.status, 5, true);        // K(j) is in
+                    if (!ok) break;
+                    if (!reads(t, j)) { mbar_arrive(bar_kfree + sl); continue; }
+                    const int bi = t * 2 + (i & 1);
+                    if (i >= 2) {                           // that S slot is free once the softmax of product i-2 has written its P
+                        ok = mbar_wait(bar_p + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 6, true);
+                        if (!ok) break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t k_addr = sK + sl * K_BYTES;
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k)
+                        umma(tmem + S2_COL + bi * BN, desc_kmajor(sQ + t * Q_BYTES + (k >> 2) * BM * 128 + (k & 3) * 32),
+                             desc_kmajor(k_addr + (k >> 2) * BN * 128 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+                    umma_commit(bar_s + bi);
+                    umma_commit(bar_kfree + sl);
+                    ++i;
+                }
+            } else {
+                constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                int i = 0;
+                for (int j = 0; j < n_kt && ok; ++j) {
+                    const int sl = j & 1;
+                    ok = mbar_wait(bar_v + sl, (j >> 1) & 1, abort_flag, A.status, 7, true);        // V(j) is in
+                    if (!ok) break;
+                    if (!reads(t, j)) { mbar_arrive(bar_vfree + sl); continue; }
+                    const int bi = t * 2 + (i & 1);
+                    ok = mbar_wait(bar_p + bi, (i >> 1) & 1, abort_flag, A.status, 8, true);        // P is written
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t v_addr = sV + sl * V_BYTES, p_addr = sP + bi * P_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k)       // O_t += P V(j)
+                        umma(tmem + O2_COL + t * D, desc_kmajor(p_addr + (k >> 2) * BM * 128 + (k & 3) * 32),
+                             desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_o + bi);
+                    umma_commit(bar_vfree + sl);
+                    ++i;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ copies: warps 12 and 13 bring Q together, then
+        // one thread of warp 12 issues the TMA boxes of K, one of warp 13 those of V, up to two tiles ahead
+        constexpr int CH = D / 8;
+        for (int idx = tid - 12 * 32; idx < QT * BM * CH; idx += 64) {    // Q tiles: row = (token, head of the group)
+            const int t = idx / (BM * CH), rem = idx - t * (BM * CH);
+            const int r = rem / CH, c = rem - r * CH;
+            const int R = row0[t] + r;
+            const bool valid = R < rows_total;
+            const bf16* src = A.q;
+            if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
+            cp_async16(sQ + t * Q_BYTES + swz(BM, r, c), src, valid);
+        }
+        cp_async_wait_all();
+        fence_async_proxy();
+        mbar_arrive(bar_q);
+        if (lane == 0) {
+            const bool is_k = warp == 12;
+            const CUtensorMap* map = is_k ? &map_k : &map_v;
+            asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+            uint64_t* bar_free = is_k ? bar_kfree : bar_vfree;
+            uint64_t* bar_full = is_k ? bar_k : bar_v;
+            const uint32_t tiles = is_k ? sK : sV;
+            int ps_shift = 0;
+            while ((1 << ps_shift) < A.page_size) ++ps_shift;
+            const int ppt = BN >> ps_shift;                 // pages per key tile: 1 to 8
+            bool ok = true;
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int sl = j & 1;
+                int page[8];
+#pragma unroll
+                for (int pg = 0; pg < 8; ++pg)              // the tile's page numbers, all requested before the wait
+                    if (pg < ppt) page[pg] = tab[min((((kt_lo + j) * BN) >> ps_shift) + pg, A.max_pages - 1)];
+                if (j >= 2) {
+                    ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
+                    if (!ok) break;
+                }
+                mbar_expect_tx(bar_full + sl, K_BYTES);
+#pragma unroll
+                for (int pg = 0; pg < 8; ++pg) {
+                    if (pg >= ppt) break;
+                    const int row = (page[pg] * A.nkv + kh) << ps_shift;
+#pragma unroll
+                    for (int db = 0; db < D / 64; ++db)
+                        tma_box(tiles + sl * K_BYTES + db * (BN * 128) + ((pg << ps_shift) * 128), map, bar_full + sl, db * 64, row);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM2_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+bool g_attr2_done = false;
+
+// The cache tensor [pages, nkv, page, D] as rows of D elements; a box is one page of one KV head, 64 wide.
+int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 101;
+}
+#endif  // HEAD_DIM <= 128
+
 bool g_attr_done = false;
 
 }  // namespace
@@ -443,4 +776,47 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     dim3 grid(total_tiles, nkv);
     attn_tc_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(A);
     return tl_launch_status();
+}
+
+// The same attention with two query tiles (256 rows) per block and K, V loaded by TMA.  total_tiles = sum over
+// requests of ceil(q_len * g / 256); `total_pages`: first dimension of the cache tensors.  Returns 2 if this build
+// or these sizes do not take this kernel (head size above 128, pages of fewer than 8 tokens, unaligned pages).
+TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                  long long total_pages, const int* table, int max_pages, int page_size,
+                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                  int window, float scale, int total_tiles, int* status, cudaStream_t stream) {
+#if HEAD_DIM <= 128
+    if (total_tiles <= 0 || B <= 0) return 0;
+    if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
+    if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
+    if (nq % nkv || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+            qres != cudaDriverEntryPointSuccess) return 100;
+        g_encode = (EncodeTiledFn)fn;
+    }
+    if (!g_attr2_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc2_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        g_attr2_done = true;
+    }
+    CUtensorMap mk, mv;
+    const long long rows = total_pages * nkv * page_size;
+    int e;
+    if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
+    if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
+    TcAttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status;
+    dim3 grid(total_tiles, nkv);
+    attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    return tl_launch_status();
+#else
+    return 2;
+#endif
 }

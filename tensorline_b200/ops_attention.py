@@ -64,6 +64,9 @@ def attn_tc_lib(head_dim: int):
         lib = load_library(f"tl_attn_tc_hd{head_dim}", ["attn_tc.cu"], {"HEAD_DIM": head_dim})
         lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P]
         lib.tl_attn_tc_prefill.restype = ctypes.c_int
+        lib.tl_attn_tc2_prefill.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F,
+                                            _I, _P, _P]
+        lib.tl_attn_tc2_prefill.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
 
@@ -87,6 +90,29 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
                                              _ptr(status_word(q.device)), _stream()), "attn_tc_prefill")
+
+
+TC_PAIR = os.environ.get("TENSORLINE_B200_TC_PAIR", "1") != "0"   # 0: one query tile per block only (A/B timing)
+
+
+def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
+                    nq, nkv, d, window, scale) -> bool:
+    """Prompt-portion attention on tcgen05 with two query tiles (256 rows) per block and K, V by TMA.
+    Head sizes 64 and 128, pages of 8 to 64 tokens; returns False (nothing launched) for other sizes."""
+    from .ops_gemm import status_word
+    if d > 128 or page_size < 8 or page_size > KEY_TILE or page_size & (page_size - 1):
+        return False
+    g = nq // nkv
+    B = len(h_q_start) - 1
+    tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in range(B))
+    rc = attn_tc_lib(d).tl_attn_tc2_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
+                                            _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
+                                            _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
+                                            _ptr(status_word(q.device)), _stream())
+    if rc == 2:
+        return False
+    _check(rc, "attn_tc2_prefill")
+    return True
 
 
 def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128, max_splits: int = 128) -> tuple:
@@ -174,6 +200,13 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05; steps of mostly
         # single tokens (a few decoded tokens beside a short portion) keep the 64-row mma.sync tiles.
         rows = ctx.T * (nq // nkv)
-        fn = prefill_tc if (TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rows >= 96 * ctx.B) else prefill
-        fn(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
-           ctx.h_q_start, nq, nkv, d, window, scale)
+        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rows >= 96 * ctx.B
+        args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
+                ctx.h_q_start, nq, nkv, d, window, scale)
+        # Two query tiles a block pay once its blocks (one per SM) fill the GPU; below that the single-tile
+        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 78 against 99 us,
+        # 4,096 174 against 275 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 90 against 78 us)
+        pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * (nq // nkv) // (2 * TC_QUERY_TILE)) for i in range(ctx.B))
+        if use_tc and TC_PAIR and pairs * nkv >= NUM_SMS and prefill_tc_pair(*args):
+            return
+        (prefill_tc if use_tc else prefill)(*args)

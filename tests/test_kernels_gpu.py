@@ -254,21 +254,27 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
     (28, 4, 128, 16, [1, 1000, 700, 63], [1, 1, 1, 1], None),
     (8, 2, 64, 8, [500, 129], [1, 1], 200),
     (3, 1, 256, 32, [333], [1], None),
+    (7, 1, 128, 16, [0, 700, 41], [200, 37, 90], None),     # several 128-row tiles a request: both tiles of a pair, a lone first tile
+    (14, 2, 64, 8, [300], [130], 70),                       # a window that lets the later tile of a pair start further on
+    (4, 2, 128, 64, [0], [129], None),
 ]
 
 
 @pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
-@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16"])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16"])
 def test_paged_attention(case, kernel):
     """Decode and prefill attention over scattered pages against the plain formula."""
     from tensorline_b200 import ops, ops_attention
     nq, nkv, d, ps, ctx_lens, step_lens, window = case
+    if kernel == "tcgen05_pair_bf16" and d % 64:
+        pytest.skip("no tcgen05 build for this head size")
     if kernel == "tcgen05_bf16" and (d % 64 or ps < 2):
         with pytest.raises(ops.KernelError):
             ops_attention.attn_tc_lib(d) if d % 64 else ops_attention.prefill_tc(
                 torch.zeros(1, nq * d, dtype=torch.bfloat16, device="cuda"), nq * d, None, None, None,
                 torch.zeros(1, 1, dtype=torch.int32, device="cuda"), ps, None, None, None, [0, 1], nq, nkv, d, None, 1.0)
         return
+    pair_ok = d <= 128 and d % 64 == 0 and ps >= 8
     adt = torch.float32 if kernel == "exact_f32" else torch.bfloat16
     B = len(ctx_lens)
     max_pages, num_pages = 128, 300
@@ -301,14 +307,19 @@ def test_paged_attention(case, kernel):
     table = table_tensor(rows, max_pages, num_pages)
     kd, vd = kps.cuda(), vps.cuda()
     scale = d ** -0.5
-    if kernel == "tcgen05_bf16":
+    if kernel in ("tcgen05_bf16", "tcgen05_pair_bf16"):
         q_start = [0]
         for n in step_lens:
             q_start.append(q_start[-1] + n)
-        ops_attention.prefill_tc(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
-                                 q_start, nq, nkv, d, window, scale)
+        fn = ops_attention.prefill_tc if kernel == "tcgen05_bf16" else ops_attention.prefill_tc_pair
+        took = fn(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
+                  q_start, nq, nkv, d, window, scale)
         from tensorline_b200 import ops_gemm
         ops_gemm.check_status()
+        if kernel == "tcgen05_pair_bf16":
+            assert took == pair_ok                                         # other sizes are left to the other kernels
+            if not took:
+                return
     elif kernel != "mma_bf16":
         ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale)
     else:
