@@ -569,31 +569,32 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();                                       // table copy and barriers are visible
 
-    auto issue_stage = [&](int st) {                       // one thread: the stage's pages, K and V, D/64 boxes each
+    // The copy warp: a thread needs about 90 cycles to issue one TMA copy, and a stage is 2 * (64 / page) * (D / 64)
+    // boxes (16 for pages of 16 tokens and head size 128), so the boxes of a stage are spread over the warp's
+    // lanes: one instruction issues them all.
+    auto issue_stage = [&](int st) {                       // whole warp: the stage's pages, K and V, D/64 boxes each
         const int buf = st % DEC_STAGES;
         unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
-        unsigned char* vt = kt + TMA_TILE_BYTES;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(full + buf)), "r"(2 * TMA_TILE_BYTES) : "memory");
-        for (int pg = 0; pg < ppt; ++pg) {
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(full + buf)), "r"(2 * TMA_TILE_BYTES) : "memory");
+        __syncwarp();
+        constexpr int DB = D / 64;
+        const int per_tensor = ppt * DB;
+        for (int idx = lane; idx < 2 * per_tensor; idx += 32) {
+            const int is_v = idx >= per_tensor, rem = idx - is_v * per_tensor;
+            const int pg = rem / DB, db = rem - pg * DB;
             const int row = (stab[st * ppt + pg] * A.nkv + kh) * A.page_size;
-#pragma unroll
-            for (int db = 0; db < D / 64; ++db) {
-                const uint32_t off = db * (BN * 128) + pg * A.page_size * 128;
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                             ::"r"(smem_u32(kt + off)), "l"(&map_k), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                             ::"r"(smem_u32(vt + off)), "l"(&map_v), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
-            }
+            const uint32_t dst = smem_u32(kt + is_v * TMA_TILE_BYTES + db * (BN * 128) + pg * A.page_size * 128);
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                         ::"r"(dst), "l"(is_v ? &map_v : &map_k), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
         }
     };
     if (warp == 4) {
-        // ------------------------------------------------------------ the copy warp: one thread keeps the ring full
-        if (lane == 0) {
-            for (int st = 0; st < n_stage; ++st) {
-                if (st >= DEC_STAGES &&
-                    !mbar_wait_tma(empty + st % DEC_STAGES, ((st / DEC_STAGES) - 1) & 1, abort_flag, status)) break;
-                issue_stage(st);
-            }
+        // ------------------------------------------------------------ the copy warp keeps the ring full
+        for (int st = 0; st < n_stage; ++st) {
+            if (st >= DEC_STAGES &&
+                !mbar_wait_tma(empty + st % DEC_STAGES, ((st / DEC_STAGES) - 1) & 1, abort_flag, status)) break;
+            issue_stage(st);
         }
         __syncthreads();                                   // meets the compute warps after their last stage
         __syncthreads();                                   // and after they have laid out their partial results

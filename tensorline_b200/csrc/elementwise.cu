@@ -91,7 +91,7 @@ template <> struct Vec4<bf16> {
 // `partial` (instead of r): the addend is still in pieces, [splits][rows of x][H] float, as a split-K product
 // leaves them; they are summed in split order and rounded to the activation type first, which is what a
 // separate reduction pass would have handed over as r.
-template <typename TA, typename TW, int NV>
+template <typename TA, typename TW, int NV, bool PIECES>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ r,
                                        const TW* __restrict__ w, TA* __restrict__ out,
                                        const int* __restrict__ rows, int H, float eps, int write_x,
@@ -99,10 +99,16 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
     __shared__ float red[33];
     const int i = blockIdx.x, nvec = H >> 2;
     float v[NV][4], wv[NV][4];
+    // The weights are nobody's output.  A launch of few rows (a decode step) reads them before the wait for the
+    // kernel in front, so only the row itself is fetched after it; a launch of many rows keeps all its loads
+    // together behind the wait (the wait would otherwise stand between two memory latencies in every block).
+    const bool early = gridDim.x <= 128;
+    if (early) {
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {                       // the weights are nobody's output: read them before the wait
-        const int c = threadIdx.x + k * blockDim.x;
-        if (c < nvec) Vec4<TW>::load(w + 4 * c, wv[k]);
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) Vec4<TW>::load(w + 4 * c, wv[k]);
+        }
     }
     grid_dependency_wait();
     grid_dependency_trigger();
@@ -110,9 +116,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restri
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
-        if (c < nvec) Vec4<float>::load(x + src + 4 * c, v[k]);
+        if (c < nvec) {
+            Vec4<float>::load(x + src + 4 * c, v[k]);
+            if (!early) Vec4<TW>::load(w + 4 * c, wv[k]);
+        }
     }
-    if (partial) {
+    if (PIECES) {                                        // an instantiation of its own: the plain one keeps its registers
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int c = threadIdx.x + k * blockDim.x;
@@ -170,7 +179,8 @@ static int launch_add_rmsnorm(void* x, const void* r, const void* w, void* out, 
                      ((((uintptr_t)x | (uintptr_t)r | (uintptr_t)w | (uintptr_t)out | (uintptr_t)partial) & 15) == 0);
     if (partial && !vec) return 1;                       // pieces only on the vector path; the caller sums them first
 #define VLAUNCH(NV) { int th = ((nvec + NV - 1) / NV + 31) / 32 * 32; \
-        launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); }
+        if (partial) launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, true>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); \
+        else launch_after_wait(add_rmsnorm_vec_kernel<TA, TW, NV, false>, dim3(R), dim3(th), 0, stream, (float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x, partial, splits, plane); }
     if (!vec) add_rmsnorm_kernel<TA, TW><<<R, 256, 0, stream>>>((float*)x, (const TA*)r, (const TW*)w, (TA*)out, rows, H, eps, write_x);
     else if (nvec <= 1024) VLAUNCH(1)
     else if (nvec <= 2048) VLAUNCH(2)

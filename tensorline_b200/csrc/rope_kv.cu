@@ -52,7 +52,7 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
 // The bfloat16 fast path (full rotary, d % 16 == 0): one block per token; the token's d/2 cosines and
 // sines are computed once into shared memory and shared by all heads; each thread moves 8 + 8 values
 // (two 16-byte loads, two 16-byte stores).  Same arithmetic as the kernel above.
-template <typename TW>
+template <typename TW, bool PIECES>
 __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict__ bias,
                                    const int* __restrict__ pos, const int* __restrict__ req_slot,
                                    const int* __restrict__ table, int max_pages, int page_size,
@@ -83,7 +83,7 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
     for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
         const int hh = item / per_head, i0 = (item - hh * per_head) * 8;
         float a[8], b[8];
-        if (pieces) {
+        if (PIECES) {                                    // an instantiation of its own: the plain one keeps its registers
 #pragma unroll
             for (int k = 0; k < 8; ++k) { a[k] = 0.f; b[k] = 0.f; }
             const float* src = pieces + (size_t)t * (nq + 2 * nkv) * d + hh * d + i0;
@@ -158,13 +158,11 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
         const int items = heads * (d / 16);
         const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
         const size_t smem = (size_t)d * sizeof(float);
-        if (bias_dtype == TL_F32)
-            return launch_after_wait(rope_kv_vec_kernel<float>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const float*)bias,
-                pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads,
-                pieces, splits, (size_t)plane);
-        return launch_after_wait(rope_kv_vec_kernel<bf16>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const bf16*)bias,
-            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads,
-            pieces, splits, (size_t)plane);
+#define VROPE(TW, P) launch_after_wait(rope_kv_vec_kernel<TW, P>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const TW*)bias, \
+            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads, pieces, splits, (size_t)plane)
+        if (bias_dtype == TL_F32) return pieces ? VROPE(float, true) : VROPE(float, false);
+        return pieces ? VROPE(bf16, true) : VROPE(bf16, false);
+#undef VROPE
     }
     dim3 grid(T, heads);
     const int half = d / 2;
