@@ -222,29 +222,42 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
     }
 }
 
-// 8 values (16 bytes of bfloat16) per thread and iteration: requires I % 8 == 0 and blk % 8 == 0.
-__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk, size_t total8) {
-    const int i8 = I >> 3;
+// 8 values (16 bytes of bfloat16) per thread and chunk: requires I % 8 == 0 and blk % 8 == 0.  grid (column
+// groups, tokens): no division per element; with many tokens a thread takes two chunks a block's width apart,
+// so four 16-byte loads are in flight before the first is used; with few it takes one, for more blocks.
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk) {
+    const size_t t = blockIdx.y;
+    const int c0 = (blockIdx.x * 256 * CHUNKS + threadIdx.x) * 8;
     grid_dependency_wait();
     grid_dependency_trigger();
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
-         idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = idx / i8;
-        const int c = (int)(idx - t * i8) * 8;
-        const int gc = (c / blk) * 2 * blk + c % blk;
-        const uint4 gv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + gc);
-        const uint4 uv = *reinterpret_cast<const uint4*>(gu + t * 2 * I + gc + blk);
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    const bf16* row = gu + t * 2 * (size_t)I;
+    uint4 gv[CHUNKS], uv[CHUNKS];
+    int cs[CHUNKS];
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) cs[k] = c0 + k * 256 * 8;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        if (cs[k] < I) {
+            const int gc = (cs[k] / blk) * 2 * blk + cs[k] % blk;
+            gv[k] = *reinterpret_cast<const uint4*>(row + gc);
+            uv[k] = *reinterpret_cast<const uint4*>(row + gc + blk);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        if (cs[k] >= I) continue;
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv[k]);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv[k]);
         uint4 ov;
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float g0 = __low2float(g2[k]), g1 = __high2float(g2[k]);
-            const float u0 = __low2float(u2[k]), u1 = __high2float(u2[k]);
-            o2[k] = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+        for (int e = 0; e < 4; ++e) {
+            const float g0 = __low2float(g2[e]), g1 = __high2float(g2[e]);
+            const float u0 = __low2float(u2[e]), u1 = __high2float(u2[e]);
+            o2[e] = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
         }
-        *reinterpret_cast<uint4*>(out + t * I + c) = ov;
+        *reinterpret_cast<uint4*>(out + t * I + cs[k]) = ov;
     }
 }
 
@@ -253,11 +266,12 @@ TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I
     if (total == 0) return 0;
     if (blk <= 0 || I % blk) return 1;
     const int threads = 256;
-    if (act_dtype == TL_BF16 && (I & 7) == 0 && (blk & 7) == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
-        const size_t total8 = total / 8;
-        const size_t want = (total8 + threads - 1) / threads;
-        return launch_after_wait(silu_mul_vec8_kernel, dim3((unsigned)(want < 148 * 32 ? want : 148 * 32)), dim3(threads), 0, stream,
-                                 (const bf16*)gu, (bf16*)out, I, blk, total8);
+    if (act_dtype == TL_BF16 && (I & 7) == 0 && (blk & 7) == 0 && T <= 65535 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
+        if (T >= 256)
+            return launch_after_wait(silu_mul_vec8_kernel<2>, dim3((unsigned)((I / 8 + 511) / 512), (unsigned)T), dim3(threads), 0, stream,
+                                     (const bf16*)gu, (bf16*)out, I, blk);
+        return launch_after_wait(silu_mul_vec8_kernel<1>, dim3((unsigned)((I / 8 + 255) / 256), (unsigned)T), dim3(threads), 0, stream,
+                                 (const bf16*)gu, (bf16*)out, I, blk);
     }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (act_dtype == TL_F32)
