@@ -346,6 +346,51 @@ def test_paged_attention(case, kernel):
     assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))
 
 
+@pytest.mark.parametrize("window", [None, 3000])
+def test_attention_over_a_long_context(window):
+    """9,000 cached tokens (563 pages of 16): a decode step with few and with many key ranges, by cp.async and
+    by TMA, and a 300-token portion on top of the cache through every prefill kernel, against the plain
+    formula.  One far key is planted so that it must win for the last query."""
+    from tensorline_b200 import ops_attention, ops_gemm
+    nq, nkv, d, ps, ctx, step = 4, 1, 128, 16, 9000, 300
+    n = ctx + step
+    k, v = rnd(n, nkv, d, seed=70, dtype=torch.bfloat16), rnd(n, nkv, d, seed=71, dtype=torch.bfloat16)
+    q = rnd(step, nq, d, seed=72, scale=2.0, dtype=torch.bfloat16)
+    far = 6500 if window else 17                                    # inside the window, or near the start
+    k[far] *= 0; k[far, :, 0] = 9.0; q[-1] *= 0; q[-1, :, 0] = 9.0
+    num_pages = 700
+    kd, vd, order = scatter_pages(k, v, ps, num_pages, seed=5)
+    table = table_tensor([order], 640, num_pages)
+    scale = d ** -0.5
+    rows = [0, 1, 150, step - 2, step - 1]                          # checked against the float64 formula
+    want = _plain_attention_rows(q[rows].double(), k.double(), v.double(), [ctx + r for r in rows], window)
+    qd = q.reshape(step, nq * d).cuda()
+    q_start, pos0, slots = i32([0, step]), i32([ctx]), i32([0])
+    outs = {}
+    for name, fn in (("mma", ops_attention.prefill), ("tcgen05", ops_attention.prefill_tc), ("pair", ops_attention.prefill_tc_pair)):
+        out = torch.zeros(step, nq * d, dtype=torch.bfloat16, device="cuda")
+        fn(qd, nq * d, out, kd, vd, table, ps, q_start, pos0, slots, [0, step], nq, nkv, d, window, scale)
+        ops_gemm.check_status()
+        assert_close(out.view(step, nq, d)[rows], want, f"{name} prefill over a long cache", **BF16)
+        outs[name] = out
+    # the decode step: the last token alone, all keys before it cached
+    last = n - 1
+    want1 = _plain_attention_rows(q[-1:].double(), k.double(), v.double(), [last], window)
+    q1 = q[-1:].reshape(1, nq * d).cuda()
+    tiles = -(-(min(n, window + 63) if window else n) // 64)
+    for splits_wanted in (1, 7, 64):
+        chunk = -(-tiles // splits_wanted) * 64
+        splits = -(-tiles * 64 // chunk)
+        po = torch.full((1, nq, splits, d), float("nan"), device="cuda")
+        pml = torch.full((1, nq, splits, 2), float("nan"), device="cuda")
+        for tma in (False, True):
+            out = torch.zeros(1, nq * d, dtype=torch.bfloat16, device="cuda")
+            ops_attention.decode(q1, nq * d, out, kd, vd, table, ps, i32([0]), i32([last]), slots, 1, nq, nkv, d, window, scale,
+                                 chunk, splits, po, pml, tma=tma)
+            ops_gemm.check_status()
+            assert_close(out.view(1, nq, d), want1, f"decode over a long cache, {splits} ranges, tma {tma}", **BF16)
+
+
 def test_attention_refuses_unsupported_head_size():
     from tensorline_b200 import ops, ops_attention
     with pytest.raises(ops.KernelError):
