@@ -68,3 +68,52 @@ def test_seven_b_layer_sizes_match_the_plain_model(big, dtype):
             assert err <= BF16_MODEL_REL * scale, f"{what}: max abs err {err:.3e} (logit scale {scale:.3f})"
     if dtype == "float32":
         assert torch.equal(whole, cut)
+
+
+def test_long_prompt_takes_the_two_tile_attention_and_agrees_with_the_other_kernels(big):
+    """A 1,600-token prompt at these sizes fills the GPU with blocks of two query tiles, so the step runs the
+    two-tile tcgen05 attention; the same prompt with that kernel switched off (one-tile kernel), and then with
+    the exact-order attention, must give the same logits within bfloat16 rounding.  Then 8 tokens are decoded
+    on top (split-K pieces summed by their consumers, activation in the product's epilogue) in one step each
+    and together as a portion."""
+    from tensorline_b200 import Engine, ops, ops_attention
+    from tensorline_b200.engine.runner import StepEntry
+    cfg, weights = big[0], big[1]
+    n, extra = 1600, 8
+    ids = torch.randint(0, cfg.vocab_size, (n + extra,), generator=torch.Generator().manual_seed(9)).tolist()
+    eng = Engine(cfg, dtype="bfloat16", weights=dict(weights), block_size=16, num_blocks=240, max_num_seqs=2,
+                 max_model_len=2048, prefix_caching=False, cuda_graphs=False)
+    runner, cache = eng.runner, eng.cache
+
+    def prompt(rid, exact=False):
+        cache.admit(rid); runner.start_request(rid)
+        cache.grow(rid, 0, n)
+        runner.force_exact_attention = exact
+        try:
+            return runner.step([StepEntry(rid, ids[:n], [0, 700, n - 1])]).double().cpu()
+        finally:
+            runner.force_exact_attention = False
+
+    before = ops.launch_count()
+    pair = prompt("pair")
+    assert ops.launch_count() > before
+    g = cfg.num_attention_heads // cfg.num_key_value_heads
+    assert -(-n * g // 256) * cfg.num_key_value_heads >= ops_attention.NUM_SMS      # the two-tile kernel did run
+    decoded = [runner.step([StepEntry("pair", [ids[n + i]], [0])]).double().cpu()[0] for i in range(extra) if cache.grow("pair", n + i, n + i + 1)]
+    cache.release("pair"); runner.end_request("pair")
+    ops_attention.TC_PAIR = False
+    try:
+        single = prompt("single")
+        cache.grow("single", n, n + extra)
+        portion = runner.step([StepEntry("single", ids[n:n + extra], list(range(extra)))]).double().cpu()
+        cache.release("single"); runner.end_request("single")
+    finally:
+        ops_attention.TC_PAIR = True
+    exact = prompt("exact", exact=True)
+    cache.release("exact"); runner.end_request("exact")
+    scale = float(exact.abs().max())
+    for what, got in (("two-tile", pair), ("one-tile", single)):
+        err = float((got - exact).abs().max())
+        assert err <= BF16_MODEL_REL * scale, f"{what} against exact-order attention: {err:.3e} (scale {scale:.3f})"
+    err = float((torch.stack(decoded) - portion).abs().max())
+    assert err <= BF16_MODEL_REL * float(portion.abs().max()), f"decoded one by one against a portion: {err:.3e}"
