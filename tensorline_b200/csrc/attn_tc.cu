@@ -190,7 +190,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     uint64_t* bar_p = bars + 4;     // [2] the 128 rows have written P(i)
     uint64_t* bar_k = bars + 6;     // [2] K(i) is in shared memory
     uint64_t* bar_v = bars + 8;     // [2] V(i) is in shared memory
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* bar_q = bars + 10;    // the Q tile is in shared memory (brought by the 128 softmax threads)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             mbar_init(bar_s + i, 1); mbar_init(bar_o + i, 1); mbar_init(bar_p + i, 128);
             mbar_init(bar_k + i, 32); mbar_init(bar_v + i, 32);
         }
+        mbar_init(bar_q, BM);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -236,6 +238,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
+        {   // the Q tile, row = (token, head of the group), while the first K and V tiles are on their way
+            constexpr int CH = D / 8;
+            for (int idx = tid; idx < BM * CH; idx += BM) {
+                const int qr = idx / CH, c = idx - qr * CH;
+                const int QR = row0 + qr;
+                const bool valid = QR < rows_total;
+                const bf16* src = A.q;
+                if (valid) src = A.q + (size_t)(qs + QR / g) * A.q_stride + (size_t)(kh * g + QR % g) * D + c * 8;
+                cp_async16(sQ + swz(BM, qr, c), src, valid);
+            }
+            cp_async_wait_all();
+            fence_async_proxy();
+            mbar_arrive(bar_q);
+        }
 
         for (int i = 0; i < n_kt && ok; ++i) {
             const int sl = i & 1, kt = kt_lo + i;
@@ -342,7 +358,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                          desc_kmajor(k_addr + (k >> 2) * BN * 128 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
                 umma_commit(bar_s + (j & 1));
             };
-            bool ok = true;
+            bool ok = mbar_wait(bar_q, 0, abort_flag, A.status, 11, true);
             for (int j = 0; j < 2 && j < n_kt && ok; ++j) {
                 ok = mbar_wait(bar_k + j, 0, abort_flag, A.status, 5, true);
                 if (!ok) break;
@@ -371,24 +387,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
             }
         }
     } else {
-        // ------------------------------------------------------------ copies: warp 5 brings Q and K, warp 6 brings V,
+        // ------------------------------------------------------------ copies: warp 5 brings K, warp 6 brings V,
         // each up to two tiles ahead of the softmax
-        constexpr int CH = D / 8;
         int ps_shift = 0;
         while ((1 << ps_shift) < A.page_size) ++ps_shift;
         const size_t page_stride = (size_t)A.nkv * A.page_size * D;
         const bool is_k = warp == 5;
         const bf16* pages = (is_k ? A.k_pages : A.v_pages) + (size_t)kh * A.page_size * D;
-        if (is_k) {
-            for (int idx = lane; idx < BM * CH; idx += 32) {    // Q tile: row = (token, head of the group)
-                const int r = idx / CH, c = idx - r * CH;
-                const int R = row0 + r;
-                const bool valid = R < rows_total;
-                const bf16* src = A.q;
-                if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
-                cp_async16(sQ + swz(BM, r, c), src, valid);
-            }
-        }
         uint64_t* bar_free = is_k ? bar_s : bar_o;           // K slot: free once S(j-2) is complete; V slot: once P V(j-2) is
         uint64_t* bar_full = is_k ? bar_k : bar_v;
         const uint32_t tiles = is_k ? sK : sV;
@@ -428,7 +433,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
 // S with 64 keys, 63 for P V; two issuing threads reach the tensor core's rate).  Here a block takes 256
 // query rows as two tiles that share every K and V tile: eight softmax warps, two per scheduler; four MMA
 // issuers (S and P V of each tile); K and V as TMA boxes (one page of one KV head, 64 elements wide, 128-byte
-// swizzle) issued by one thread each.  Measured: 2,070 cycles a key tile for both query tiles, of which the
+// swizzle) issued by one thread each, from the block's first cycle on, while the softmax warps fetch their Q tile
+// (a copy warp fetching Q first cost every block 7 to 10 us before its first product).  Measured: 2,070 cycles a key tile for both query tiles, of which the
 // exponentials of 2 x 128 x 64 scores are 1,024 on the special-function unit.  Tensor memory: S[tile][2] at
 // columns 0..255, O[tile] behind them.
 constexpr int QT = 2;
@@ -499,7 +505,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (tid == 0) {
         for (int i = 0; i < 4; ++i) { mbar_init(bar_s + i, 1); mbar_init(bar_p + i, 128); mbar_init(bar_o + i, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar_k + i, 1); mbar_init(bar_v + i, 1); mbar_init(bar_kfree + i, 2); mbar_init(bar_vfree + i, 2); }
-        mbar_init(bar_q, 64);
+        mbar_init(bar_q, QT * BM);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -522,6 +528,20 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int n_mine = kt_last[t] - kt_first[t] + 1;   // <= 0: this tile has no rows
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
+        {   // the tile's Q rows, row = (token, head of the group), while the first K and V tiles are on their way
+            constexpr int CH = D / 8;
+            for (int idx = r; idx < BM * CH; idx += BM) {
+                const int qr = idx / CH, c = idx - qr * CH;
+                const int QR = row0[t] + qr;
+                const bool valid = QR < rows_total;
+                const bf16* src = A.q;
+                if (valid) src = A.q + (size_t)(qs + QR / g) * A.q_stride + (size_t)(kh * g + QR % g) * D + c * 8;
+                cp_async16(sQ + t * Q_BYTES + swz(BM, qr, c), src, valid);
+            }
+            cp_async_wait_all();
+            fence_async_proxy();
+            mbar_arrive(bar_q);
+        }
 
         for (int i = 0; i < n_mine && ok; ++i) {
             const int sl = i & 1, kt = kt_first[t] + i, bi = t * 2 + sl;
@@ -670,21 +690,8 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     } else {
-        // ------------------------------------------------------------ copies: warps 12 and 13 bring Q together, then
-        // one thread of warp 12 issues the TMA boxes of K, one of warp 13 those of V, up to two tiles ahead
-        constexpr int CH = D / 8;
-        for (int idx = tid - 12 * 32; idx < QT * BM * CH; idx += 64) {    // Q tiles: row = (token, head of the group)
-            const int t = idx / (BM * CH), rem = idx - t * (BM * CH);
-            const int r = rem / CH, c = rem - r * CH;
-            const int R = row0[t] + r;
-            const bool valid = R < rows_total;
-            const bf16* src = A.q;
-            if (valid) src = A.q + (size_t)(qs + R / g) * A.q_stride + (size_t)(kh * g + R % g) * D + c * 8;
-            cp_async16(sQ + t * Q_BYTES + swz(BM, r, c), src, valid);
-        }
-        cp_async_wait_all();
-        fence_async_proxy();
-        mbar_arrive(bar_q);
+        // ------------------------------------------------------------ copies: one thread of warp 12 issues the TMA
+        // boxes of K, one of warp 13 those of V, up to two tiles ahead (the softmax warps bring their own Q tile)
         if (lane == 0) {
             const bool is_k = warp == 12;
             const CUtensorMap* map = is_k ? &map_k : &map_v;
