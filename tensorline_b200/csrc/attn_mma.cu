@@ -484,7 +484,11 @@ constexpr int TMA_TILE_BYTES = BN * D * 2;                       // K or V of on
 constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
 constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
 constexpr int TMA_TAB_OFFSET = TMA_BAR_OFFSET + 128;             // room for 2 * DEC_STAGES barriers and a flag
-constexpr int TMA_DEC_THREADS = 160;                             // four compute warps and the copy warp
+#ifndef TL_TMA_COPY_WARPS
+#define TL_TMA_COPY_WARPS 2
+#endif
+constexpr int TMA_COPY_WARPS = TL_TMA_COPY_WARPS;
+constexpr int TMA_DEC_THREADS = 128 + 32 * TMA_COPY_WARPS;       // four compute warps and the copy warps
 static_assert(2 * DEC_STAGES * 8 + 8 <= 128, "the barrier area holds at most 7 stages");
 constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM) ? 1 : 0;
 static_assert(TMA_MERGE_OK == 1, "the stage buffers must hold the merge area");
@@ -544,13 +548,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int i = tid; i < n_stage * ppt; i += TMA_DEC_THREADS) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
     if (tid == 0) {
         for (int s_ = 0; s_ < DEC_STAGES; ++s_) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + s_)), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + s_)), "r"(TMA_COPY_WARPS));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(empty + s_)), "r"(4));
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid == 128) {                                      // the copy thread fetches the two descriptors meanwhile
+    if (tid == 128) {                                      // a copy thread fetches the two descriptors meanwhile
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
@@ -569,32 +573,32 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     __syncthreads();                                       // table copy and barriers are visible
 
-    // The copy warp: a thread needs about 90 cycles to issue one TMA copy, and a stage is 2 * (64 / page) * (D / 64)
-    // boxes (16 for pages of 16 tokens and head size 128), so the boxes of a stage are spread over the warp's
-    // lanes: one instruction issues them all.
-    auto issue_stage = [&](int st) {                       // whole warp: the stage's pages, K and V, D/64 boxes each
-        const int buf = st % DEC_STAGES;
-        unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
-        if (lane == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(full + buf)), "r"(2 * TMA_TILE_BYTES) : "memory");
-        __syncwarp();
+    // The copy warps: a TMA copy takes about 95 cycles to issue, whether the boxes of a stage come from one thread
+    // or from the lanes of one warp instruction, and a stage is 2 * (64 / page) * (D / 64) boxes (16 for pages of
+    // 16 tokens and head size 128: 1,550 cycles, more than the four compute warps need for the stage).  So the
+    // boxes are dealt out to TMA_COPY_WARPS warps, each with its own share of the stage's bytes on the barrier.
+    if (warp >= 4) {
+        const int w = warp - 4;
         constexpr int DB = D / 64;
-        const int per_tensor = ppt * DB;
-        for (int idx = lane; idx < 2 * per_tensor; idx += 32) {
-            const int is_v = idx >= per_tensor, rem = idx - is_v * per_tensor;
-            const int pg = rem / DB, db = rem - pg * DB;
-            const int row = (stab[st * ppt + pg] * A.nkv + kh) * A.page_size;
-            const uint32_t dst = smem_u32(kt + is_v * TMA_TILE_BYTES + db * (BN * 128) + pg * A.page_size * 128);
-            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                         ::"r"(dst), "l"(is_v ? &map_v : &map_k), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
-        }
-    };
-    if (warp == 4) {
-        // ------------------------------------------------------------ the copy warp keeps the ring full
+        const int per_tensor = ppt * DB, total = 2 * per_tensor;
+        const int mine = (total - w + TMA_COPY_WARPS - 1) / TMA_COPY_WARPS;       // boxes w, w + TMA_COPY_WARPS, ...
+        const uint32_t box_bytes = (uint32_t)A.page_size * 128u;
         for (int st = 0; st < n_stage; ++st) {
-            if (st >= DEC_STAGES &&
-                !mbar_wait_tma(empty + st % DEC_STAGES, ((st / DEC_STAGES) - 1) & 1, abort_flag, status)) break;
-            issue_stage(st);
+            const int buf = st % DEC_STAGES;
+            if (st >= DEC_STAGES && !mbar_wait_tma(empty + buf, ((st / DEC_STAGES) - 1) & 1, abort_flag, status)) break;
+            unsigned char* kt = tiles + buf * 2 * TMA_TILE_BYTES;
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(full + buf)), "r"(mine * box_bytes) : "memory");
+            __syncwarp();
+            for (int k = lane; k < mine; k += 32) {
+                const int idx = w + k * TMA_COPY_WARPS;
+                const int is_v = idx >= per_tensor, rem = idx - is_v * per_tensor;
+                const int pg = rem / DB, db = rem - pg * DB;
+                const int row = (stab[st * ppt + pg] * A.nkv + kh) * A.page_size;
+                const uint32_t dst = smem_u32(kt + is_v * TMA_TILE_BYTES + db * (BN * 128) + pg * A.page_size * 128);
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                             ::"r"(dst), "l"(is_v ? &map_v : &map_k), "r"(smem_u32(full + buf)), "r"(db * 64), "r"(row) : "memory");
+            }
         }
         __syncthreads();                                   // meets the compute warps after their last stage
         __syncthreads();                                   // and after they have laid out their partial results
