@@ -23,7 +23,7 @@ import torch
 
 from ..cache import CacheManager, PagedKV
 from ..config.engine import EngineConfig
-from ..models import load_config, load_model, build_model
+from ..models import build_model, load_model
 from ..parts import Runtime
 from ..sampling import GenStats, Sampler, SamplingParams, request_seed
 from .runner import ModelRunner, StepEntry

@@ -17,7 +17,7 @@ from ..config.qwen2 import Qwen2Config
 from ..parts import Runtime
 from ..weights import load_weights
 from .qwen2 import describe_qwen2
-from .spec import Model, ModelSpec
+from .spec import Model
 
 
 @dataclass(frozen=True)

@@ -10,12 +10,11 @@ The cache manager is told one need per cache-owning entry.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 
-from ..parts import BLOCKS, NORMS, POSITION_ENCODINGS, Embedding, KVCacheView, LMHead, PartSpec, Runtime, StateView
-from ..cache import PagedKV, SlotState
+from ..parts import BLOCKS, NORMS, POSITION_ENCODINGS, Embedding, KVCacheView, LMHead, PartSpec, Runtime
 
 
 @dataclass(frozen=True)

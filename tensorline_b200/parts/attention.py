@@ -17,7 +17,7 @@ import torch
 
 from .. import ops
 from ..cache import PagedKV
-from .base import MIXERS, POSITION_ENCODINGS, Part, PartSpec, Runtime, TensorSpec, register_mixer
+from .base import POSITION_ENCODINGS, Part, PartSpec, Runtime, TensorSpec, register_mixer
 from .linear import SplitSum, matmul
 
 
