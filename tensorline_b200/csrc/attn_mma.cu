@@ -520,6 +520,21 @@ __device__ __forceinline__ bool mbar_wait_tma(uint64_t* bar, uint32_t parity, vo
     }
 }
 
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The same shared-memory location in block `rank` of this cluster.
+__device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
+    uint64_t out;
+    asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"(reinterpret_cast<uint64_t>(p)), "r"(rank));
+    return reinterpret_cast<const float*>(out);
+}
+
+// CLUSTER: the blocks of one (request, KV head) - one per key range - form a thread-block cluster and merge their
+// partial results through distributed shared memory (every block finishes a slice of the head dimension), so
+// nothing goes through global memory and no combine kernel follows.  Needs 2 to 8 key ranges and at most 16
+// query heads per KV head (one row tile).  A block whose key range is empty takes part with weight zero.
+template <bool CLUSTER>
 __global__ void __launch_bounds__(TMA_DEC_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const AttnArgs A, int* status) {
@@ -538,9 +553,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int lo = A.window > 0 ? max(0, len - A.window) : 0;
     const int base = (lo / BN) * BN;
     const int k_begin = base + split * A.chunk;
-    if (k_begin >= len) return;
-    const int k_end = min(len, k_begin + A.chunk);
-    const int n_stage = (k_end - k_begin + BN - 1) / BN;
+    if (!CLUSTER && k_begin >= len) return;
+    const int k_end = max(k_begin, min(len, k_begin + A.chunk));
+    const int n_stage = (k_end - k_begin + BN - 1) / BN;  // 0: an empty range (CLUSTER only)
     const int* gtab = A.table + (size_t)A.slots[b] * A.max_pages;
     const int qrow = A.q_start[b];
     const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
@@ -602,6 +617,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         __syncthreads();                                   // meets the compute warps after their last stage
         __syncthreads();                                   // and after they have laid out their partial results
+        if (CLUSTER) { cluster_barrier(); cluster_barrier(); }
         return;
     }
     cp_async_wait<0>();
@@ -653,10 +669,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + buf)) : "memory");
     }
     __syncthreads();                                       // the stage buffers become the merge area
-    if (*abort_flag) { __syncthreads(); return; }
+    if (*abort_flag) {
+        __syncthreads();
+        if (CLUSTER) { cluster_barrier(); cluster_barrier(); }     // the others must not wait for this block for ever
+        return;
+    }
 
     float* mO = reinterpret_cast<float*>(tiles);           // [4][16][D]
     float* mML = mO + 4 * 16 * D;                          // [4][16][2]
+    float* bO = mML + 4 * 16 * 2;                          // [16][D]   the block's own result, read by its cluster
+    float* bML = bO + 16 * D;                              // [16][2]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float lr = l[r];
@@ -687,13 +709,45 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             lt += f * mML[(w * 16 + row) * 2 + 1];
         }
         const int head = kh * g + hg;
-        if (A.splits == 1) {
+        if (CLUSTER) {
+            bO[row * D + col] = acc;
+            if (col == 0) { bML[row * 2] = mm; bML[row * 2 + 1] = lt; }
+        } else if (A.splits == 1) {
             A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
         } else {
             const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
             A.part_o[pi * D + col] = acc;
             if (col == 0) { A.part_ml[pi * 2] = mm; A.part_ml[pi * 2 + 1] = lt; }
         }
+    }
+    if (CLUSTER) {
+        cluster_barrier();                                 // every block's result is in its shared memory
+        const int ns = A.splits, cpc = (D + ns - 1) / ns;  // this block finishes columns [split * cpc, + cpc)
+        for (int idx = tid; idx < g * cpc; idx += 128) {
+            const int row = idx / cpc, col = split * cpc + (idx - row * cpc);
+            if (col >= D) continue;
+            float ms[8], ls[8], os[8];
+            float mm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                if (sp < ns) {
+                    const float2 ml = *reinterpret_cast<const float2*>(cluster_peer(bML + row * 2, sp));
+                    ms[sp] = ml.x; ls[sp] = ml.y;
+                    os[sp] = *cluster_peer(bO + row * D + col, sp);
+                    mm = fmaxf(mm, ml.x);
+                }
+            }
+            float acc = 0.f, lt = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                if (sp < ns) {
+                    const float f = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - mm);
+                    acc += f * os[sp]; lt += f * ls[sp];
+                }
+            }
+            A.out[((size_t)qrow * A.nq + kh * g + row) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+        }
+        cluster_barrier();                                 // nobody leaves while its shared memory is still read
     }
 }
 #endif  // HEAD_DIM % 64 == 0
@@ -866,11 +920,13 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
                                  long long total_pages, const int* table, int max_pages, int page_size,
                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
                                  int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
-                                 int* status, cudaStream_t stream) {
+                                 int* status, int cluster_merge, cudaStream_t stream) {
 #if HEAD_DIM % 64 == 0
     if (B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
-    if (nq % nkv || chunk % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return 1;
+    // cluster_merge: the key ranges of a (request, KV head) merge inside a thread-block cluster, no partials needed
+    if (cluster_merge && (splits < 2 || splits > 8 || nq / (nkv > 0 ? nkv : 1) > 16)) return 1;
+    if (nq % nkv || chunk % BN || splits < 1 || (splits > 1 && !cluster_merge && (!part_o || !part_ml))) return 1;
     if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
     if (!g_encode) {
         void* fn = nullptr;
@@ -883,8 +939,11 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     if (tab_entries > DECODE_MAX_TAB) return 1;
     const int smem = TMA_TAB_OFFSET + tab_entries * 4 + 1024;
     if (!g_tma_attr_done) {
-        cudaError_t ce = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t ce = cudaFuncSetAttribute(attn_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
+        if (ce == cudaSuccess)
+            ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
         if (ce != cudaSuccess) return (int)ce;
         g_tma_attr_done = true;
     }
@@ -904,7 +963,20 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
-    e = launch_after_wait(attn_decode_tma_kernel, grid, dim3(TMA_DEC_THREADS), (size_t)smem, stream, mk, mv, A, status);
+    if (cluster_merge) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(TMA_DEC_THREADS); cfg.dynamicSmemBytes = (size_t)smem; cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = tl_dependent_launch_enabled() ? 2 : 1;
+        const cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_tma_kernel<true>, mk, mv, A, status);
+        return ce != cudaSuccess ? (int)ce : tl_launch_status();
+    }
+    e = launch_after_wait(attn_decode_tma_kernel<false>, grid, dim3(TMA_DEC_THREADS), (size_t)smem, stream, mk, mv, A, status);
     if (e || splits == 1) return e;
     dim3 cgrid(nq, B);
     return launch_after_wait(attn_combine_kernel, cgrid, dim3(D < 128 ? ((D + 31) / 32) * 32 : 128), 0, stream, A);

@@ -38,7 +38,7 @@ def attn_lib(head_dim: int):
         lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
         lib.tl_attn_decode.restype = ctypes.c_int
         lib.tl_attn_decode_tma.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
-                                           _F, _I, _I, _P, _P, _P, _P]
+                                           _F, _I, _I, _P, _P, _P, _I, _P]
         lib.tl_attn_decode_tma.restype = ctypes.c_int
         _libs[head_dim] = lib
     return lib
@@ -148,31 +148,38 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
 
 
 TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.async loads only (A/B timing)
+CLUSTER_MERGE = os.environ.get("TENSORLINE_B200_CLUSTER_MERGE", "1") != "0"   # 0: partials + combine kernel (A/B timing)
 
 
 def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
-           nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None, tma: bool | None = None) -> None:
+           nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None, tma: bool | None = None,
+           cluster: bool | None = None) -> None:
     """Split-KV decode attention.  `tma`: load K and V by TMA (head sizes that are multiples of 64, pages of
-    8..64 tokens); None = wherever that applies."""
+    8..64 tokens); None = wherever that applies.  `cluster` (TMA path, 2..8 key ranges, groups of at most 16
+    heads): the ranges of a request merge inside a thread-block cluster, no partials, no second kernel;
+    None = wherever that applies."""
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
-    if splits > 1:
+    use_tma = (TMA_DECODE and B >= 4 if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
+    can_cluster = use_tma and 2 <= splits <= 8 and nq // nkv <= 16
+    use_cluster = can_cluster and (CLUSTER_MERGE if cluster is None else cluster)
+    if splits > 1 and not use_cluster:
         if part_o is None or part_o.numel() < B * nq * splits * d or part_o.dtype != torch.float32:
             raise KernelError("attn_decode: part_o must be float32 [B, nq, splits, d]")
         if part_ml is None or part_ml.numel() < B * nq * splits * 2 or part_ml.dtype != torch.float32:
             raise KernelError("attn_decode: part_ml must be float32 [B, nq, splits, 2]")
     # measured at 7B sizes: TMA loads win from about four requests on (5.8 against 5.4 TB/s at batch 64);
     # below that the launch is too short for the difference to show and the tensor-map set-up costs a little
-    use_tma = (TMA_DECODE and B >= 4 if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
     if use_tma:
         from .ops_gemm import status_word
         rc = attn_lib(d).tl_attn_decode_tma(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), chunk, splits,
-                                            _ptr(part_o) if splits > 1 else None, _ptr(part_ml) if splits > 1 else None,
-                                            _ptr(status_word(q.device)), _stream())
+                                            _ptr(part_o) if splits > 1 and not use_cluster else None,
+                                            _ptr(part_ml) if splits > 1 and not use_cluster else None,
+                                            _ptr(status_word(q.device)), int(use_cluster), _stream())
         if rc != 2:                                    # 2: this build or these sizes do not take the TMA path
-            _check(rc, "attn_decode_tma", launches=2 if splits > 1 else 1)
+            _check(rc, "attn_decode_tma", launches=2 if splits > 1 and not use_cluster else 1)
             return
     _check(attn_lib(d).tl_attn_decode(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                       table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,

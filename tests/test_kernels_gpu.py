@@ -337,10 +337,12 @@ def test_paged_attention(case, kernel):
                 po = torch.full((B, nq, splits, d), float("nan"), device="cuda")
                 pml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")
                 out.zero_()
-                for tma in (False, True):             # K, V by cp.async, or by TMA where the sizes allow it
+                # K, V by cp.async, or by TMA where the sizes allow it; with TMA, the ranges merged by a second
+                # kernel or (2..8 ranges, groups of up to 16 heads) inside a thread-block cluster
+                for tma, cluster in ((False, False), (True, False), (True, True)):
                     out.zero_()
-                    ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml, tma=tma)
-                    assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits, tma {tma}", **BF16)
+                    ops_attention.decode(*args, B, nq, nkv, d, window, scale, chunk, splits, po, pml, tma=tma, cluster=cluster)
+                    assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits, tma {tma}, cluster {cluster}", **BF16)
             out.zero_()
         ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale)
     assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))
@@ -383,12 +385,12 @@ def test_attention_over_a_long_context(window):
         splits = -(-tiles * 64 // chunk)
         po = torch.full((1, nq, splits, d), float("nan"), device="cuda")
         pml = torch.full((1, nq, splits, 2), float("nan"), device="cuda")
-        for tma in (False, True):
+        for tma, cluster in ((False, False), (True, False), (True, True)):
             out = torch.zeros(1, nq * d, dtype=torch.bfloat16, device="cuda")
             ops_attention.decode(q1, nq * d, out, kd, vd, table, ps, i32([0]), i32([last]), slots, 1, nq, nkv, d, window, scale,
-                                 chunk, splits, po, pml, tma=tma)
+                                 chunk, splits, po, pml, tma=tma, cluster=cluster)
             ops_gemm.check_status()
-            assert_close(out.view(1, nq, d), want1, f"decode over a long cache, {splits} ranges, tma {tma}", **BF16)
+            assert_close(out.view(1, nq, d), want1, f"decode over a long cache, {splits} ranges, tma {tma}, cluster {cluster}", **BF16)
 
 
 def test_attention_refuses_unsupported_head_size():
