@@ -521,7 +521,7 @@ __device__ __forceinline__ bool mbar_wait_tma(uint64_t* bar, uint32_t parity, vo
 }
 
 __device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");   // not .aligned: lanes of a warp may arrive apart
 }
 // The same shared-memory location in block `rank` of this cluster.
 __device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {

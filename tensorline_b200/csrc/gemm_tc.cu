@@ -94,6 +94,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");   // not .aligned: lanes of a warp may arrive apart
+}
+// The same shared-memory location in block `rank` of this cluster.
+__device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
+    uint64_t out;
+    asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"(reinterpret_cast<uint64_t>(p)), "r"(rank));
+    return reinterpret_cast<const float*>(out);
+}
+
 struct GemmArgs {
     void* out;            // bf16 or float [rows, ldo]
     float* partial;       // [splits, RB or RA rows..] float, when splits > 1
@@ -104,6 +114,8 @@ struct GemmArgs {
     int out_f32;
     int* status;
     int* counters;        // one per output tile, zero between calls: the last block of a tile to finish sums the partials
+    int cluster_reduce;   // the K ranges of a tile are a thread-block cluster (grid z) and sum their tiles through
+                          // distributed shared memory: no pieces in global memory (swap = 1, 2..8 ranges)
     int gated;            // swap, one split: rows 0..63 of every 128-row tile of A are gate features, rows 64..127 the
                           // up features of the same 64 columns; out[b, 64 tile + j] = silu(gate) * up, [RB, RA / 2]
 };
@@ -201,7 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
                 tmem_ld16(taddr + c0, r);
-                if (a >= G.RA && !G.gated) continue;
+                if (a >= G.RA && !G.gated && !G.cluster_reduce) continue;
                 if (G.gated) {
                     // The up half (TMEM lanes 64..127) hands its values over through shared memory (the tile ring is
                     // idle by now); the gate half rounds both to bfloat16 as a stored gate|up product would have
@@ -228,6 +240,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");                   // `hand` is free for the next 16 tokens
+                    continue;
+                }
+                if (G.cluster_reduce) {                  // [token][128 rows of A] floats in the idle tile ring
+                    float* red = reinterpret_cast<float*>(tiles);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) red[(c0 + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
                     continue;
                 }
                 if (gridDim.z > 1) {                     // float partial, laid out like the output
@@ -302,6 +320,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
+    if (G.cluster_reduce) {
+        // Every block of the cluster (one per K range of this tile) has laid its accumulator out in its shared
+        // memory; block z now sums a z-th share of the tile over all blocks, in range order, and stores it.
+        cluster_barrier();
+        if (warp >= 2 && !*abort_flag) {
+            const float* red = reinterpret_cast<const float*>(tiles);
+            const int nz = (int)gridDim.z, ntok = min(BN, G.RB - b0);
+            const int total = ntok * BM, share = (((total + nz - 1) / nz) + 3) & ~3;
+            const int lo = split * share, hi = min(total, lo + share);
+            for (int idx = lo + (int)threadIdx.x - 64; idx < hi; idx += 128) {
+                float acc = 0.f;
+                for (int z = 0; z < nz; ++z) acc += *cluster_peer(red + idx, z);
+                const int tok = idx / BM, a = a0 + (idx - tok * BM);
+                if (a < G.RA) {
+                    const size_t o = (size_t)(b0 + tok) * G.ldo + a;
+                    if (G.out_f32) ((float*)G.out)[o] = acc;
+                    else ((bf16*)G.out)[o] = __float2bfloat16_rn(acc);
+                }
+            }
+        }
+        cluster_barrier();                               // nobody leaves while its shared memory is still read
+    }
     // ---------------------------------------------------------------- teardown
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -366,6 +406,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
+    if (G.cluster_reduce) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = grid.z;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = tl_dependent_launch_enabled() ? 2 : 1;
+        const cudaError_t ce = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, ma, mb, G);
+        return ce != cudaSuccess ? (int)ce : tl_launch_status();
+    }
     return launch_after_wait(gemm_tc_kernel<BN, STAGES>, grid, dim3(THREADS), SMEM, stream, ma, mb, G);
 }
 
@@ -376,13 +429,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
 // (splits * T * N floats); with `counters` (n_counters zeroed ints, at least one per tile, left zeroed) the
 // last block of a tile sums the partials inside the same launch, else a second kernel does.  `status` (device int, zero before
 // the call) receives a non-zero code if a wait inside the kernel ran out.  `gated` (swap = 1, one split, N % 128 == 0, bfloat16 out):
-// w holds gate and up rows interleaved in blocks of 64 and y [T, N / 2] receives silu(gate) * up.
+// w holds gate and up rows interleaved in blocks of 64 and y [T, N / 2] receives silu(gate) * up.  `cluster_reduce` (swap = 1,
+// 2..8 ranges): the ranges of a tile are a thread-block cluster and sum their tiles through distributed shared memory.
 TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
                          int bn, int splits, float* partial, int* status, int* counters, int n_counters,
-                         int gated, cudaStream_t stream) {
+                         int gated, int cluster_reduce, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
-    if (splits < 1 || (splits > 1 && partial == nullptr)) return 1;
+    if (splits < 1 || (splits > 1 && partial == nullptr && !cluster_reduce)) return 1;
     int e = get_encode();
     if (e) return e;
     const void* a = swap ? w : x;
@@ -399,6 +453,8 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     if (gated && (!swap || splits != 1 || out_f32 || (N & 127) || y == nullptr)) return 1;   // whole 64 + 64 tiles, one split
     GemmArgs G{};
     G.gated = gated;
+    G.cluster_reduce = (cluster_reduce && splits >= 2) ? 1 : 0;
+    if (cluster_reduce && (!swap || splits > 8 || y == nullptr)) return 1;
     G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
     dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);
@@ -412,7 +468,7 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
         case 256: e = launch<256, 4>(ma, mb, G, grid, stream); break;
         default: return 1;
     }
-    if (e || splits == 1 || G.counters != nullptr || y == nullptr) return e;      // y null: the caller sums the pieces
+    if (e || splits == 1 || G.counters != nullptr || y == nullptr || G.cluster_reduce) return e;      // y null: the caller sums the pieces
     const size_t total = (size_t)T * N;
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (void*)y, out_f32, splits, T, N, ldo);

@@ -12,6 +12,7 @@ tokens on, so it is off by default).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -28,7 +29,7 @@ def lib():
     global _lib
     if _lib is None:
         l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
-        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _P]
+        l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _P]
         l.tl_gemm_tc.restype = ctypes.c_int
         l.tl_splitk_reduce.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
         l.tl_splitk_reduce.restype = ctypes.c_int
@@ -37,6 +38,8 @@ def lib():
 
 
 N_COUNTERS = 8192
+CLUSTER_MAX = 8                # portable cluster size
+CLUSTER_REDUCE = os.environ.get("TENSORLINE_B200_CLUSTER_REDUCE", "1") != "0"   # 0: pieces + a summing pass (A/B timing)
 
 
 def status_word(device) -> torch.Tensor:
@@ -67,15 +70,19 @@ def plan(T: int, N: int, K: int) -> tuple:
         splits = 1
         if tiles < NUM_SMS:                           # too few tiles to give every SM a block: split K so that
             splits = max(1, min(k_tiles // 4, (2 * NUM_SMS - 40) // tiles))   # one round of blocks is nearly full
+            if CLUSTER_REDUCE and splits > CLUSTER_MAX:
+                splits = CLUSTER_MAX                  # the ranges of a tile then sum inside a thread-block cluster
         return 1, bn, splits
     return 0, 128 if N <= 4096 else 256, 1
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
             splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False, pieces: bool = False,
-            gated: bool = False):
-    """x [T, K] times w [N, K]^T.  `pieces`: when the plan splits K, return the float32 pieces
-    [S, T, N] unsummed (for a consumer that adds them up itself) instead of the product.
+            gated: bool = False, cluster: bool | None = None):
+    """x [T, K] times w [N, K]^T.  With 2..8 K ranges (few-token order) the ranges of a tile form a
+    thread-block cluster and sum through distributed shared memory (`cluster`; None = wherever it
+    applies).  `pieces`: when K is split otherwise, return the float32 pieces [S, T, N] unsummed (for a
+    consumer that adds them up itself) instead of the product.
     `gated`: w holds gate and up rows interleaved in blocks of 64 (N % 128 == 0); the result is
     silu(gate) * up, [T, N / 2] bfloat16, formed in the epilogue (few tokens, one split only:
     check `can_gate` first)."""
@@ -95,7 +102,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     splits = p_splits if splits is None else splits
     k_tiles = -(-K // 64)
     splits = -(-k_tiles // -(-k_tiles // min(splits, k_tiles)))          # as the kernel rounds it: no empty split
-    pieces = pieces and splits > 1 and not fused_reduce
+    use_cluster = (CLUSTER_REDUCE if cluster is None else cluster) and swap and 2 <= splits <= CLUSTER_MAX and not fused_reduce
+    pieces = pieces and splits > 1 and not fused_reduce and not use_cluster
     if gated:
         if not swap or splits != 1 or N % 128 or out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: the gated epilogue needs the few-token order, one split, N % 128 == 0, bfloat16")
@@ -109,12 +117,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
         out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     elif out.shape != (T, N) or out.dtype != out_dtype or out.stride(1) != 1:
         raise KernelError("gemm_tc: out must be [T, N] of the output type with unit inner stride")
-    partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 and not use_cluster else None
     st = status_word(x.device)
     _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), N if pieces else out.stride(0),
                             T, N, K, swap, bn, splits, _ptr(partial), _ptr(st),
-                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, int(gated), _stream()),
-           "gemm_tc", launches=1 if (splits == 1 or fused_reduce or pieces) else 2)
+                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, int(gated), int(use_cluster), _stream()),
+           "gemm_tc", launches=1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2)
     return partial if pieces else out
 
 

@@ -411,7 +411,8 @@ TC_CASES = [  # tokens, N, K, forced (swap, bn, splits) or None for the launcher
 @pytest.mark.parametrize("fused", [False, True])
 def test_tcgen05_matrix_product(case, fused):
     """The tensor-memory kernel against float64: both operand orders, ragged edges in every dimension,
-    K split across blocks with either way of summing the partials, float32 and bfloat16 outputs."""
+    K split across blocks with every way of summing the partials (a thread-block cluster, the last block, a
+    second kernel), float32 and bfloat16 outputs."""
     from tensorline_b200 import ops_gemm
     T, N, K, forced = case
     x = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
@@ -421,6 +422,8 @@ def test_tcgen05_matrix_product(case, fused):
     y32 = ops_gemm.gemm_tc(x, w, torch.float32, fused_reduce=fused, **kw)
     y16 = ops_gemm.gemm_tc(x, w, torch.bfloat16, fused_reduce=fused, **kw)
     ops_gemm.check_status()
+    if not fused:                                          # K ranges summed by a second kernel instead of a cluster
+        assert torch.equal(y32, ops_gemm.gemm_tc(x, w, torch.float32, cluster=False, **kw))
     assert_close(y32, want, "float32 out", rtol=1e-4, atol=1e-4 * float(want.abs().max()))
     assert_close(y16, want, "bfloat16 out", rtol=1e-2, atol=1e-2 * float(want.abs().max()))
     assert int(ops_gemm.status_word(x.device)[1:].abs().sum()) == 0          # arrival counters are back at zero
@@ -435,10 +438,14 @@ def test_split_product_summed_inside_the_norm(rows):
     T, N, K, eps = 5, 264, 2056, 1e-5
     a = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
     w = rnd(N, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()
-    pieces = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4, pieces=True)
+    pieces = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4, pieces=True, cluster=False)
     assert pieces.shape == (4, T, N) and pieces.dtype == torch.float32
-    whole = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4)
+    whole = ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4, cluster=False)
     assert torch.equal(resolve(SplitSum(pieces, torch.bfloat16)), whole)
+    # the same four ranges summed inside a thread-block cluster: the same additions in the same order
+    assert torch.equal(ops_gemm.gemm_tc(a, w, swap=1, bn=16, splits=4, pieces=True, cluster=True), whole)
+    assert torch.equal(ops_gemm.gemm_tc(a, w, torch.float32, swap=1, bn=16, splits=4, cluster=True),
+                       ops_gemm.gemm_tc(a, w, torch.float32, swap=1, bn=16, splits=4, cluster=False))
     assert_close(whole, a.double() @ w.double().T, "product", rtol=1e-2, atol=1e-2)
     x = rnd(T, N, seed=3, scale=2.0).cuda()
     nw = (1 + rnd(N, seed=4, scale=0.3)).to(torch.bfloat16).cuda()
