@@ -95,6 +95,38 @@ def test_bfloat16_greedy_tokens_follow_the_plain_model_where_it_is_decided(tiny_
     assert compared >= 4
 
 
+def test_bfloat16_engine_at_head_size_128_with_graphs_and_without(tmp_path):
+    """Head size 128 in groups of 7, pages of 16, six requests: the decode steps take the TMA attention with the
+    merge inside clusters, captured in CUDA graphs with dependent launches and overlapped scheduling.  The same
+    engine without graphs must give the same tokens, and both follow the plain model where it is decided."""
+    from tests.gpu_helpers import BF16_MODEL_REL
+    folder = write_tiny("C", tmp_path / "c")
+    plain = PlainQwen2(folder)
+    V = CONFIGS["C"]["vocab_size"]
+    prompts = [random_tokens(V, n, seed=70 + n) for n in (3, 150, 47, 66, 80, 34)]
+    outs = {}
+    for graphs in (True, False):
+        eng = engine(folder, dtype="bfloat16", block_size=PAGE_SIZE["C"], num_blocks=96, max_model_len=512,
+                     cuda_graphs=graphs, overlap=graphs)
+        outs[graphs] = [o.token_ids for o in eng.generate(prompts, params(12))]
+        st = eng.stats()
+        assert st["free_pages"] == st["num_pages"]
+        assert (st["graph_replays"] > 0) == graphs
+    assert outs[True] == outs[False]
+    compared = 0
+    for p, toks in zip(prompts, outs[True]):
+        seq = list(p)
+        for tok in toks:
+            logits = forward(plain, seq)[-1]
+            top = torch.topk(logits, 2).values
+            if float(top[0] - top[1]) <= 2 * BF16_MODEL_REL * float(logits.abs().max()):
+                break
+            assert tok == int(logits.argmax())
+            compared += 1
+            seq.append(tok)
+    assert compared >= 12
+
+
 def test_request_that_does_not_fit_fails_and_others_go_on(tiny_a):
     from tensorline_b200.engine import RequestDoesNotFit
     folder, prompts, want = tiny_a
