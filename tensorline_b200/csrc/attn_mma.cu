@@ -236,11 +236,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     bf16* sK = sQ + BM * DP;                               // [2][BN][DP]
     bf16* sV = sK + 2 * BN * DP;                           // [2][BN][DP]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int kh = blockIdx.y, g = A.nq / A.nkv;
+    const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
 
     // Blocks are handed out in index order and a tile's work grows with its position in the request
     // (causal), so the tiles are taken from the end: the longest ones start first.
-    int tile = gridDim.x - 1 - blockIdx.x, b = 0;
+    int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;
     for (; b < A.B; ++b) {
         const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
         if (tile < nt) break;
@@ -855,7 +855,7 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
-    dim3 grid(total_tiles, nkv);
+    dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     if (page_size <= 32) attn_prefill_kernel<32><<<grid, 128, prefill_smem<32>(), stream>>>(A);
     else                 attn_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(A);
     return tl_launch_status();

@@ -195,9 +195,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kh = blockIdx.y, g = A.nq / A.nkv;
+    const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
 
-    int tile = gridDim.x - 1 - blockIdx.x, b = 0;          // longest tiles (late rows of a request) first
+    int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
     for (; b < A.B; ++b) {
         const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
         if (tile < nt) break;
@@ -472,9 +472,9 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kh = blockIdx.y, g = A.nq / A.nkv;
+    const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
 
-    int tile = gridDim.x - 1 - blockIdx.x, b = 0;          // longest tiles (late rows of a request) first
+    int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
     for (; b < A.B; ++b) {
         const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + QT * BM - 1) / (QT * BM);
         if (tile < nt) break;
@@ -780,7 +780,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status;
-    dim3 grid(total_tiles, nkv);
+    dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(A);
     return tl_launch_status();
 }
@@ -820,7 +820,7 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status;
-    dim3 grid(total_tiles, nkv);
+    dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
     return tl_launch_status();
 #else

@@ -211,8 +211,8 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
         # Two query tiles a block pay once its blocks (one per SM) fill the GPU; below that the single-tile
-        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 65 against 76 us,
-        # 4,096 154 against 231 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 82 against 72 us)
+        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 50 against 76 us,
+        # 4,096 152 against 230 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 84 against 70 us)
         pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * (nq // nkv) // (2 * TC_QUERY_TILE)) for i in range(ctx.B))
         if use_tc and TC_PAIR and pairs * nkv >= NUM_SMS and prefill_tc_pair(*args):
             return
