@@ -98,7 +98,7 @@ def test_long_prompt_takes_the_two_tile_attention_and_agrees_with_the_other_kern
     pair = prompt("pair")
     assert ops.launch_count() > before
     g = cfg.num_attention_heads // cfg.num_key_value_heads
-    assert -(-n * g // 256) * cfg.num_key_value_heads >= ops_attention.NUM_SMS      # the two-tile kernel did run
+    assert -(-n * g // 256) * cfg.num_key_value_heads >= 0.7 * ops_attention.NUM_SMS      # the two-tile kernel did run
     decoded = [runner.step([StepEntry("pair", [ids[n + i]], [0])]).double().cpu()[0] for i in range(extra) if cache.grow("pair", n + i, n + i + 1)]
     cache.release("pair"); runner.end_request("pair")
     ops_attention.TC_PAIR = False
