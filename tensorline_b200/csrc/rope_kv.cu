@@ -49,6 +49,17 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
     }
 }
 
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 x = *reinterpret_cast<const float4*>(p), y = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { v[2 * k] = __low2float(h[k]); v[2 * k + 1] = __high2float(h[k]); }
+}
+
 // The bfloat16 fast path (full rotary, d % 16 == 0): one block per token; the token's d/2 cosines and
 // sines are computed once into shared memory and shared by all heads; each thread moves 8 + 8 values
 // (two 16-byte loads, two 16-byte stores).  Same arithmetic as the kernel above.
@@ -109,12 +120,12 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
                 b[2 * k] = __low2float(b2[k]); b[2 * k + 1] = __high2float(b2[k]);
             }
         }
-        if (bias) {
+        if (bias) {                                      // 8 + 8 consecutive values: vector loads (i0 and d are multiples of 8)
+            float ba[8], bb[8];
+            load8(bias + hh * d + i0, ba);
+            load8(bias + hh * d + half + i0, bb);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                a[k] += to_f<TW>(bias[hh * d + i0 + k]);
-                b[k] += to_f<TW>(bias[hh * d + half + i0 + k]);
-            }
+            for (int k = 0; k < 8; ++k) { a[k] += ba[k]; b[k] += bb[k]; }
         }
         if (hh < nq + nkv) {
 #pragma unroll
@@ -152,7 +163,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
     const int heads = write_kv ? nq + 2 * nkv : nq;
     if (heads > 65535) return 1;
-    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)pieces) & 15) == 0);
+    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)pieces | (uintptr_t)bias) & 15) == 0);
     if (pieces && !(act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned)) return 1;   // pieces: the fast path only
     if (act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned) {
         const int items = heads * (d / 16);
