@@ -25,7 +25,7 @@ from ..cache import CacheManager, PagedKV
 from ..config.engine import EngineConfig
 from ..models import build_model, load_model
 from ..parts import Runtime
-from ..sampling import GenStats, Sampler, SamplingParams, request_seed
+from ..sampling import GenStats, Sampler, SamplingParams, draw_rows, request_seed
 from .runner import ModelRunner, StepEntry
 from .scheduler import Request, Scheduler
 
@@ -98,8 +98,8 @@ class Engine:
         eos = self.model.spec.eos_token_id
         self.default_stops = {eos} if eos is not None else set()     # tensorline/engine.py:76-77
         self._known_to_runner: set = set()
-        # Overlap (tensorline/batch_engine.py:478-533): in steady greedy decoding the next step is launched
-        # from the tokens still on the device before the previous step's tokens are read back.
+        # Overlap (tensorline/batch_engine.py:478-533): in steady decoding the next step is launched from the
+        # tokens still on the device before the previous step's tokens are read back.
         self.overlap = bool(o.overlap and o.cuda_graphs)
         self._inflight = None                            # (requests, DecodeHandle) of the step not yet read back
         self.overlapped_steps = 0
@@ -135,7 +135,9 @@ class Engine:
     def _launch(self, reqs, prev=None):
         """Start a decode step for `reqs` without waiting for its tokens."""
         entries = [StepEntry(r.rid, [r.tokens[-1] if prev is None else 0], [0]) for r in reqs]
-        handle = self.runner.launch_decode(entries, None if prev is None else prev[1])
+        ahead = 0 if prev is None else 1                 # the step in flight has one token of each request still to come
+        draw = draw_rows([(r.params, r.seed, r.num_generated + ahead) for r in reqs])
+        handle = self.runner.launch_decode(entries, None if prev is None else prev[1], draw)
         self.scheduler.computed([(r, 1) for r in reqs])
         return reqs, handle
 
@@ -154,15 +156,16 @@ class Engine:
 
     def _can_continue(self) -> bool:
         """Whether the step after the one in flight can be launched before that one is read back
-        (tensorline/batch_engine.py:510-521): same requests, all greedy, nobody near a limit, a page
-        for one more token each."""
+        (tensorline/batch_engine.py:510-521): same requests, nobody near a limit, a page for one more
+        token each.  tzar-beep/Tensorline also asks for greedy requests; here sampled ones go on as well:
+        a draw's uniform number depends on (seed, token index) only, so it is known a step ahead, and the
+        sampling kernel runs on the device behind the decode graph."""
         reqs = self._inflight[0]
         sch = self.scheduler
         if sch.waiting or len(sch.running) != len(reqs) or any(a is not b for a, b in zip(sch.running, reqs)):
             return False
         for r in reqs:      # the pending token is appended when the step is read back; leave room for one more
-            if (r.done or r.params.temperature > 0 or r.num_generated + 2 > r.params.max_tokens
-                    or len(r.tokens) + 2 > sch.max_model_len):
+            if r.done or r.num_generated + 2 > r.params.max_tokens or len(r.tokens) + 2 > sch.max_model_len:
                 return False
         return all(self.cache.grow(r.rid, r.num_computed, r.num_computed + 1) for r in reqs)
 
@@ -198,7 +201,7 @@ class Engine:
                 end = req.num_computed + n
                 want = [n - 1] if end == len(req.tokens) else []      # tensorline/batch_engine.py:376
                 entries.append(StepEntry(req.rid, req.tokens[req.num_computed:end], want))
-            if (self.overlap and all(r.params.temperature <= 0 for r, _ in plan) and self.runner.can_replay(entries)):
+            if self.overlap and self.runner.can_replay(entries):
                 self._inflight = self._launch([r for r, _ in plan])      # its tokens are read at the next call
                 return []
             sampled = [req for (req, n), e in zip(plan, entries) if e.want]

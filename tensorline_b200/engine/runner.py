@@ -109,6 +109,11 @@ class ModelRunner:
         self._graphable = all(isinstance(c, KVCacheView) for c in self.caches.values())
         self._token_hosts = [torch.zeros(cache.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._flip = 0
+        # temperature, top-p and uniform number per row for steps that sample on the device without waiting
+        self._draw_hosts = [torch.zeros(3, cache.max_num_seqs, dtype=torch.float32).pin_memory() for _ in range(4)]
+        self._draw_events = [None] * 4
+        self._draw_turn = 0
+        self._draw_dev = torch.zeros(3, cache.max_num_seqs, dtype=torch.float32, device=self.device)
 
     def _wait_for_table_copy(self) -> None:
         if self._table_event is not None:
@@ -291,13 +296,26 @@ class ModelRunner:
         return self._can_replay(list(entries))
 
     @torch.inference_mode()
-    def launch_decode(self, entries, ids_from=None):
-        """Replay the decode graph for `entries` and start copying its greedy tokens to the host without
-        waiting (tensorline/batch_engine.py:478-498).  `ids_from`: the handle of the previous launch of
-        the same requests in the same order; its tokens, still on the device, are this step's input ids."""
+    def launch_decode(self, entries, ids_from=None, draw=None):
+        """Replay the decode graph for `entries` and start copying its tokens to the host without waiting
+        (tensorline/batch_engine.py:478-498).  `ids_from`: the handle of the previous launch of the same
+        requests in the same order; its tokens, still on the device, are this step's input ids.  `draw`:
+        None (every row takes the graph's argmax) or (temperatures, top-p values, uniform numbers) per row:
+        the sampling kernel then runs behind the graph and its tokens take the place of the argmax."""
         entries = list(entries)
         n = len(entries)
         g = self._run_graph(entries, None if ids_from is None else ids_from.graph.tokens[:n])
+        if draw is not None:
+            turn = self._draw_turn = (self._draw_turn + 1) % len(self._draw_hosts)
+            if self._draw_events[turn] is not None:
+                self._draw_events[turn].synchronize()
+            host = self._draw_hosts[turn]
+            host[:, :n] = torch.tensor(draw, dtype=torch.float32)
+            self._draw_dev.copy_(host, non_blocking=True)
+            self._draw_events[turn] = torch.cuda.Event()
+            self._draw_events[turn].record()
+            d = self._draw_dev
+            ops.sample(g.logits[:n], d[0, :n], d[1, :n], d[2, :n], g.tokens[:n])
         self._flip ^= 1
         host = self._token_hosts[self._flip][:n]
         host.copy_(g.tokens[:n], non_blocking=True)

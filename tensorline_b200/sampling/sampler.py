@@ -31,6 +31,14 @@ def request_seed(engine_seed: int, rid: int, params: SamplingParams) -> int:
     return int.from_bytes(digest, "little") & 0x7FFFFFFFFFFFFFFF
 
 
+def draw_rows(rows: list):
+    """`rows`: one (params, seed, token_index) each.  None if every row is greedy, else the numbers the
+    sampling kernel needs, as three lists: temperatures, top-p values, uniform numbers."""
+    if all(p.temperature <= 0 for p, _, _ in rows):
+        return None
+    return ([p.temperature for p, _, _ in rows], [p.top_p for p, _, _ in rows], [uniform_for(s, i) for _, s, i in rows])
+
+
 class Sampler:
     def __init__(self, device):
         self.device = device
@@ -42,11 +50,10 @@ class Sampler:
         if R == 0:
             return []
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
-        if all(p.temperature <= 0 for p, _, _ in rows):
+        draw = draw_rows(rows)
+        if draw is None:
             ops.argmax(logits, out)
         else:
-            host = torch.tensor([[p.temperature for p, _, _ in rows], [p.top_p for p, _, _ in rows],
-                                 [uniform_for(s, i) for _, s, i in rows]], dtype=torch.float32)
-            dev = host.to(logits.device)
+            dev = torch.tensor(draw, dtype=torch.float32).to(logits.device)
             ops.sample(logits, dev[0], dev[1], dev[2], out)
         return out.tolist()

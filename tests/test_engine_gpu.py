@@ -206,3 +206,37 @@ def test_overlapped_decoding_equals_synchronous(tiny_a):
     assert results[True] == results[False]
     assert results[True][0][0] == want[0] and results[True][1][0] == want[1][:3]
     assert results[True][3][1] == "stop" and results[True][3][0] == want[3][:want[3].index(want[3][5])]
+
+
+def test_overlapped_decoding_with_sampled_requests_equals_synchronous(tiny_a):
+    """Sampled requests go on overlapped as well (a draw's uniform number is known a step ahead; the sampling
+    kernel runs behind the decode graph): greedy and seeded temperature / top-p requests side by side give the
+    same tokens with the overlap on and off, with a stop token and a length limit on the way."""
+    from tensorline_b200 import SamplingParams
+    folder, prompts, want = tiny_a
+    sampled = dict(temperature=0.9, top_p=0.85, ignore_eos=True)
+    results = {}
+    for overlap in (False, True):
+        eng = engine(folder, overlap=overlap)
+        sp = [SamplingParams(max_tokens=10, seed=7, **sampled), params(8),
+              SamplingParams(max_tokens=4, seed=8, **sampled), SamplingParams(max_tokens=9, seed=9, temperature=0.7, ignore_eos=True)]
+        reqs = [eng.add_request(p, s) for p, s in zip(prompts, sp)]
+        while any(not r.done for r in reqs):
+            eng.step()
+        results[overlap] = [(r.output_tokens, r.stats.finish_reason) for r in reqs]
+        st = eng.stats()
+        assert st["free_pages"] == st["num_pages"]
+        assert (st["overlapped_steps"] > 0) == overlap
+    assert results[True] == results[False]
+    assert results[True][1][0] == want[1]                                   # the greedy one beside them is untouched
+    assert [len(t) for t, _ in results[True]] == [10, 8, 4, 9]
+    # a stop token drawn by a sampled request ends it there, overlapped or not
+    stop = results[True][0][0][6]
+    outs = {}
+    for overlap in (False, True):
+        eng = engine(folder, overlap=overlap)
+        outs[overlap] = eng.generate([prompts[0]], SamplingParams(max_tokens=10, seed=7, temperature=0.9, top_p=0.85,
+                                                                  stop_token_ids={stop}))[0]
+    first = results[True][0][0].index(stop)
+    assert outs[True].token_ids == outs[False].token_ids == results[True][0][0][:first]
+    assert outs[True].finish_reason == outs[False].finish_reason == "stop"
