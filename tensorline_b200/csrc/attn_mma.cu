@@ -75,6 +75,9 @@ struct AttnArgs {
     // decode only
     int chunk, splits;
     float* part_o; float* part_ml;     // [B, nq, splits, D] and [B, nq, splits, 2]
+    // prefill only: the tiles in the order in which blocks take them, (request << 16 | tile), longest first over
+    // all requests; null: one request after the other from the end
+    const int* order;
 };
 
 // A [ROWS][DP] tile of keys (or values) of one KV head is filled by 128 threads in chunks of 16
@@ -241,10 +244,15 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     // Blocks are handed out in index order and a tile's work grows with its position in the request
     // (causal), so the tiles are taken from the end: the longest ones start first.
     int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;
-    for (; b < A.B; ++b) {
-        const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
-        if (tile < nt) break;
-        tile -= nt;
+    if (A.order != nullptr) {
+        const int packed = A.order[blockIdx.x / A.nkv];
+        b = packed >> 16; tile = packed & 0xFFFF;
+    } else {
+        for (; b < A.B; ++b) {
+            const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
+            if (tile < nt) break;
+            tile -= nt;
+        }
     }
     if (b >= A.B) return;
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
@@ -844,7 +852,7 @@ TL_EXPORT int tl_attn_head_dim() { return D; }
 TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                               const int* table, int max_pages, int page_size, const int* q_start,
                               const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
-                              float scale, int total_tiles, cudaStream_t stream) {
+                              float scale, int total_tiles, const int* order, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
     if (nq % nkv || BN % page_size) return 1;
     int e = set_attrs();
@@ -853,6 +861,7 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.order = order;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);

@@ -157,6 +157,9 @@ struct TcAttnArgs {
     int B, nq, nkv, window;
     float scale_log2;
     int* status;
+    // the tiles in the order in which blocks take them, (request << 16 | tile), longest first over all requests;
+    // null: one request after the other from the end
+    const int* order;
 };
 
 // Keys [key0, key0 + BN) of one KV head into a swizzled [BN][D] tile, by one warp; keys past
@@ -198,10 +201,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
 
     int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
-    for (; b < A.B; ++b) {
-        const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
-        if (tile < nt) break;
-        tile -= nt;
+    if (A.order != nullptr) {
+        const int packed = A.order[blockIdx.x / A.nkv];
+        b = packed >> 16; tile = packed & 0xFFFF;
+    } else {
+        for (; b < A.B; ++b) {
+            const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + BM - 1) / BM;
+            if (tile < nt) break;
+            tile -= nt;
+        }
     }
     if (b >= A.B) return;
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
@@ -475,10 +483,15 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
 
     int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
-    for (; b < A.B; ++b) {
-        const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + QT * BM - 1) / (QT * BM);
-        if (tile < nt) break;
-        tile -= nt;
+    if (A.order != nullptr) {
+        const int packed = A.order[blockIdx.x / A.nkv];
+        b = packed >> 16; tile = packed & 0xFFFF;
+    } else {
+        for (; b < A.B; ++b) {
+            const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + QT * BM - 1) / (QT * BM);
+            if (tile < nt) break;
+            tile -= nt;
+        }
     }
     if (b >= A.B) return;
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
@@ -766,7 +779,7 @@ TL_EXPORT int tl_attn_tc_head_dim() { return D; }
 TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                  const int* table, int max_pages, int page_size, const int* q_start,
                                  const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
-                                 float scale, int total_tiles, int* status, cudaStream_t stream) {
+                                 float scale, int total_tiles, int* status, const int* order, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
     if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size * 32 < BN || page_size > 64 || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
     if (!g_attr_done) {
@@ -779,7 +792,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
-    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(A);
     return tl_launch_status();
@@ -791,7 +804,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
 TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                   long long total_pages, const int* table, int max_pages, int page_size,
                                   const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
-                                  int window, float scale, int total_tiles, int* status, cudaStream_t stream) {
+                                  int window, float scale, int total_tiles, int* status, const int* order, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
@@ -819,7 +832,7 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
-    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
     return tl_launch_status();

@@ -33,7 +33,7 @@ def attn_lib(head_dim: int):
         if os.environ.get("TL_DEC_STAGES"):
             defines["TL_DEC_STAGES"] = int(os.environ["TL_DEC_STAGES"])
         lib = load_library(f"tl_attn_hd{head_dim}", ["attn_mma.cu"], defines)
-        lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P]
+        lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P]
         lib.tl_attn_prefill.restype = ctypes.c_int
         lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
         lib.tl_attn_decode.restype = ctypes.c_int
@@ -62,10 +62,10 @@ def attn_tc_lib(head_dim: int):
         if head_dim % 64 or not 64 <= head_dim <= 256:
             raise KernelError(f"head_dim {head_dim}: the tcgen05 attention kernel takes 64, 128, 192 or 256")
         lib = load_library(f"tl_attn_tc_hd{head_dim}", ["attn_tc.cu"], {"HEAD_DIM": head_dim})
-        lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P]
+        lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P, _P]
         lib.tl_attn_tc_prefill.restype = ctypes.c_int
         lib.tl_attn_tc2_prefill.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F,
-                                            _I, _P, _P]
+                                            _I, _P, _P, _P]
         lib.tl_attn_tc2_prefill.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
@@ -77,7 +77,7 @@ def tc_min_page(head_dim: int) -> int:
 
 
 def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-               nq, nkv, d, window, scale) -> None:
+               nq, nkv, d, window, scale, order=None) -> None:
     """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory."""
     from .ops_gemm import status_word
     if page_size < tc_min_page(d) or page_size > KEY_TILE or page_size & (page_size - 1):
@@ -89,14 +89,37 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
     _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
-                                             _ptr(status_word(q.device)), _stream()), "attn_tc_prefill")
+                                             _ptr(status_word(q.device)), _ptr(order) if order is not None else None,
+                                             _stream()), "attn_tc_prefill")
 
 
+def tile_order(h_q_start, h_start_pos, group: int, rows_per_tile: int, device):
+    """The order in which a prompt-portion kernel's blocks take the query tiles of a step with several requests:
+    int32 (request << 16 | tile), the tile that reads the most keys first, so that the long tiles of every request
+    start in the first round of blocks and the short ones fill the end.  None for one request (the kernel's own
+    order, last tile first, is the same) or when the numbers do not fit 16 bits."""
+    B = len(h_q_start) - 1
+    if B <= 1 or B >= 1 << 15:
+        return None
+    tiles = []
+    for b in range(B):
+        rows = (h_q_start[b + 1] - h_q_start[b]) * group
+        n = -(-rows // rows_per_tile)
+        if n >= 1 << 16:
+            return None
+        for t in range(n):
+            last_token = min(rows, (t + 1) * rows_per_tile) - 1
+            tiles.append((-(h_start_pos[b] + last_token // group + 1), b, t))
+    tiles.sort()
+    return torch.tensor([(b << 16) | t for _, b, t in tiles], dtype=torch.int32).to(device, non_blocking=True)
+
+
+TILE_ORDER = os.environ.get("TENSORLINE_B200_TILE_ORDER", "1") != "0"   # 0: request after request (A/B timing)
 TC_PAIR = os.environ.get("TENSORLINE_B200_TC_PAIR", "1") != "0"   # 0: one query tile per block only (A/B timing)
 
 
 def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-                    nq, nkv, d, window, scale) -> bool:
+                    nq, nkv, d, window, scale, order=None) -> bool:
     """Prompt-portion attention on tcgen05 with two query tiles (256 rows) per block and K, V by TMA.
     Head sizes 64 and 128, pages of 8 to 64 tokens; returns False (nothing launched) for other sizes."""
     from .ops_gemm import status_word
@@ -108,7 +131,8 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     rc = attn_tc_lib(d).tl_attn_tc2_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
-                                            _ptr(status_word(q.device)), _stream())
+                                            _ptr(status_word(q.device)), _ptr(order) if order is not None else None,
+                                            _stream())
     if rc == 2:
         return False
     _check(rc, "attn_tc2_prefill")
@@ -136,7 +160,7 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
 
 
 def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-            nq, nkv, d, window, scale) -> None:
+            nq, nkv, d, window, scale, order=None) -> None:
     g = nq // nkv
     B = len(h_q_start) - 1
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // KEY_TILE) for i in range(B))
@@ -144,7 +168,8 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
     _check(attn_lib(d).tl_attn_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                        table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
-                                       nq, nkv, int(window or 0), float(scale), tiles, _stream()), "attn_prefill")
+                                       nq, nkv, int(window or 0), float(scale), tiles,
+                                       _ptr(order) if order is not None else None, _stream()), "attn_prefill")
 
 
 TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.async loads only (A/B timing)
@@ -215,6 +240,16 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         # 4,096 152 against 230 us, 1,024 on 3,072 cached (112 blocks of pairs) 84 against 119 us, 1,024 alone 30
         # against 29 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 84 against 70 us)
         pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * (nq // nkv) // (2 * TC_QUERY_TILE)) for i in range(ctx.B))
-        if use_tc and TC_PAIR and pairs * nkv >= 0.7 * NUM_SMS and prefill_tc_pair(*args):
+        def order(rows_per_tile):
+            key = ("tile_order", nq // nkv, rows_per_tile)
+            if not TILE_ORDER:
+                return None
+            if key not in ctx.scratch:
+                ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, nq // nkv, rows_per_tile, qkv.device)
+            return ctx.scratch[key]
+        if use_tc and TC_PAIR and pairs * nkv >= 0.7 * NUM_SMS and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
             return
-        (prefill_tc if use_tc else prefill)(*args)
+        if use_tc:
+            prefill_tc(*args, order(TC_QUERY_TILE))
+        else:
+            prefill(*args, order(KEY_TILE))

@@ -320,6 +320,15 @@ def test_paged_attention(case, kernel):
             assert took == pair_ok                                         # other sizes are left to the other kernels
             if not took:
                 return
+        # the same tiles taken longest first over all requests: every row as before, bit for bit
+        order = ops_attention.tile_order(q_start, ctx_lens, nq // nkv, 128 if kernel == "tcgen05_bf16" else 256, "cuda")
+        assert (order is None) == (B == 1)
+        if order is not None:
+            again = torch.zeros_like(out)
+            fn(q_all, nq * d, again, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
+               q_start, nq, nkv, d, window, scale, order)
+            ops_gemm.check_status()
+            assert torch.equal(again, out)
     elif kernel != "mma_bf16":
         ops.attn_tokenwise(q_all, nq * d, out, kd, vd, table, ps, i32(pos_all), i32(slot_all), nq, nkv, d, window, scale)
     else:
@@ -345,6 +354,11 @@ def test_paged_attention(case, kernel):
                     assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} splits, tma {tma}, cluster {cluster}", **BF16)
             out.zero_()
         ops_attention.prefill(*args, q_start, nq, nkv, d, window, scale)
+        order = ops_attention.tile_order(q_start, ctx_lens, nq // nkv, 64, "cuda")
+        if order is not None:
+            again = torch.zeros_like(out)
+            ops_attention.prefill(q_all, nq * d, again, *args[3:], q_start, nq, nkv, d, window, scale, order)
+            assert torch.equal(again, out)
     assert_close(out.view(T, nq, d), torch.cat(want), kernel, **tol(adt))
 
 
