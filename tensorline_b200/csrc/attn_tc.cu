@@ -143,6 +143,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// the largest of a row's scores: two chains of three-input maxima (half the instructions of two-input ones)
+template <int N>
+__device__ __forceinline__ float row_max(const float (&s)[N]) {
+    static_assert(N % 4 == 0 && N >= 8, "row_max");
+    float a = max3(s[0], s[1], s[2]), b = max3(s[3], s[4], s[5]);
+#pragma unroll
+    for (int c = 6; c + 3 < N; c += 4) { a = max3(a, s[c], s[c + 1]); b = max3(b, s[c + 2], s[c + 3]); }
+    return max3(a, b, fmaxf(s[N - 2], s[N - 1]));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -161,6 +175,37 @@ struct TcAttnArgs {
     // null: one request after the other from the end
     const int* order;
 };
+
+// One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
+// the group).  Where 128 is a multiple of the chunks a row has (head sizes 64, 128, 256) a thread keeps its chunk
+// column and its rows are 128 / CH apart: token and head then advance by additions from one division.
+__device__ __forceinline__ void load_q_rows(uint32_t dst_tile, const bf16* q, int q_stride, int qs, int head0, int g,
+                                            int row0, int rows_total, int r) {
+    constexpr int CH = D / 8;
+    if constexpr (BM % CH == 0) {
+        constexpr int ROW_STEP = BM / CH;
+        const int c = r % CH;
+        int qr = r / CH;
+        int tok = (row0 + qr) / g, rem = (row0 + qr) - tok * g;
+        const int d_tok = ROW_STEP / g, d_rem = ROW_STEP - d_tok * g;
+#pragma unroll 4
+        for (int k = 0; k < CH; ++k, qr += ROW_STEP) {
+            const bool valid = row0 + qr < rows_total;
+            const bf16* src = valid ? q + (size_t)(qs + tok) * q_stride + (size_t)(head0 + rem) * D + c * 8 : q;
+            cp_async16(dst_tile + swz(BM, qr, c), src, valid);
+            tok += d_tok; rem += d_rem;
+            if (rem >= g) { rem -= g; ++tok; }
+        }
+    } else {
+        for (int idx = r; idx < BM * CH; idx += BM) {
+            const int qr = idx / CH, c = idx - qr * CH;
+            const int QR = row0 + qr;
+            const bool valid = QR < rows_total;
+            const bf16* src = valid ? q + (size_t)(qs + QR / g) * q_stride + (size_t)(head0 + QR % g) * D + c * 8 : q;
+            cp_async16(dst_tile + swz(BM, qr, c), src, valid);
+        }
+    }
+}
 
 // Keys [key0, key0 + BN) of one KV head into a swizzled [BN][D] tile, by one warp; keys past
 // last_key are zeros.  The page size is a power of two, at least BN / 32 (shift, mask).  The tile's
@@ -247,15 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         {   // the Q tile, row = (token, head of the group), while the first K and V tiles are on their way
-            constexpr int CH = D / 8;
-            for (int idx = tid; idx < BM * CH; idx += BM) {
-                const int qr = idx / CH, c = idx - qr * CH;
-                const int QR = row0 + qr;
-                const bool valid = QR < rows_total;
-                const bf16* src = A.q;
-                if (valid) src = A.q + (size_t)(qs + QR / g) * A.q_stride + (size_t)(kh * g + QR % g) * D + c * 8;
-                cp_async16(sQ + swz(BM, qr, c), src, valid);
-            }
+            load_q_rows(sQ, A.q, A.q_stride, qs, kh * g, g, row0, rows_total, tid);
             cp_async_wait_all();
             fence_async_proxy();
             mbar_arrive(bar_q);
@@ -279,10 +316,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                     if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four short chains, not one long one
-#pragma unroll
-            for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * A.scale_log2;
+            const float mx = row_max(s) * A.scale_log2;
             // Raise the reference maximum only when a tile exceeds it by more than the threshold.  The
             // tensor-memory loads and stores are warp-wide instructions, so the warp corrects O together
             // (factor 1 for rows that do not move) if any of its rows has to.
@@ -442,10 +476,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
 // query rows as two tiles that share every K and V tile: eight softmax warps, two per scheduler; four MMA
 // issuers (S and P V of each tile); K and V as TMA boxes (one page of one KV head, 64 elements wide, 128-byte
 // swizzle) issued by one thread each, from the block's first cycle on, while the softmax warps fetch their Q tile
-// (a copy warp fetching Q first cost every block 7 to 10 us before its first product).  Measured: 2,070 cycles a key tile for both query tiles, of which the
-// exponentials of 2 x 128 x 64 scores are 1,024 on the special-function unit.  Tensor memory: S[tile][2] at
-// columns 0..255, O[tile] behind them.
+// (a copy warp fetching Q first cost every block 7 to 10 us before its first product).  Measured: about 2,000 cycles
+// a key tile for both query tiles.  The exponentials of 2 x 128 x 64 scores are 1,024 of them on the special-function
+// unit, and the softmax body of two warps on one scheduler, run alone, takes 1,320; what the step cannot go below
+// here is shared memory: the products read Q and K (6 KB an instruction for S), P and V (8 KB for P V), the softmax
+// writes P and the copies write K and V, 224 KB a key tile at 128 bytes a cycle = 1,750 cycles.  (P as a tensor-memory
+// operand would take 64 KB of that away; tensor memory is full with two S slots a tile.)  Tensor memory: S[tile][2]
+// at columns 0..255, O[tile] behind them.
 constexpr int QT = 2;
+constexpr int TURN_AT = 6;               // the turn at the exponentials passes on after this 8-score group of 0..7 (measured best)
 constexpr int THREADS2 = 448;           // warps 0..7: softmax (tile = warp / 4); 8..11: MMA issue; 12: K copies; 13: V copies
 constexpr int SMEM2_TILES = QT * Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + QT * 2 * P_BYTES;
 constexpr int SMEM2_BYTES = SMEM2_TILES + 1024 + 256;
@@ -476,7 +515,8 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     uint64_t* bar_kfree = bars + 16; // [slot] both S issuers are done with this K slot (a commit, or a plain arrival)
     uint64_t* bar_vfree = bars + 18; // [slot] both P V issuers are done with this V slot
     uint64_t* bar_q = bars + 20;     // both Q tiles are in shared memory
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+    uint64_t* bar_x = bars + 21;     // [tile * 4 + warp of the tile] that warp's exponentials of a key tile are issued
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 29);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -519,6 +559,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         for (int i = 0; i < 4; ++i) { mbar_init(bar_s + i, 1); mbar_init(bar_p + i, 128); mbar_init(bar_o + i, 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar_k + i, 1); mbar_init(bar_v + i, 1); mbar_init(bar_kfree + i, 2); mbar_init(bar_vfree + i, 2); }
         mbar_init(bar_q, QT * BM);
+        for (int i = 0; i < 8; ++i) mbar_init(bar_x + i, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -539,18 +580,19 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int lo_r = A.window > 0 ? max(0, pos_r - A.window + 1) : 0;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int n_mine = kt_last[t] - kt_first[t] + 1;   // <= 0: this tile has no rows
+        // The two warps of a scheduler (one of each query tile) take turns at the exponentials.  Left alone they run
+        // in step: both load and reduce (the special-function unit idle), then both want that unit at once, 2,060
+        // cycles a key tile where the two phases side by side need 1,300.  Over the key tiles that both query tiles
+        // read, tile 1's warp starts its exponentials of key tile j when tile 0's warp is through its own of j, and
+        // tile 0's of j + 1 when tile 1's of j are through; the order follows the key tiles, so neither waits for
+        // anything the other can only reach later.
+        const int x_lo = max(kt_first[0], kt_first[1]), x_hi = min(kt_last[0], kt_last[1]);   // empty if tile 1 has no rows
+        uint64_t* const x_mine = bar_x + t * 4 + (warp & 3);
+        uint64_t* const x_other = bar_x + (1 - t) * 4 + (warp & 3);
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         {   // the tile's Q rows, row = (token, head of the group), while the first K and V tiles are on their way
-            constexpr int CH = D / 8;
-            for (int idx = r; idx < BM * CH; idx += BM) {
-                const int qr = idx / CH, c = idx - qr * CH;
-                const int QR = row0[t] + qr;
-                const bool valid = QR < rows_total;
-                const bf16* src = A.q;
-                if (valid) src = A.q + (size_t)(qs + QR / g) * A.q_stride + (size_t)(kh * g + QR % g) * D + c * 8;
-                cp_async16(sQ + t * Q_BYTES + swz(BM, qr, c), src, valid);
-            }
+            load_q_rows(sQ + t * Q_BYTES, A.q, A.q_stride, qs, kh * g, g, row0[t], rows_total, r);
             cp_async_wait_all();
             fence_async_proxy();
             mbar_arrive(bar_q);
@@ -575,10 +617,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * A.scale_log2;
+            const float mx = row_max(s) * A.scale_log2;
             const bool raise = mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY);
             const float m_new = raise ? fmaxf(mx, m_ref) : m_ref;
             const bool fix_o = raise && i > 0 && m_ref != -INFINITY;        // O holds earlier tiles of this row
@@ -604,6 +643,11 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 ok = mbar_wait(bar_o + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 3);
                 if (!ok) break;
             }
+            const bool in_turns = kt >= x_lo && kt <= x_hi;
+            if (in_turns && (t == 1 || kt > x_lo)) {
+                ok = mbar_wait(x_other, (kt - x_lo - (t == 0 ? 1 : 0)) & 1, abort_flag, A.status, 12);
+                if (!ok) break;
+            }
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j8 = 0; j8 < BN / 8; ++j8) {
@@ -616,6 +660,10 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 const uint32_t dst = sP + bi * P_BYTES + swz(BM, r, j8);
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
                              "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
+                if (j8 == TURN_AT && in_turns) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(x_mine);
+                }
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             fence_async_proxy();                            // generic-proxy writes of P before the MMA reads them

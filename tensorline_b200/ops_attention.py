@@ -236,9 +236,9 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
         # Two query tiles a block pay once its blocks (one per SM) fill most of the GPU; below that the one-tile
-        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 50 against 76 us,
-        # 4,096 152 against 230 us, 1,024 on 3,072 cached (112 blocks of pairs) 84 against 119 us, 1,024 alone 30
-        # against 29 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 84 against 70 us)
+        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 45 against 71 us,
+        # 4,096 140 against 219 us, 1,024 on 3,072 cached (112 blocks of pairs) 78 against 116 us, 1,024 alone 27
+        # against 27 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 76 against 69 us)
         pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * (nq // nkv) // (2 * TC_QUERY_TILE)) for i in range(ctx.B))
         def order(rows_per_tile):
             key = ("tile_order", nq // nkv, rows_per_tile)
