@@ -86,6 +86,8 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
     g = nq // nkv
     B = len(h_q_start) - 1
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // TC_QUERY_TILE) for i in range(B))
+    if order is not None:
+        tiles = order.numel()                           # the array may leave requests out
     _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
@@ -93,16 +95,19 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
                                              _stream()), "attn_tc_prefill")
 
 
-def tile_order(h_q_start, h_start_pos, group: int, rows_per_tile: int, device):
+def tile_order(h_q_start, h_start_pos, group: int, rows_per_tile: int, device, skip=()):
     """The order in which a prompt-portion kernel's blocks take the query tiles of a step with several requests:
     int32 (request << 16 | tile), the tile that reads the most keys first, so that the long tiles of every request
-    start in the first round of blocks and the short ones fill the end.  None for one request (the kernel's own
-    order, last tile first, is the same) or when the numbers do not fit 16 bits."""
+    start in the first round of blocks and the short ones fill the end.  Requests in `skip` get no tile (another
+    kernel serves them).  None for one request and nothing to skip (the kernel's own order, last tile first, is
+    the same) or when the numbers do not fit 16 bits."""
     B = len(h_q_start) - 1
-    if B <= 1 or B >= 1 << 15:
+    if (B <= 1 and not skip) or B >= 1 << 15:
         return None
     tiles = []
     for b in range(B):
+        if b in skip:
+            continue
         rows = (h_q_start[b + 1] - h_q_start[b]) * group
         n = -(-rows // rows_per_tile)
         if n >= 1 << 16:
@@ -128,6 +133,8 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     g = nq // nkv
     B = len(h_q_start) - 1
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in range(B))
+    if order is not None:
+        tiles = order.numel()
     rc = attn_tc_lib(d).tl_attn_tc2_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
@@ -166,6 +173,8 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
     g = nq // nkv
     B = len(h_q_start) - 1
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // KEY_TILE) for i in range(B))
+    if order is not None:
+        tiles = order.numel()
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
     _check(attn_lib(d).tl_attn_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
@@ -231,23 +240,40 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
     else:
+        g = nq // nkv
+        singles = _single_token_requests(ctx, qkv.device, g)
+        skip = singles["set"] if singles else frozenset()
+        if singles:
+            # the single decoded tokens of a mixed step: the decode kernel cuts their keys into ranges, where a
+            # query tile of the portion kernels would walk one request's whole context with 1 row in 18 used
+            span = min(singles["span"], window + KEY_TILE - 1) if window else singles["span"]
+            n = len(skip)
+            chunk, splits = plan_splits(n, nkv, g, span, d)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty((n, nq, splits, d), dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty((n, nq, splits, 2), dtype=torch.float32, device=qkv.device)
+            decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
+                   singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+        rest = [i for i in range(ctx.B) if i not in skip]
+        rest_rows = sum(ctx.h_q_start[i + 1] - ctx.h_q_start[i] for i in rest) * g
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05; steps of mostly
         # single tokens (a few decoded tokens beside a short portion) keep the 64-row mma.sync tiles.
-        rows = ctx.T * (nq // nkv)
-        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rows >= 96 * ctx.B
+        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rest_rows >= 96 * len(rest)
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
         # Two query tiles a block pay once its blocks (one per SM) fill most of the GPU; below that the one-tile
         # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 45 against 71 us,
         # 4,096 140 against 219 us, 1,024 on 3,072 cached (112 blocks of pairs) 78 against 116 us, 1,024 alone 27
         # against 27 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 76 against 69 us)
-        pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * (nq // nkv) // (2 * TC_QUERY_TILE)) for i in range(ctx.B))
+        pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in rest)
+
         def order(rows_per_tile):
-            key = ("tile_order", nq // nkv, rows_per_tile)
-            if not TILE_ORDER:
+            if not TILE_ORDER and not skip:
                 return None
+            key = ("tile_order", g, rows_per_tile)
             if key not in ctx.scratch:
-                ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, nq // nkv, rows_per_tile, qkv.device)
+                ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, g, rows_per_tile, qkv.device, skip)
             return ctx.scratch[key]
         if use_tc and TC_PAIR and pairs * nkv >= 0.7 * NUM_SMS and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
             return
@@ -255,3 +281,34 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
             prefill_tc(*args, order(TC_QUERY_TILE))
         else:
             prefill(*args, order(KEY_TILE))
+
+
+SINGLES_MIN_KEYS = int(os.environ.get("TENSORLINE_B200_SINGLES_MIN_KEYS", 768))
+SINGLES_RATIO = float(os.environ.get("TENSORLINE_B200_SINGLES_RATIO", 1.5))
+
+
+def _single_token_requests(ctx, device, group: int):
+    """The requests of a mixed step that bring one token, if they are worth a launch of the decode kernel: the longest
+    of them reads SINGLES_MIN_KEYS keys or more and SINGLES_RATIO times as many as any other request of the step (a
+    query tile walks its keys alone, so the longest one sets the pace of the portion kernel; measured at 7B sizes,
+    a layer: 7 x 4,000 cached beside 2,041 new tokens 66 against 83 us, 3 x 8,000 beside 509 33 against 156 us, 31
+    x 1,000 beside 481 30 against 35 us, but 3,000 / 2,000 / 500 beside 2,045 66 against 62 us and 7 x 4,000 beside
+    2,041 on 2,048 cached 122 against 115 us).  {"set", "rows", "start_pos", "slots", "span"} with device tensors,
+    or None.  Computed once a step."""
+    key = ("single_token_requests", group)
+    if key not in ctx.scratch:
+        B = ctx.B
+        ones = [b for b in range(B) if ctx.h_q_start[b + 1] - ctx.h_q_start[b] == 1]
+        found = None
+        span = max((ctx.h_start_pos[b] + 1 for b in ones), default=0)
+        rest_span = max((ctx.h_start_pos[b] + ctx.h_q_start[b + 1] - ctx.h_q_start[b] for b in range(B)
+                         if ctx.h_q_start[b + 1] - ctx.h_q_start[b] != 1), default=0)
+        if ones and len(ones) < B and B < 1 << 15 and span >= SINGLES_MIN_KEYS and span >= SINGLES_RATIO * rest_span and \
+                all((ctx.h_q_start[b + 1] - ctx.h_q_start[b]) * group < KEY_TILE << 16 for b in range(B)):
+            n = len(ones)
+            packed = torch.tensor([ctx.h_q_start[b] for b in ones] + [ctx.h_start_pos[b] for b in ones] +
+                                  [ctx.h_slots[b] for b in ones], dtype=torch.int32).to(device, non_blocking=True)
+            found = {"set": frozenset(ones), "rows": packed[:n], "start_pos": packed[n:2 * n], "slots": packed[2 * n:],
+                     "span": span}
+        ctx.scratch[key] = found
+    return ctx.scratch[key]

@@ -407,6 +407,71 @@ def test_attention_over_a_long_context(window):
             assert_close(out.view(1, nq, d), want1, f"decode over a long cache, {splits} ranges, tma {tma}, cluster {cluster}", **BF16)
 
 
+@pytest.mark.parametrize("case", [
+    # nq, nkv, d, page, (cached, new tokens) a request, window
+    (28, 4, 128, 16, [(1500, 1), (0, 300), (1100, 1), (40, 1)], None),      # singles between and around a portion
+    (8, 2, 64, 8, [(70, 2), (1300, 1), (0, 150), (900, 1)], 700),           # a window; the two-token portion stays
+    (6, 2, 48, 16, [(1200, 1), (5, 40)], None),                             # a head size without tcgen05 build
+])
+def test_single_tokens_of_a_mixed_step_take_the_decode_kernel(case, monkeypatch):
+    """attend_bf16 on a step of portions beside single decoded tokens: the single tokens with long contexts go
+    through the decode kernel (their keys cut into ranges), the portions through a prompt kernel that is told to
+    leave them out; every row against the plain formula, and against the same step with everything in the prompt
+    kernel."""
+    from types import SimpleNamespace
+    from tensorline_b200 import ops_attention, ops_gemm
+    nq, nkv, d, ps, reqs, window = case
+    B = len(reqs)
+    num_pages, max_pages = 1200, 256
+    kps = torch.zeros(num_pages + 1, nkv, ps, d, dtype=torch.bfloat16)
+    vps = torch.zeros_like(kps)
+    rows, qs, want, q_start, start_pos = [], [], [], [0], []
+    for b, (cached, new) in enumerate(reqs):
+        n = cached + new
+        k, v = rnd(n, nkv, d, seed=20 + b, dtype=torch.bfloat16), rnd(n, nkv, d, seed=40 + b, dtype=torch.bfloat16)
+        q = rnd(new, nq, d, seed=60 + b, scale=2.0, dtype=torch.bfloat16)
+        if cached > 600:                            # one far key that must win for the single token
+            far = cached - 500
+            k[far] *= 0; k[far, :, 0] = 9.0; q[-1] *= 0; q[-1, :, 0] = 9.0
+        gen = torch.Generator().manual_seed(100 + b)
+        mine = (torch.randperm(num_pages // B, generator=gen)[:-(-n // ps)] * B + b).tolist()
+        for i in range(n):
+            kps[mine[i // ps], :, i % ps] = k[i]
+            vps[mine[i // ps], :, i % ps] = v[i]
+        rows.append(mine)
+        want.append(_plain_attention_rows(q.double(), k.double(), v.double(), list(range(cached, n)), window))
+        qs.append(q)
+        q_start.append(q_start[-1] + new)
+        start_pos.append(cached)
+    T = q_start[-1]
+    qkv = torch.zeros(T, (nq + 2 * nkv) * d, dtype=torch.bfloat16)
+    qkv[:, :nq * d] = torch.cat(qs).reshape(T, nq * d)
+    qkv = qkv.cuda()
+    table = table_tensor(rows, max_pages, num_pages)
+    kd, vd = kps.cuda(), vps.cuda()
+
+    def run():
+        ctx = SimpleNamespace(B=B, T=T, decode_only=False, page_size=ps, q_start=i32(q_start), start_pos=i32(start_pos),
+                              slots=i32(list(range(B))), h_q_start=q_start, h_start_pos=start_pos,
+                              h_slots=list(range(B)), graph_max_ctx=0, max_ctx=max(c + n for c, n in reqs), scratch={})
+        out = torch.zeros(T, nq * d, dtype=torch.bfloat16, device="cuda")
+        ops_attention.attend_bf16(qkv, out, ctx, kd, vd, table, nq, nkv, d, window, d ** -0.5)
+        ops_gemm.check_status()
+        return out, ctx
+
+    out, ctx = run()
+    found = ctx.scratch[("single_token_requests", nq // nkv)]
+    assert found is not None and found["set"] == frozenset(b for b, (c, n) in enumerate(reqs) if n == 1)
+    assert_close(out.view(T, nq, d), torch.cat(want), "mixed step, single tokens by the decode kernel", **BF16)
+    monkeypatch.setattr(ops_attention, "SINGLES_MIN_KEYS", 1 << 30)
+    whole, ctx = run()
+    assert ctx.scratch[("single_token_requests", nq // nkv)] is None
+    assert_close(whole.view(T, nq, d), torch.cat(want), "mixed step, all in the prompt kernel", **BF16)
+    single_rows = [q_start[b] for b, (c, n) in enumerate(reqs) if n == 1]
+    other = [r for r in range(T) if r not in single_rows]
+    assert torch.equal(out[other], whole[other])            # the portions' rows do not notice
+
+
 def test_attention_refuses_unsupported_head_size():
     from tensorline_b200 import ops, ops_attention
     with pytest.raises(ops.KernelError):
