@@ -266,7 +266,7 @@ def run_ours(a):
     torch.cuda.set_device(device)
     pk, pk_src = peaks()
     weights = random_weights(cfg, device)
-    max_seqs = 64
+    max_seqs = max(64, a.batch)
     eng = Engine(cfg, dtype="bfloat16", weights=weights, block_size=PAGE, max_num_seqs=max_seqs,
                  max_batched_tokens=2048, max_model_len=CONTEXT, num_blocks=max_seqs * (CONTEXT // PAGE),
                  prefix_caching=False, cuda_graphs=True)
