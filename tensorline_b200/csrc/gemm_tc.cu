@@ -329,14 +329,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int nz = (int)gridDim.z, ntok = min(BN, G.RB - b0);
             const int total = ntok * BM, share = (((total + nz - 1) / nz) + 3) & ~3;
             const int lo = split * share, hi = min(total, lo + share);
-            for (int idx = lo + (int)threadIdx.x - 64; idx < hi; idx += 128) {
-                float acc = 0.f;
-                for (int z = 0; z < nz; ++z) acc += *cluster_peer(red + idx, z);
+            // four rows of A a thread and step (shares and BM are multiples of 4): one 16-byte load a peer
+            const bool wide = (G.ldo & 3) == 0 && (((uintptr_t)G.out) & 15) == 0;
+            for (int idx = lo + 4 * ((int)threadIdx.x - 64); idx < hi; idx += 4 * 128) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int z = 0; z < nz; ++z) {
+                    const float4 v = *reinterpret_cast<const float4*>(cluster_peer(red + idx, z));
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
                 const int tok = idx / BM, a = a0 + (idx - tok * BM);
-                if (a < G.RA) {
-                    const size_t o = (size_t)(b0 + tok) * G.ldo + a;
-                    if (G.out_f32) ((float*)G.out)[o] = acc;
-                    else ((bf16*)G.out)[o] = __float2bfloat16_rn(acc);
+                const size_t o = (size_t)(b0 + tok) * G.ldo + a;
+                if (wide && a + 3 < G.RA) {
+                    if (G.out_f32) {
+                        *reinterpret_cast<float4*>((float*)G.out + o) = acc;
+                    } else {
+                        __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc.x, acc.y), hi2 = __floats2bfloat162_rn(acc.z, acc.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo2); packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+                        *reinterpret_cast<uint2*>((bf16*)G.out + o) = packed;
+                    }
+                } else {
+                    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+                    for (int j = 0; j < 4; ++j) {
+                        if (a + j < G.RA) {
+                            if (G.out_f32) ((float*)G.out)[o + j] = vals[j];
+                            else ((bf16*)G.out)[o + j] = __float2bfloat16_rn(vals[j]);
+                        }
+                    }
                 }
             }
         }
