@@ -24,3 +24,38 @@ def test_every_tile_once_and_the_longest_first():
         assert sorted(seen) == want
         keys = [pos[b] + (min(lens[b] * group, (t + 1) * rows_per_tile) - 1) // group + 1 for b, t in seen]
         assert keys == sorted(keys, reverse=True)
+
+
+def _ctx(reqs):
+    """A step's host-side description: (cached, new tokens) a request."""
+    from types import SimpleNamespace
+    q_start = [0]
+    for _, n in reqs:
+        q_start.append(q_start[-1] + n)
+    return SimpleNamespace(B=len(reqs), h_q_start=q_start, h_start_pos=[c for c, _ in reqs],
+                           h_slots=list(range(10, 10 + len(reqs))), scratch={})
+
+
+def test_which_single_tokens_of_a_mixed_step_leave_the_portion_kernel():
+    from tensorline_b200.ops_attention import _single_token_requests
+    # long single contexts beside a short portion: all single tokens go, with their rows, positions and slots
+    ctx = _ctx([(4000, 1), (0, 300), (50, 1), (2000, 1)])
+    found = _single_token_requests(ctx, "cpu", 7)
+    assert found["set"] == frozenset({0, 2, 3}) and found["span"] == 4001
+    assert found["rows"].tolist() == [0, 301, 302]
+    assert found["start_pos"].tolist() == [4000, 50, 2000] and found["slots"].tolist() == [10, 12, 13]
+    assert _single_token_requests(ctx, "cpu", 7) is found                       # once a step
+    # the portion reads about as many keys as the longest single token: one kernel for all
+    assert _single_token_requests(_ctx([(4000, 1), (2048, 2041)]), "cpu", 7) is None
+    # short contexts, only single tokens, no single tokens
+    assert _single_token_requests(_ctx([(300, 1), (0, 100)]), "cpu", 7) is None
+    assert _single_token_requests(_ctx([(4000, 1), (3000, 1)]), "cpu", 7) is None
+    assert _single_token_requests(_ctx([(4000, 2), (0, 100)]), "cpu", 7) is None
+
+
+def test_skipped_requests_get_no_tile():
+    order = tile_order([0, 1, 301, 302], [4000, 0, 900], 7, 128, "cpu", skip=frozenset({0, 2})).tolist()
+    assert sorted(v >> 16 for v in order) == [1] * (-(-300 * 7 // 128))
+    assert [v & 0xFFFF for v in order] == sorted((v & 0xFFFF for v in order), reverse=True)
+    # one request left and others skipped: still an explicit order (the kernel's own would include them)
+    assert tile_order([0, 1, 101], [4000, 0], 1, 64, "cpu", skip=frozenset({0})).tolist() == [(1 << 16) | 1, 1 << 16]
