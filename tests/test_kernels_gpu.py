@@ -87,7 +87,7 @@ def test_silu_mul_interleaved(adt, I, block):
         ops.silu_mul(gu.cuda(), a, block=I - 1)
 
 
-@pytest.mark.parametrize("T", [1, 8, 37])
+@pytest.mark.parametrize("T", [1, 8, 37, 64])
 def test_tcgen05_product_with_the_activation_in_its_epilogue(T):
     """Against interleaved gate / up rows the gated epilogue gives bit for bit what the product, stored in
     bfloat16, followed by the activation kernel gives."""
@@ -483,6 +483,8 @@ def test_attention_refuses_unsupported_head_size():
 TC_CASES = [  # tokens, N, K, forced (swap, bn, splits) or None for the launcher's plan
     (8, 128, 64, (1, 16, 1)), (8, 200, 1000, (1, 16, 1)), (37, 300, 520, (1, 64, 3)), (1, 3584, 2048, None),
     (16, 4608, 3584, None), (130, 200, 72, (0, 128, 1)), (300, 520, 1000, (0, 256, 1)), (5, 264, 2056, (1, 32, 4)),
+    # 64-token tiles: weight and activation tiles in rings of their own, many K tiles a block
+    (64, 384, 3000, (1, 64, 1)), (50, 264, 2056, (1, 64, 2)), (130, 200, 1000, (0, 64, 1)), (64, 3584, 18944, None),
 ]
 
 
