@@ -105,7 +105,7 @@ def random_weights(cfg, device, seed=0):
     for name, spec in expected_tensors(cfg).items():
         if spec.optional:
             continue
-        if "norm" in name:
+        if spec.init == "ones":
             out[name] = torch.ones(spec.shape, dtype=torch.bfloat16, device=device)
         else:
             t = torch.empty(spec.shape, dtype=torch.bfloat16, device=device)

@@ -17,9 +17,11 @@ tables and slots index are allocated by the model runner from `groups` and `stat
 Rules kept from tzar-beep/Tensorline: position p of a request lives in page
 `table[p // page_size]` at offset `p % page_size` (tensorline/paged.py:202); allocation is
 all-or-nothing (paged.py:57-69, batch_engine.py:248-259); only full, fully computed pages are
-published for sharing (batch_engine.py:282-290); a fully cached prompt gives back its last
-page so that its last token is computed for logits (batch_engine.py:277-279); one extra page
-past the pool is a sink for padding rows (paged.py:125-127).
+published for sharing (batch_engine.py:282-290); a prompt found whole in the cache still computes
+its last token, for the logits (batch_engine.py:277-279); one extra page past the pool is a sink
+for padding rows (paged.py:125-127).  Beyond it: every page group shares prefixes, a window group
+too (a new request takes only the published pages its window still reaches, the entries before
+them point at the sink); groups may have pools of different sizes.
 """
 from __future__ import annotations
 
@@ -71,14 +73,16 @@ class PageGroup:
 @dataclass
 class _Held:
     slot: int
-    pages: list                                         # per group: list of page ids, -1 once given back
-    hashes: list = field(default_factory=list)          # hashes of the published full pages (full-attention only)
+    pages: list                                         # per group: page ids in position order, -1 once given back
+    digests: list = field(default_factory=list)         # chained digests of the request's full, computed pages
+    offered: list = field(default_factory=list)         # per group: how many of them were offered for publishing
 
 
 class CacheManager:
-    def __init__(self, needs: dict, *, page_size: int, num_pages: int, max_num_seqs: int,
+    def __init__(self, needs: dict, *, page_size: int, num_pages, max_num_seqs: int,
                  max_model_len: int, prefix_caching: bool = True):
-        """`needs`: cache id -> `PagedKV` | `SlotState` (one id per cache that a run entry owns)."""
+        """`needs`: cache id -> `PagedKV` | `SlotState` (one id per cache that a run entry owns).
+        `num_pages`: pages of every group's pool, or {window (None: all keys): pages} per group."""
         if page_size < 1:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
@@ -100,15 +104,16 @@ class CacheManager:
                 raise ValueError(f"cache {cid!r}: window must be positive")
             g = by_key.get(need.group_key)
             if g is None:
-                g = PageGroup(len(self.groups), need.window, PagePool(num_pages, False))
-                g.table = np.full((max_num_seqs + 1, self.max_pages_per_seq), num_pages, dtype=np.int32)
+                n = num_pages[need.window] if isinstance(num_pages, dict) else num_pages
+                g = PageGroup(len(self.groups), need.window, PagePool(n, False))
+                g.table = np.full((max_num_seqs + 1, self.max_pages_per_seq), n, dtype=np.int32)
                 by_key[need.group_key] = g
                 self.groups.append(g)
             g.caches.append(cid)
             self.group_of[cid] = g.index
-        # Sharing a prefix needs every cache of a request to be restorable from pages alone.
-        self.prefix_caching = bool(prefix_caching and len(self.groups) == 1
-                                   and self.groups[0].window is None and not self.state_needs)
+        # A shared prefix is restored from pages alone: every page group can do that (a window group
+        # needs only the pages its window still reaches), state of fixed size cannot.
+        self.prefix_caching = bool(prefix_caching and self.groups and not self.state_needs)
         for g in self.groups:
             g.pool.prefix_caching = self.prefix_caching
         self._free_slots = list(range(max_num_seqs - 1, -1, -1))
@@ -152,36 +157,87 @@ class CacheManager:
     def pages(self, rid, group: int = 0) -> list[int]:
         return list(self._held[rid].pages[group])
 
+    def capacity(self, rid) -> int:
+        """Positions [0, capacity) of `rid` have a table entry in every group (a page, or the sink for
+        what a window has passed); a step may not write at or beyond it.  Without page groups there
+        is no bound."""
+        held = self._held[rid]
+        if not self.groups:
+            return self.max_model_len
+        return min(len(p) for p in held.pages) * self.page_size
+
+    def room_for(self, rid, start: int) -> int:
+        """How many tokens from position `start` on `grow` could make room for right now, counting the
+        pages the request already holds, the idle ones and those its windows have passed at `start`."""
+        held = self._held[rid]
+        room = self.max_pages_per_seq * self.page_size - start
+        for g, pages in zip(self.groups, held.pages):
+            first = self._first_needed_page(g, start)
+            # a passed page that others share comes back to nobody: count the request's own only
+            returning = sum(1 for p in pages[:first] if p >= 0 and g.pool.refcount(p) == 1)
+            room = min(room, (len(pages) + g.pool.num_free + returning) * self.page_size - start)
+        return max(0, room)
+
     # ------------------------------------------------------------------ life of a request
+    def _chain(self, tokens, upto_pages: int, known: list) -> list:
+        """Chained digests of the first `upto_pages` full pages of `tokens`, extending `known`."""
+        ps = self.page_size
+        for i in range(len(known), upto_pages):
+            known.append(page_hash(known[-1] if known else None, tokens[i * ps:(i + 1) * ps]))
+        return known
+
+    def _shared_prefix_pages(self, tokens) -> tuple:
+        """(k, digests): the largest number k of leading full pages of `tokens` that every group can
+        serve from published pages.  A group that keeps all keys needs all k pages; a window group
+        only those a query at position k * page_size can still read.  At least one token is left to
+        compute (tensorline/batch_engine.py:277-279: the last token's logits are wanted)."""
+        ps = self.page_size
+        most = (len(tokens) - 1) // ps
+        digests = self._chain(tokens, most, [])
+
+        def served(g: PageGroup, i: int) -> bool:
+            return g.pool.find(digests[i], digests[i - 1] if i else None, tokens[i * ps:(i + 1) * ps]) is not None
+
+        for g in self.groups:                            # groups that keep everything bound k from above
+            if g.window is None:
+                k = 0
+                while k < most and served(g, k):
+                    k += 1
+                most = k
+        for k in range(most, 0, -1):
+            if all(served(g, i) for g in self.groups if g.window is not None
+                   for i in range(self._first_needed_page(g, k * ps), k)):
+                return k, digests[:k]
+        return 0, []
+
     def admit(self, rid, tokens=None) -> int | None:
-        """Give `rid` a slot and, if sharing is on, the published pages of the longest prefix
-        of `tokens`.  Returns the number of tokens whose cache is already there, or None if no
-        slot is free (tensorline/batch_engine.py:266-280)."""
+        """Give `rid` a slot and, if sharing is on, the published pages of the longest prefix of
+        `tokens` that all groups can serve.  Returns the number of tokens whose cache is already
+        there, or None if no slot is free."""
         if rid in self._held:
             raise CacheError(f"request {rid!r} is already admitted")
         if not self._free_slots:
             return None
-        held = _Held(self._free_slots.pop(), [[] for _ in self.groups])
+        held = _Held(self._free_slots.pop(), [[] for _ in self.groups], offered=[0] * len(self.groups))
         self._held[rid] = held
-        cached = 0
-        if self.prefix_caching and tokens is not None:
-            ps, pool, parent = self.page_size, self.groups[0].pool, None
-            pages = held.pages[0]
-            for i in range(len(tokens) // ps):
-                chunk = tokens[i * ps:(i + 1) * ps]
-                h = page_hash(parent, chunk)
-                page = pool.lookup(h, parent, chunk)
+        if not self.prefix_caching or tokens is None:
+            return 0
+        ps = self.page_size
+        k, digests = self._shared_prefix_pages(tokens)
+        if k == 0:
+            return 0
+        held.digests = digests
+        for g, pages in zip(self.groups, held.pages):
+            first = self._first_needed_page(g, k * ps)
+            pages += [-1] * first                        # what the window has passed is never read
+            for i in range(first, k):
+                page = g.pool.adopt(digests[i], digests[i - 1] if i else None, tokens[i * ps:(i + 1) * ps])
                 if page is None:
-                    break
+                    raise CacheError(f"published page {i} of group {g.index} vanished during admission")
                 pages.append(page)
-                held.hashes.append(h)
-                parent = h
-            if pages and len(pages) * ps == len(tokens):       # fully cached: recompute the last page
-                pool.free([pages.pop()])
-                held.hashes.pop()
-            cached = len(pages) * ps
-            self._write_table(0, held.slot, 0, pages)
-        return cached
+            held.offered[g.index] = k
+            self._write_table(g.index, held.slot, first, pages[first:])
+        return k * ps
 
     def _first_needed_page(self, g: PageGroup, start: int) -> int:
         """Index of the first page a query at position >= `start` can still read."""
@@ -204,7 +260,7 @@ class CacheManager:
             return False
         for g, n, pages in zip(self.groups, need, held.pages):
             if n:
-                got = g.pool.allocate(n)
+                got = g.pool.take(n)
                 first = len(pages)
                 pages += got
                 self._write_table(g.index, held.slot, first, got)
@@ -217,27 +273,27 @@ class CacheManager:
             first = min(self._first_needed_page(g, start), len(pages))
             gone = [(i, p) for i, p in enumerate(pages[:first]) if p >= 0]
             if gone:
-                g.pool.free([p for _, p in gone])
+                g.pool.drop([p for _, p in gone])
                 self._touch(g)
                 for i, _ in gone:
                     pages[i] = -1
                     g.table[held.slot, i] = g.scratch_page
 
     def advance(self, rid, num_computed: int, tokens) -> None:
-        """After a step: publish the pages that are now full and computed
-        (tensorline/batch_engine.py:282-290) and give back pages behind every window."""
+        """After a step: offer the pages that are now full and computed for sharing, in every group
+        that still holds them (only full pages whose tokens are all computed:
+        tensorline/batch_engine.py:282-290), then give back the pages behind every window."""
         held = self._held[rid]
+        if self.prefix_caching and tokens is not None:
+            ps = self.page_size
+            full = min(num_computed, len(tokens)) // ps
+            digests = self._chain(tokens, full, held.digests)
+            for g, pages in zip(self.groups, held.pages):
+                for i in range(held.offered[g.index], full):
+                    if pages[i] >= 0:
+                        g.pool.publish(pages[i], digests[i], digests[i - 1] if i else None, tokens[i * ps:(i + 1) * ps])
+                held.offered[g.index] = max(held.offered[g.index], full)
         self._release_behind_window(held, num_computed)
-        if not self.prefix_caching:
-            return
-        ps, pool, pages = self.page_size, self.groups[0].pool, held.pages[0]
-        while len(held.hashes) < min(num_computed, len(tokens)) // ps:
-            i = len(held.hashes)
-            parent = held.hashes[-1] if i else None
-            chunk = tokens[i * ps:(i + 1) * ps]
-            h = page_hash(parent, chunk)
-            held.hashes.append(h)
-            pool.register(pages[i], h, parent, chunk)
 
     def release(self, rid) -> None:
         """Give back everything `rid` holds: pages of every group and its slot
@@ -246,7 +302,7 @@ class CacheManager:
         if held is None:
             raise CacheError(f"request {rid!r} released but not admitted (double release)")
         for g, pages in zip(self.groups, held.pages):
-            g.pool.free([p for p in pages if p >= 0])
+            g.pool.drop([p for p in pages if p >= 0])
             self._touch(g)
             g.table[held.slot, :] = g.scratch_page
         self._free_slots.append(held.slot)

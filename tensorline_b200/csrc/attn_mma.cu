@@ -831,22 +831,26 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
 template <int PBN> constexpr int prefill_smem() { return (BM + 4 * PBN) * DP * 2; }
 constexpr int DECODE_SMEM_MAX = DECODE_TAB_OFFSET + DECODE_MAX_TAB * 4;
 
-int g_attr_done = 0;
+bool g_attr_done[TL_MAX_DEVICES] = {};        // kernel attributes belong to a device: each one is set up at its first call
 int set_attrs() {
-    if (g_attr_done) return 0;
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (g_attr_done[dev]) return 0;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<32>());
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, prefill_smem<64>());
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM_MAX);
     if (e != cudaSuccess) return (int)e;
-    g_attr_done = 1;
+    g_attr_done[dev] = true;
     return 0;
 }
 
 }  // namespace
 
 TL_EXPORT int tl_attn_head_dim() { return D; }
+// Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
+TL_EXPORT int tl_attn_decode_max_table() { return DECODE_MAX_TAB; }
 
 // total_tiles = sum over requests of ceil(q_len * g / 64), computed by the caller.
 TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
@@ -906,7 +910,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
-bool g_tma_attr_done = false;
+bool g_tma_attr_done[TL_MAX_DEVICES] = {};
 
 // The cache tensor [pages, nkv, page, D] as rows of D elements; a box is one page of one KV head, 64 wide.
 int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
@@ -947,14 +951,16 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     const int tab_entries = chunk / page_size;
     if (tab_entries > DECODE_MAX_TAB) return 1;
     const int smem = TMA_TAB_OFFSET + tab_entries * 4 + 1024;
-    if (!g_tma_attr_done) {
+    const int dev_index = tl_device_index();
+    if (dev_index < 0) return 1;
+    if (!g_tma_attr_done[dev_index]) {
         cudaError_t ce = cudaFuncSetAttribute(attn_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
         if (ce == cudaSuccess)
             ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
         if (ce != cudaSuccess) return (int)ce;
-        g_tma_attr_done = true;
+        g_tma_attr_done[dev_index] = true;
     }
     int e = set_attrs();                                   // the combine kernel's library state
     if (e) return e;
@@ -1005,7 +1011,7 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
 static __device__ __align__(256) float g_static_partials[TL_ATTN_STATIC_SCRATCH_FLOATS];
 
 namespace {
-constexpr int MAX_DEVICES = 64;
+constexpr int MAX_DEVICES = TL_MAX_DEVICES;
 float* g_static_ptr[MAX_DEVICES] = {};      // device address of the array, per device, set at the first call
 
 int fail(char* err, int err_len, int code, const char* msg) {

@@ -14,9 +14,13 @@
 //     Every GPU on which a process loads this library holds those 4 MiB until the process exits.
 //   * A call needs B * nq * splits * (head_dim + 2) floats when splits > 1 (none when splits == 1).
 //     Larger requests are refused with a message; nothing is launched.  Use fewer splits.
-//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
-//     that device current) and raises the kernels' shared-memory limit.  Make that first call
-//     outside any stream capture; later calls do no set-up.
+//   * The key ranges must cover the longest context of the call: chunk * splits >= the largest
+//     start_pos[b] + 1, rounded up to a multiple of 64 (with a window: the window + 63).  The lengths
+//     live on the device, so this entry point cannot check it; keys beyond chunk * splits are not read
+//     and the result is then wrong without an error.
+//   * The first call on each device (with that device current) looks up the array's device address
+//     (cudaGetSymbolAddress) and raises the kernels' shared-memory limit on that device.  Make that
+//     first call outside any stream capture; later calls on the device do no set-up.
 //   * All calls on a device share the one array, and it keeps whatever the last call left in it.
 //     Nothing in it has to start at zero: a call reads only the partials that the same call wrote.
 //     Two calls whose kernels overlap on the GPU (different streams, no ordering between them) race

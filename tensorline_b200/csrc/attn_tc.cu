@@ -802,7 +802,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
-bool g_attr2_done = false;
+bool g_attr2_done[TL_MAX_DEVICES] = {};
 
 // The cache tensor [pages, nkv, page, D] as rows of D elements; a box is one page of one KV head, 64 wide.
 int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
@@ -817,7 +817,7 @@ int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_
 }
 #endif  // HEAD_DIM <= 128
 
-bool g_attr_done = false;
+bool g_attr_done[TL_MAX_DEVICES] = {};
 
 }  // namespace
 
@@ -830,10 +830,12 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
                                  float scale, int total_tiles, int* status, const int* order, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
     if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size * 32 < BN || page_size > 64 || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
-    if (!g_attr_done) {
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (!g_attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        g_attr_done = true;
+        g_attr_done[dev] = true;
     }
     TcAttnArgs A{};
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
@@ -865,10 +867,12 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
             qres != cudaDriverEntryPointSuccess) return 100;
         g_encode = (EncodeTiledFn)fn;
     }
-    if (!g_attr2_done) {
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (!g_attr2_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc2_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
         if (e != cudaSuccess) return (int)e;
-        g_attr2_done = true;
+        g_attr2_done[dev] = true;
     }
     CUtensorMap mk, mv;
     const long long rows = total_pages * nkv * page_size;

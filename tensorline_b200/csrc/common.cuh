@@ -71,6 +71,27 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 static inline int tl_launch_status() { return (int)cudaGetLastError(); }
 
+// Host-side state that belongs to a device (kernel attributes that were set, addresses that were looked up) is
+// kept per device index, so a process that uses several GPUs sets each of them up.
+constexpr int TL_MAX_DEVICES = 64;
+static inline int tl_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TL_MAX_DEVICES) return -1;
+    return dev;
+}
+// Streaming multiprocessors of the current device, asked once per device.
+static inline int tl_num_sms() {
+    static int count[TL_MAX_DEVICES] = {};
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 1;
+        count[dev] = n;
+    }
+    return count[dev];
+}
+
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
 // the kernel before it in the stream is still running; its blocks run their set-up and then stop in
 // grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched

@@ -273,7 +273,8 @@ TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I
         return launch_after_wait(silu_mul_vec8_kernel<1>, dim3((unsigned)((I / 8 + 255) / 256), (unsigned)T), dim3(threads), 0, stream,
                                  (const bf16*)gu, (bf16*)out, I, blk);
     }
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const size_t cap = (size_t)tl_num_sms() * 16;
+    const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
     if (act_dtype == TL_F32)
         silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total);
     else

@@ -19,6 +19,8 @@
 // records an error code in `status`, stops issuing work, frees its tensor memory and returns.
 #include "common.cuh"
 #include <cuda.h>
+#include <mutex>
+#include <unordered_map>
 
 namespace {
 
@@ -26,7 +28,7 @@ constexpr int BM = 128;                // rows of A per tile = MMA M
 constexpr int BK = 64;                 // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long long WAIT_CYCLES = 4000000000LL;     // ~2 s at 2 GHz
+constexpr long long WAIT_CYCLES = 4000000000LL;     // ~2 s at 2 GHz; tl_gemm_tc_test_hooks can shorten it
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -46,13 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records `code`) if the barrier did not flip in time or another
 // role of the block already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;
@@ -118,6 +121,8 @@ struct GemmArgs {
                           // distributed shared memory: no pieces in global memory (swap = 1, 2..8 ranges)
     int gated;            // swap, one split: rows 0..63 of every 128-row tile of A are gate features, rows 64..127 the
                           // up features of the same 64 columns; out[b, 64 tile + j] = silu(gate) * up, [RB, RA / 2]
+    long long wait_cycles;   // how long a wait on a barrier may take before the block gives up
+    int drop_last_load;      // tests only: the copy thread leaves out its last stage, so the MMA thread's wait runs out
 };
 
 template <int BN, int STAGES>
@@ -161,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------------------------------------------------------- TMA producer
         // The weights are nobody's output: the first ring of weight tiles is requested before the wait for the
         // kernel that writes the activations, so the stream from memory is already running when that kernel ends.
-        const int ahead = n_kt < STAGES ? n_kt : STAGES;
+        const int ahead = (n_kt < STAGES ? n_kt : STAGES) - ((G.drop_last_load && n_kt <= STAGES) ? 1 : 0);
         for (int i = 0; i < ahead; ++i) {
             mbar_expect_tx(full_bar + i, STAGE_BYTES);
             unsigned char* st = tiles + i * STAGE_BYTES;
@@ -175,9 +180,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (G.swap) tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
             else        tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
         }
-        for (int i = ahead; i < n_kt; ++i) {
+        for (int i = ahead; i < n_kt - G.drop_last_load; ++i) {
             const int s = i % STAGES;
-            if (!mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1)) break;
+            if (!mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1, G.wait_cycles)) break;
             mbar_expect_tx(full_bar + s, STAGE_BYTES);
             unsigned char* st = tiles + s * STAGE_BYTES;
             tma_load_2d(st, &map_a, full_bar + s, (kt_begin + i) * BK, a0);
@@ -190,7 +195,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         grid_dependency_wait();                          // the bounded waits below start counting once the copies can land
         for (int i = 0; i < n_kt && ok; ++i) {
             const int s = i % STAGES;
-            ok = mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, G.status, 2);
+            ok = mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, G.status, 2, G.wait_cycles);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_addr = smem_addr(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
@@ -204,7 +209,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp >= 2) {
         // ---------------------------------------------------------------- epilogue: 4 warps, 32 lanes of TMEM each
         grid_dependency_wait();                          // the output may still be read by the kernel before
-        if (mbar_wait(done_bar, 0, abort_flag, G.status, 3)) {
+        if (mbar_wait(done_bar, 0, abort_flag, G.status, 3, G.wait_cycles)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3;                // the TMEM lanes a warp may read: 32 * (warp % 4)
             const int a = a0 + quarter * 32 + lane;      // row of A = TMEM lane
@@ -416,14 +421,48 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
     return r == CUDA_SUCCESS ? 0 : 101;
 }
 
+// Encoding a tensor map costs the host a microsecond or two; the same (matrix, box) pairs come back with every
+// step (weights always, activations whenever the allocator hands out the same block), so maps are kept by key.
+struct MapKey {
+    const void* base; int rows, K, box_rows;
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && K == o.K && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= ((size_t)(unsigned)k.rows << 32 | (unsigned)k.K) + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+        return h ^ ((size_t)k.box_rows * 0xC2B2AE3D27D4EB4Full);
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_lock;
+constexpr size_t MAP_CACHE_ENTRIES = 8192;
+
+int cached_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    const MapKey key{base, rows, K, box_rows};
+    std::lock_guard<std::mutex> hold(g_maps_lock);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *map = it->second; return 0; }
+    const int e = make_map(map, base, rows, K, box_rows);
+    if (e) return e;
+    if (g_maps.size() >= MAP_CACHE_ENTRIES) g_maps.clear();
+    g_maps.emplace(key, *map);
+    return 0;
+}
+
+long long g_wait_cycles = WAIT_CYCLES;
+int g_drop_last_load = 0;
+
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3 grid, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM + BN) * BK * 2 + 1024 + (2 * STAGES + 1) * 8 + 32;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[TL_MAX_DEVICES] = {};
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_set[dev] = true;
     }
     if (G.cluster_reduce) {
         cudaLaunchConfig_t cfg = {};
@@ -462,8 +501,8 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     const void* b = swap ? x : w;
     const int RA = swap ? N : T, RB = swap ? T : N;
     CUtensorMap ma, mb;
-    if ((e = make_map(&ma, a, RA, K, BM))) return e;
-    if ((e = make_map(&mb, b, RB, K, bn))) return e;
+    if ((e = cached_map(&ma, a, RA, K, BM))) return e;
+    if ((e = cached_map(&mb, b, RB, K, bn))) return e;
     const int k_tiles = (K + BK - 1) / BK;
     if (splits > k_tiles) splits = k_tiles;
     const int per = (k_tiles + splits - 1) / splits;
@@ -476,6 +515,7 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     if (cluster_reduce && (!swap || splits > 8 || y == nullptr)) return 1;
     G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
+    G.wait_cycles = g_wait_cycles; G.drop_last_load = g_drop_last_load;
     dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return 1;
     G.counters = (splits > 1 && counters != nullptr && (long long)grid.x * grid.y <= n_counters) ? counters : nullptr;
@@ -489,8 +529,18 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     }
     if (e || splits == 1 || G.counters != nullptr || y == nullptr || G.cluster_reduce) return e;      // y null: the caller sums the pieces
     const size_t total = (size_t)T * N;
-    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    const size_t cap = (size_t)tl_num_sms() * 8;
+    const int blocks = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
     return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (void*)y, out_f32, splits, T, N, ldo);
+}
+
+// For tests of the failure path only.  `wait_cycles` > 0: how many clock cycles a wait on a barrier may take from
+// now on (0: back to the default of about two seconds).  `drop_last_load` = 1: the copy thread of every block leaves
+// out its last stage of operands, so the MMA thread's bounded wait for it runs out, the block records status 2,
+// frees its tensor memory and returns with invalid output; nothing is left in flight.  Never set in serving.
+TL_EXPORT void tl_gemm_tc_test_hooks(long long wait_cycles, int drop_last_load) {
+    g_wait_cycles = wait_cycles > 0 ? wait_cycles : WAIT_CYCLES;
+    g_drop_last_load = drop_last_load ? 1 : 0;
 }
 
 // out[T, ldo] = the sum of the S pieces partial[S][T][N] in split order, converted.
@@ -498,6 +548,7 @@ TL_EXPORT int tl_splitk_reduce(const float* partial, void* y, int out_f32, int s
                                cudaStream_t stream) {
     const size_t total = (size_t)T * N;
     if (total == 0) return 0;
-    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    const size_t cap = (size_t)tl_num_sms() * 8;
+    const int blocks = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
     return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partial, y, out_f32, splits, T, N, ldo);
 }

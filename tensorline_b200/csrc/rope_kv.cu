@@ -8,6 +8,11 @@
 // k and the biased v go to the page `table[slot][pos / page]` at offset `pos % page`
 // (tensorline/paged.py:202, :252-253).  Pages are laid out [page, kv head, offset, d] so that one
 // head's part of a page is contiguous.
+//
+// Two options of other position encodings and mixers are arguments, not copies of the kernel: the pairing of
+// the rotated dimensions (`interleaved`: pair i is dimensions (2i, 2i + 1) instead of (i, i + rot/2)), and an
+// RMS norm of every q and k head over its d dimensions with a weight of its own (`q_norm`, `k_norm`, `norm_eps`),
+// applied after the bias and before the rotation, statistics in float.
 #include "common.cuh"
 
 // grid (T, heads): one block per (token, head), one thread per pair of dimensions, so that all loads
@@ -17,7 +22,9 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
                                const int* __restrict__ pos, const int* __restrict__ req_slot,
                                const int* __restrict__ table, int max_pages, int page_size,
                                const float* __restrict__ inv_freq, int rot, int nq, int nkv, int d,
-                               TA* __restrict__ k_pages, TA* __restrict__ v_pages) {
+                               TA* __restrict__ k_pages, TA* __restrict__ v_pages, int interleaved,
+                               const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps) {
+    __shared__ float red[33];
     const int t = blockIdx.x, hh = blockIdx.y;
     const int p = pos[t];
     const int half = d >> 1, rhalf = rot >> 1;
@@ -30,13 +37,29 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
               (((size_t)page * nkv + kh) * page_size + (p % page_size)) * d;
     }
     const bool rotate_head = hh < nq + nkv;
+    const float* nw = !rotate_head ? nullptr : (hh < nq ? q_norm : k_norm);
+    float rstd = 1.0f;
+    if (nw) {                                                    // RMS over the head: sum of squares of the biased values
+        float ss = 0.f;
+        for (int e = threadIdx.x; e < d; e += blockDim.x) {
+            float v = to_f<TA>(row[e]);
+            if (bias) v += to_f<TW>(bias[hh * d + e]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, red);
+        rstd = 1.0f / sqrtf(ss / (float)d + norm_eps);
+    }
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         int e1, e2;
-        if (i < rhalf) { e1 = i; e2 = i + rhalf; }
+        if (i < rhalf) { e1 = interleaved ? 2 * i : i; e2 = interleaved ? 2 * i + 1 : i + rhalf; }
         else           { e1 = rot + 2 * (i - rhalf); e2 = e1 + 1; }
         float a = to_f<TA>(row[e1]);
         float b = to_f<TA>(row[e2]);
         if (bias) { a += to_f<TW>(bias[hh * d + e1]); b += to_f<TW>(bias[hh * d + e2]); }
+        if (nw) {                                                // cast before the weight, as the layer norms do
+            a = to_f<TA>(from_f<TA>(a * rstd)) * nw[e1];
+            b = to_f<TA>(from_f<TA>(b * rstd)) * nw[e2];
+        }
         if (rotate_head && i < rhalf) {
             float s, c;
             sincosf(__fmul_rn((float)p, inv_freq[i]), &s, &c);
@@ -158,14 +181,17 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
                                const int* pos, const int* req_slot, const int* table, int max_pages,
                                int page_size, const float* inv_freq, int rot, int nq, int nkv, int d,
                                void* k_pages, void* v_pages, int write_kv, int T, const float* pieces, int splits,
-                               long long plane, cudaStream_t stream) {
+                               long long plane, int interleaved, const float* q_norm, const float* k_norm,
+                               float norm_eps, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
     const int heads = write_kv ? nq + 2 * nkv : nq;
     if (heads > 65535) return 1;
     const bool aligned = ((((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)pieces | (uintptr_t)bias) & 15) == 0);
-    if (pieces && !(act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned)) return 1;   // pieces: the fast path only
-    if (act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned) {
+    if ((q_norm == nullptr) != (k_norm == nullptr)) return 1;
+    const bool plain = !interleaved && q_norm == nullptr;         // the fast path: rotate-half pairs, no q/k norm
+    if (pieces && !(plain && act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned)) return 1;   // pieces: the fast path only
+    if (plain && act_dtype == TL_BF16 && rot == d && (d & 15) == 0 && aligned) {
         const int items = heads * (d / 16);
         const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
         const size_t smem = (size_t)d * sizeof(float);
@@ -180,7 +206,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
     const int threads = half < 256 ? ((half + 31) / 32) * 32 : 256;
 #define LAUNCH(TA, TW) rope_kv_kernel<TA, TW><<<grid, threads, 0, stream>>>( \
         (TA*)qkv, (const TW*)bias, pos, req_slot, table, max_pages, page_size, inv_freq, rot, nq, nkv, d, \
-        (TA*)k_pages, (TA*)v_pages)
+        (TA*)k_pages, (TA*)v_pages, interleaved, q_norm, k_norm, norm_eps)
     if (act_dtype == TL_F32) { if (bias_dtype == TL_F32) LAUNCH(float, float); else LAUNCH(float, bf16); }
     else                     { if (bias_dtype == TL_F32) LAUNCH(bf16, float);  else LAUNCH(bf16, bf16); }
 #undef LAUNCH

@@ -390,7 +390,10 @@ TL_EXPORT int tl_sample(const float* logits, int ld, int R, int V, const float* 
     const size_t limit = 227 * 1024;
     const bool cached = sizeof(DrawShared) + (size_t)slice * 4 <= limit;
     const size_t smem = sizeof(DrawShared) + (cached ? (size_t)slice * 4 : 0);
-    static bool attr_done = false;
+    static bool attr_done_on[TL_MAX_DEVICES] = {};
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    bool& attr_done = attr_done_on[dev];
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(draw_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit);
         if (e == cudaSuccess)

@@ -27,7 +27,7 @@ from ..models import build_model, load_model
 from ..parts import Runtime
 from ..sampling import GenStats, Sampler, SamplingParams, draw_rows, request_seed
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, Scheduler
+from .scheduler import Request, Scheduler, Slice
 
 
 @dataclass
@@ -37,6 +37,14 @@ class Output:
     stats: GenStats
     text: str | None = None
     prompt_token_ids: list = field(default_factory=list)
+
+
+@dataclass
+class _StepInFlight:
+    """A decode step that is on the device while the host goes on: its requests, in row order, and the
+    runner's handle for its tokens."""
+    requests: list
+    handle: object
 
 
 def pick_device(requested: str = "auto") -> torch.device:
@@ -98,10 +106,11 @@ class Engine:
         eos = self.model.spec.eos_token_id
         self.default_stops = {eos} if eos is not None else set()     # tensorline/engine.py:76-77
         self._known_to_runner: set = set()
-        # Overlap (tensorline/batch_engine.py:478-533): in steady decoding the next step is launched from the
-        # tokens still on the device before the previous step's tokens are read back.
+        # Running ahead (the idea of tensorline/batch_engine.py:478-533): while the same requests keep
+        # decoding, the next step is started from the tokens still on the device before the host has
+        # seen the previous step's tokens.  At most one step is ahead of the host.
         self.overlap = bool(o.overlap and o.cuda_graphs)
-        self._inflight = None                            # (requests, DecodeHandle) of the step not yet read back
+        self._ahead: _StepInFlight | None = None
         self.overlapped_steps = 0
 
     # ------------------------------------------------------------------ requests
@@ -126,100 +135,101 @@ class Engine:
         self._sync_runner()
 
     def _sync_runner(self) -> None:
-        """Tell the runner which requests entered or left the cache since the last step."""
+        """Tell the runner which requests left the cache since the last step."""
         for rid in [r for r in self._known_to_runner if not self.cache.holds(r)]:
             self.runner.end_request(rid)
             self._known_to_runner.discard(rid)
 
-    # ------------------------------------------------------------------ overlap
-    def _launch(self, reqs, prev=None):
-        """Start a decode step for `reqs` without waiting for its tokens."""
-        entries = [StepEntry(r.rid, [r.tokens[-1] if prev is None else 0], [0]) for r in reqs]
-        ahead = 0 if prev is None else 1                 # the step in flight has one token of each request still to come
-        draw = draw_rows([(r.params, r.seed, r.num_generated + ahead) for r in reqs])
-        handle = self.runner.launch_decode(entries, None if prev is None else prev[1], draw)
-        self.scheduler.computed([(r, 1) for r in reqs])
-        return reqs, handle
+    # ------------------------------------------------------------------ decode steps that run ahead of the host
+    def _start_decode(self, reqs, after: "_StepInFlight | None" = None) -> "_StepInFlight":
+        """Put a decode step for `reqs` on the device and return without its tokens.  `after`: the step
+        of the same requests that is still in flight; its tokens, on the device, are this step's inputs."""
+        behind = 0 if after is None else 1               # tokens of each request the host has not seen yet
+        entries = [StepEntry(r.rid, [r.tokens[-1] if after is None else 0], [0]) for r in reqs]
+        draw = draw_rows([(r.params, r.seed, r.num_generated + behind) for r in reqs])
+        handle = self.runner.launch_decode(entries, None if after is None else after.handle, draw)
+        self.scheduler.computed([Slice(r, r.num_computed, 1) for r in reqs])
+        return _StepInFlight(list(reqs), handle)
 
-    def _resolve(self, inflight) -> list:
-        """Read a launched step's tokens back and accept them; a request that finished one step
-        earlier has produced one token too many, which is dropped (tensorline/batch_engine.py:500-508)."""
-        reqs, handle = inflight
-        toks = self.runner.read_tokens(handle)
+    def _collect(self, step: "_StepInFlight") -> list:
+        """Wait for a started step, check the device status that came back with it, and hand its tokens
+        to the scheduler.  A request that ended with the step before has produced one token too many,
+        which is dropped (tensorline/batch_engine.py:500-508)."""
+        toks = self.runner.read_tokens(step.handle)      # raises KernelError if a kernel gave up on a wait
         now = time.perf_counter()
-        out = []
-        for req, tok in zip(reqs, toks):
-            if not req.done and self.scheduler.accept(req, tok, now):
-                out.append((req, tok))
+        kept = [(req, tok) for req, tok in zip(step.requests, toks)
+                if not req.done and self.scheduler.accept(req, tok, now)]
         self._sync_runner()
-        return out
+        return kept
 
-    def _can_continue(self) -> bool:
-        """Whether the step after the one in flight can be launched before that one is read back
-        (tensorline/batch_engine.py:510-521): same requests, nobody near a limit, a page for one more
-        token each.  tzar-beep/Tensorline also asks for greedy requests; here sampled ones go on as well:
-        a draw's uniform number depends on (seed, token index) only, so it is known a step ahead, and the
-        sampling kernel runs on the device behind the decode graph."""
-        reqs = self._inflight[0]
+    def _may_run_ahead(self, step: "_StepInFlight") -> bool:
+        """Whether the step after `step` can be started before `step` is read: nothing waits, the running
+        set is exactly `step`'s requests, each has room for two more tokens under its limits, and the
+        cache has a place for one more token each (tensorline/batch_engine.py:510-521).
+        tzar-beep/Tensorline also asks for greedy requests; here sampled ones go on as well: a draw's
+        uniform number depends on (seed, token index) only, so it is known a step ahead, and the sampling
+        kernel runs on the device behind the decode graph."""
         sch = self.scheduler
-        if sch.waiting or len(sch.running) != len(reqs) or any(a is not b for a, b in zip(sch.running, reqs)):
+        if sch.waiting or len(sch.running) != len(step.requests):
             return False
-        for r in reqs:      # the pending token is appended when the step is read back; leave room for one more
-            if r.done or r.num_generated + 2 > r.params.max_tokens or len(r.tokens) + 2 > sch.max_model_len:
+        for mine, theirs in zip(step.requests, sch.running):
+            if mine is not theirs or mine.done:
                 return False
-        return all(self.cache.grow(r.rid, r.num_computed, r.num_computed + 1) for r in reqs)
+            if mine.num_generated + 2 > mine.params.max_tokens or len(mine.tokens) + 2 > sch.max_model_len:
+                return False
+        return all(self.cache.grow(r.rid, r.num_computed, r.num_computed + 1) for r in step.requests)
 
     def flush(self) -> list:
         """Read back the step in flight, if any."""
-        if self._inflight is None:
+        if self._ahead is None:
             return []
-        prev, self._inflight = self._inflight, None
-        return self._resolve(prev)
+        step, self._ahead = self._ahead, None
+        return self._collect(step)
 
     # ------------------------------------------------------------------ one iteration
     def step(self) -> list:
         """Schedule, run one batch, sample, finish.  Returns [(request, token)] for the tokens that
         became known in this call (with overlap on, a decode step's tokens arrive one call later)."""
-        sch = self.scheduler
         try:
-            if self._inflight is not None:
-                if self._can_continue():
-                    prev = self._inflight
-                    self._inflight = self._launch(prev[0], prev)
-                    self.overlapped_steps += 1
-                    return self._resolve(prev)
-                return self.flush()
-            plan = sch.schedule()
-            self._sync_runner()
-            if not plan:
-                return []
-            entries = []
-            for req, n in plan:
-                if req.rid not in self._known_to_runner or self.runner.positions.get(req.rid) != req.num_computed:
-                    self.runner.start_request(req.rid, req.num_computed)      # new, or back after a preemption
-                    self._known_to_runner.add(req.rid)
-                end = req.num_computed + n
-                want = [n - 1] if end == len(req.tokens) else []      # tensorline/batch_engine.py:376
-                entries.append(StepEntry(req.rid, req.tokens[req.num_computed:end], want))
-            if self.overlap and self.runner.can_replay(entries):
-                self._inflight = self._launch([r for r, _ in plan])      # its tokens are read at the next call
-                return []
-            sampled = [req for (req, n), e in zip(plan, entries) if e.want]
-            rows = [(r.params, r.seed, r.num_generated) for r in sampled]
-            tokens = self.runner.step_and_sample(entries, self.sampler, rows)
-            sch.computed(plan)
-            now = time.perf_counter()
-            out = []
-            for req, tok in zip(sampled, tokens):
-                if sch.accept(req, tok, now):
-                    out.append((req, tok))
-            self._sync_runner()
-            return out
-        except Exception as e:                                       # tensorline/batch_engine.py:568-576
-            self._inflight = None
-            sch.fail_all(e)
+            if self._ahead is not None:
+                if not self._may_run_ahead(self._ahead):
+                    return self.flush()
+                earlier = self._ahead
+                self._ahead = self._start_decode(earlier.requests, after=earlier)
+                self.overlapped_steps += 1
+                return self._collect(earlier)
+            return self._scheduled_step()
+        except Exception as e:                           # tensorline/batch_engine.py:568-576
+            self._ahead = None
+            self.scheduler.fail_all(e)
             self._sync_runner()
             raise
+
+    def _scheduled_step(self) -> list:
+        sch = self.scheduler
+        plan = sch.schedule()
+        self._sync_runner()
+        if not plan:
+            return []
+        entries = []
+        for sl in plan:
+            rid = sl.request.rid
+            if rid not in self._known_to_runner or self.runner.positions.get(rid) != sl.start:
+                self.runner.start_request(rid, sl.start)             # new, or back after a preemption
+                self._known_to_runner.add(rid)
+            entries.append(StepEntry(rid, sl.tokens, [sl.count - 1] if sl.wants_logits else []))
+        if self.overlap and self.runner.can_replay(entries):
+            self._ahead = self._start_decode([sl.request for sl in plan])     # its tokens are read at the next call
+            return []
+        sampled = [sl.request for sl in plan if sl.wants_logits]
+        rows = [(r.params, r.seed, r.num_generated) for r in sampled]
+        tokens = self.runner.step_and_sample(entries, self.sampler, rows)
+        self.runner.check_device_status()
+        sch.computed(plan)
+        now = time.perf_counter()
+        kept = [(req, tok) for req, tok in zip(sampled, tokens) if sch.accept(req, tok, now)]
+        self._sync_runner()
+        return kept
 
     def generate(self, prompts, params: SamplingParams | list | None = None) -> list:
         """Run the prompts to completion; returns one `Output` per prompt, in order."""

@@ -106,8 +106,11 @@ class ModelRunner:
         self.graph_replays = 0
         self._graphs: dict = {}
         self._graph_pool = None
-        self._graphable = all(isinstance(c, KVCacheView) for c in self.caches.values())
-        self._token_hosts = [torch.zeros(cache.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        # State of fixed size lives at fixed addresses indexed by slot (padding rows use the spare row), so a
+        # model with such state is captured like any other, as long as its parts read the step from device
+        # tensors only (`Part.graph_capturable`).
+        self._graphable = model.graph_capturable()
+        self._token_hosts = [torch.zeros(cache.max_num_seqs + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._flip = 0
         # temperature, top-p and uniform number per row for steps that sample on the device without waiting
         self._draw_hosts = [torch.zeros(3, cache.max_num_seqs, dtype=torch.float32).pin_memory() for _ in range(4)]
@@ -164,9 +167,9 @@ class ModelRunner:
                 raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
             start = self.positions[e.rid]
             slot = self.cache.slot(e.rid)
-            held = len(self.cache._held[e.rid].pages[0]) * ps if self.cache.groups else start + n
-            if start + n > held:
-                raise RuntimeError(f"request {e.rid!r}: positions up to {start + n} but pages for {held}; "
+            room = self.cache.capacity(e.rid)
+            if start + n > room:
+                raise RuntimeError(f"request {e.rid!r}: positions up to {start + n} but pages for {room}; "
                                    "grow its cache before the step")
             row0 = len(ids)
             ids.extend(int(t) for t in e.tokens)
@@ -221,7 +224,10 @@ class ModelRunner:
             g = self._run_graph(entries)
             n = len(entries)
             if all(p.temperature <= 0 for p, _, _ in rows):
-                return g.tokens[:n].tolist()
+                got = g.tokens.tolist()
+                if got[-1] != 0:
+                    ops.raise_device_status(self.device, got[-1])
+                return got[:n]
             return sampler.sample(g.logits[:n], rows)
         logits = self.step(entries)
         return sampler.sample(logits, rows)
@@ -255,11 +261,13 @@ class ModelRunner:
                           page_size=self.page_size, decode_only=True, max_q_len=1, max_ctx=self.cache.max_model_len,
                           h_q_start=list(range(nb + 1)), h_start_pos=[0] * nb, h_slots=[pad] * nb,
                           force_exact_attention=self.force_exact_attention, graph_max_ctx=self.cache.max_model_len)
-        tokens = torch.zeros(nb, dtype=torch.int32, device=dev)
+        tokens = torch.zeros(nb + 1, dtype=torch.int32, device=dev)     # the rows' tokens, then the device status word
+        status = ops.device_status(dev)
 
         def run():
             logits = self.model.forward(ctx, self.caches)
-            ops.argmax(logits, tokens)
+            ops.argmax(logits, tokens[:nb])
+            tokens[nb:].copy_(status[:1])                    # a wait that ran out inside a kernel travels with the tokens
             return logits
 
         side = torch.cuda.Stream(device=dev)
@@ -317,15 +325,26 @@ class ModelRunner:
             d = self._draw_dev
             ops.sample(g.logits[:n], d[0, :n], d[1, :n], d[2, :n], g.tokens[:n])
         self._flip ^= 1
-        host = self._token_hosts[self._flip][:n]
-        host.copy_(g.tokens[:n], non_blocking=True)
+        host = self._token_hosts[self._flip][:g.batch + 1]
+        host.copy_(g.tokens, non_blocking=True)              # one copy: the bucket's tokens and the status word
         ev = torch.cuda.Event()
         ev.record()
         return DecodeHandle(g, n, host, ev)
 
     def read_tokens(self, handle) -> list:
+        """The tokens of a launched step, once it has finished.  Raises `KernelError` if a kernel of the
+        step (or of an earlier one) gave up on a wait: its output is not valid."""
         handle.event.synchronize()
-        return handle.host.tolist()
+        got = handle.host.tolist()
+        if got[-1] != 0:
+            ops.raise_device_status(self.device, got[-1])
+        return got[:handle.n]
+
+    def check_device_status(self) -> None:
+        """After an eager step whose results the host has already waited for: raise `KernelError` if a
+        kernel gave up on a wait (a synchronising read of one word; a no-op for engines whose kernels
+        have no such waits)."""
+        ops.check_device_status(self.device)
 
     @torch.inference_mode()
     def _run_graph(self, entries, dev_ids=None):
@@ -345,7 +364,7 @@ class ModelRunner:
         for i, e in enumerate(entries):
             p = self.positions[e.rid]
             slot = self.cache.slot(e.rid)
-            if p + 1 > len(self.cache._held[e.rid].pages[0]) * self.page_size:
+            if p + 1 > self.cache.capacity(e.rid):
                 raise RuntimeError(f"request {e.rid!r}: no page for position {p}; grow its cache before the step")
             h[i] = e.tokens[0]
             h[nb + i] = p

@@ -14,7 +14,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts import BLOCKS, NORMS, POSITION_ENCODINGS, Embedding, KVCacheView, LMHead, PartSpec, Runtime
+from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITION_ENCODINGS, KVCacheView, PartSpec, Runtime
 
 
 @dataclass(frozen=True)
@@ -44,6 +44,8 @@ class ModelSpec:
     embedding_position_prefix: str = "model.embed_positions"     # where its tensors live, if it has any
     eos_token_id: int | None = None
     max_position_embeddings: int | None = None
+    embedding: PartSpec = PartSpec("token_table")     # built with vocab= and dim=; another kind may scale its rows
+    head: PartSpec = PartSpec("linear")               # built with vocab=, dim= and tied=; another kind may add a bias or a cap
 
 
 class Model:
@@ -51,10 +53,10 @@ class Model:
 
     def __init__(self, spec: ModelSpec, rt: Runtime):
         self.spec, self.rt = spec, rt
-        self.embedding = Embedding(rt, spec.vocab_size, spec.hidden_size)
+        self.embedding = EMBEDDINGS.build(spec.embedding, rt, vocab=spec.vocab_size, dim=spec.hidden_size)
         self.blocks = [BLOCKS.build(l.block, rt) for l in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, rt)
-        self.head = LMHead(rt, spec.vocab_size, spec.hidden_size, spec.tie_word_embeddings)
+        self.head = HEADS.build(spec.head, rt, vocab=spec.vocab_size, dim=spec.hidden_size, tied=spec.tie_word_embeddings)
         self.embedding_position = (POSITION_ENCODINGS.build(spec.embedding_position, rt)
                                    if spec.embedding_position else None)
         for i, e in enumerate(spec.run):
@@ -94,6 +96,14 @@ class Model:
                 if need is not None:
                     needs[i] = need
         return needs
+
+    def graph_capturable(self) -> bool:
+        """Whether a step of single tokens can be captured in a CUDA graph: every part reads the step from
+        device tensors only."""
+        parts = [self.embedding, self.final_norm, self.head, *self.blocks]
+        if self.embedding_position is not None:
+            parts.append(self.embedding_position)
+        return all(getattr(p, "graph_capturable", False) for p in parts)
 
     # ---- one step
     def forward(self, ctx, caches: dict) -> torch.Tensor:

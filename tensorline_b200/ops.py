@@ -20,7 +20,8 @@ _SIGNATURES = {
     "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
-    "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong, _P],
+    "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
+                         _I, _P, _P, _F, _P],
     "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
@@ -86,6 +87,62 @@ def _check(status: int, what: str, launches: int = 1) -> None:
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status} at launch")
     _launches += launches
+
+
+# ---------------------------------------------------------------------------------------------
+# The device status word.  Kernels that wait on barriers (the tcgen05 products and attention, the TMA
+# decode attention) bound every wait; a block whose wait runs out records a code here, stops and leaves
+# output that is not valid.  The engine reads the word where the host waits for a step anyway (it
+# travels with the sampled tokens) and fails the step's requests.
+
+N_COUNTERS = 8192
+_status: dict = {}
+STATUS_ROLES = {1: "tcgen05 product: the copy thread waited for a free stage", 2: "tcgen05 product: the MMA thread waited for a stage's copies",
+                3: "tcgen05 product: the epilogue waited for the accumulator", 20: "decode attention: a wait for a stage of keys and values"}
+
+
+def device_status(device) -> torch.Tensor:
+    """int32 [1 + N_COUNTERS] on `device`: [0] is the status word (0 = no wait ran out), the rest are the
+    per-tile arrival counters of split products (zero between calls)."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    t = _status.get(device)
+    if t is None:
+        t = torch.zeros(1 + N_COUNTERS, dtype=torch.int32, device=device)
+        _status[device] = t
+    return t
+
+
+def raise_device_status(device, code: int) -> None:
+    """Clear the word and raise: a wait ran out inside a kernel."""
+    device_status(device)[:1].zero_()
+    what = STATUS_ROLES.get(int(code), "an attention kernel's pipeline wait" if int(code) >= 10 else "a pipeline wait")
+    raise KernelError(f"a kernel on {device} gave up on a wait that did not complete in time (code {int(code)}: {what}); "
+                      "the step's output is not valid")
+
+
+def check_device_status(device=None) -> None:
+    """Raise if any kernel launched so far gave up on a wait (synchronises; reads one word per device
+    that has one)."""
+    for dev, t in list(_status.items()):
+        code = int(t[0].item())
+        if code:
+            raise_device_status(dev, code)
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device)."""
+    dev = None if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return n
+
+
+_sm_counts: dict = {}
 
 
 def _contig(t: torch.Tensor, name: str) -> None:
@@ -162,12 +219,25 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None) -> N
 def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tensor, req_slot: torch.Tensor,
                   table: torch.Tensor, page_size: int, inv_freq: torch.Tensor, rot: int, nq: int, nkv: int,
                   d: int, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True,
-                  pieces: torch.Tensor | None = None) -> None:
+                  pieces: torch.Tensor | None = None, pairing: str = "half", q_norm: torch.Tensor | None = None,
+                  k_norm: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
     """Bias, rotary encoding of q and k in place, and the write of k, v into their pages.
+    `pairing`: "half" rotates dimensions (i, i + rot/2), "interleaved" (2i, 2i + 1).  `q_norm`, `k_norm`
+    (float32 [d], both or neither): every q and k head is RMS-normalised over its d dimensions (after the
+    bias, before the rotation; statistics in float32) and multiplied by the weight.
     `pieces` [S, T, width] float32: the projection as a split-K product left it; the kernel sums them
     (bfloat16, full rotary, d % 16 == 0 only) and qkv is output only (its q columns are written)."""
     T = qkv.shape[0]
     splits = plane = 0
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"rope_kv_write: pairing {pairing!r} is neither 'half' nor 'interleaved'")
+    if (q_norm is None) != (k_norm is None):
+        raise KernelError("rope_kv_write: q_norm and k_norm come together")
+    for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != d or not w.is_contiguous()):
+            raise KernelError(f"rope_kv_write: {name} must be float32 [d]")
+    if pieces is not None and (pairing != "half" or q_norm is not None):
+        raise KernelError("rope_kv_write: pieces go with rotate-half pairing and no q/k norm")
     if pieces is not None:
         if (pieces.dtype != torch.float32 or pieces.dim() != 3 or pieces.shape[1:] != qkv.shape
                 or qkv.dtype != torch.bfloat16 or rot != d or d % 16):
@@ -188,7 +258,8 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
         _ptr(qkv), dtype_code(qkv.dtype), _ptr(bias), dtype_code(bias.dtype) if bias is not None else 0,
         _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(inv_freq), rot, nq, nkv, d,
         _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T,
-        _ptr(pieces), splits, plane, _stream()), "rope_kv_write")
+        _ptr(pieces), splits, plane, int(pairing == "interleaved"), _ptr(q_norm), _ptr(k_norm), float(norm_eps),
+        _stream()), "rope_kv_write")
 
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

@@ -12,13 +12,14 @@ import os
 import torch
 
 from .csrc.build import load_library
+from . import ops
 from .ops import KernelError, _check, _ptr, _stream
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _libs: dict = {}
 
-NUM_SMS = 148
 KEY_TILE = 64
+DECODE_MAX_TABLE_ENTRIES = 2048     # block-table entries a decode block copies to shared memory (`tl_attn_decode_max_table`)
 TC_PREFILL = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: mma.sync attention only (A/B timing)
 
 
@@ -40,6 +41,9 @@ def attn_lib(head_dim: int):
         lib.tl_attn_decode_tma.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _P, _P, _P, _I, _P]
         lib.tl_attn_decode_tma.restype = ctypes.c_int
+        if lib.tl_attn_decode_max_table() != DECODE_MAX_TABLE_ENTRIES:
+            raise KernelError(f"the attention library copies {lib.tl_attn_decode_max_table()} block-table entries a block, "
+                              f"the split planner assumes {DECODE_MAX_TABLE_ENTRIES}")
         _libs[head_dim] = lib
     return lib
 
@@ -146,13 +150,17 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     return True
 
 
-def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128, max_splits: int = 128) -> tuple:
+def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128, max_splits: int = 128,
+                page_size: int = 16, sms: int | None = None) -> tuple:
     """(chunk, splits) for a decode step; `span` is the largest number of keys a request can read.
     A block streams its range of keys tile by tile (64 keys), and a tile costs it about a microsecond
     whatever else runs, so a request's keys are cut into ranges until the blocks fill the GPU's resident
     slots once (a second, partly filled round would double the time) - but not finer than four tiles a
     range (two when that leaves 64 blocks or fewer), below which the merge of the partials costs more
-    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 4 -> 16, 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1."""
+    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 4 -> 16, 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1.
+    A block copies its range's block-table entries to shared memory, DECODE_MAX_TABLE_ENTRIES at most: a range is
+    never longer than that many pages, whatever the rules above say (long contexts on small pages get more ranges)."""
+    NUM_SMS = sms or ops.num_sms()
     m_tiles = -(-group // 16)
     tiles = max(1, -(-span // KEY_TILE))
     base = max(1, batch * nkv * m_tiles)
@@ -164,6 +172,8 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     if 8 < splits <= 12:
         splits = 8          # eight ranges merge inside a cluster; measured at batch 8, 8 k to 32 k keys: 27 / 46 / 86 against 30 / 49 / 88 us with nine
     chunk = -(-tiles // splits) * KEY_TILE
+    most = max(KEY_TILE, DECODE_MAX_TABLE_ENTRIES * page_size // KEY_TILE * KEY_TILE)
+    chunk = min(chunk, most)
     splits = -(-tiles * KEY_TILE // chunk)
     return chunk, splits
 
@@ -232,7 +242,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
         span = ctx.graph_max_ctx or ctx.max_ctx
         if window:
             span = min(span, window + KEY_TILE - 1)
-        chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span, d)
+        chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span, d, page_size=ctx.page_size)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
@@ -248,7 +258,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
             # query tile of the portion kernels would walk one request's whole context with 1 row in 18 used
             span = min(singles["span"], window + KEY_TILE - 1) if window else singles["span"]
             n = len(skip)
-            chunk, splits = plan_splits(n, nkv, g, span, d)
+            chunk, splits = plan_splits(n, nkv, g, span, d, page_size=ctx.page_size)
             part_o = part_ml = None
             if splits > 1:
                 part_o = torch.empty((n, nq, splits, d), dtype=torch.float32, device=qkv.device)
@@ -275,7 +285,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
             if key not in ctx.scratch:
                 ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, g, rows_per_tile, qkv.device, skip)
             return ctx.scratch[key]
-        if use_tc and TC_PAIR and pairs * nkv >= 0.7 * NUM_SMS and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
+        if use_tc and TC_PAIR and pairs * nkv >= 0.7 * ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
             return
         if use_tc:
             prefill_tc(*args, order(TC_QUERY_TILE))

@@ -3,9 +3,9 @@
     y[T, N] = x[T, K] w[N, K]^T     bfloat16 in, float32 accumulation in tensor memory
 
 With few tokens the weight matrix takes the 128-row side of the MMA tile ("swap") and, if it gives
-fewer tiles than the GPU has SMs, the reduction is split across blocks.  A device status word records
-a wait that ran out inside a kernel; `check_status()` reads it (a synchronising call, used by tests and
-at the end of a generation, never inside a step).  With `fused_reduce` the last block of a tile sums the
+fewer tiles than the GPU has SMs, the reduction is split across blocks.  A wait that runs out inside a
+kernel is recorded in the device status word (`ops.device_status`), which the engine reads with every
+step's tokens.  With `fused_reduce` the last block of a tile sums the
 split partials inside the same launch instead of a second kernel (faster for one token, slower from a few
 tokens on, so it is off by default).
 """
@@ -17,12 +17,11 @@ import os
 import torch
 
 from .csrc.build import load_library
+from . import ops
 from .ops import KernelError, _check, _ptr, _stream
 
 _P, _I = ctypes.c_void_p, ctypes.c_int
 _lib = None
-_status: dict = {}
-NUM_SMS = 148
 
 
 def lib():
@@ -37,32 +36,16 @@ def lib():
     return _lib
 
 
-N_COUNTERS = 8192
+N_COUNTERS = ops.N_COUNTERS
 CLUSTER_MAX = 8                # portable cluster size
 CLUSTER_REDUCE = os.environ.get("TENSORLINE_B200_CLUSTER_REDUCE", "1") != "0"   # 0: pieces + a summing pass (A/B timing)
+status_word = ops.device_status
+check_status = ops.check_device_status
 
 
-def status_word(device) -> torch.Tensor:
-    """[0]: the status word; [1:]: the per-tile arrival counters of split products (zero between calls)."""
-    t = _status.get(device)
-    if t is None:
-        t = torch.zeros(1 + N_COUNTERS, dtype=torch.int32, device=device)
-        _status[device] = t
-    return t
-
-
-def check_status() -> None:
-    """Raise if any kernel launched so far gave up on a wait (synchronises the device)."""
-    for dev, t in _status.items():
-        code = int(t[0].item())
-        if code:
-            t.zero_()
-            raise KernelError(f"tcgen05 matrix product on {dev}: a pipeline wait ran out (role {code}); "
-                              "its output is not valid")
-
-
-def plan(T: int, N: int, K: int) -> tuple:
-    """(swap, bn, splits) for a product of T tokens."""
+def plan(T: int, N: int, K: int, sms: int | None = None) -> tuple:
+    """(swap, bn, splits) for a product of T tokens on a GPU of `sms` multiprocessors."""
+    NUM_SMS = sms or ops.num_sms()
     k_tiles = -(-K // 64)
     if T <= 64:
         bn = 16 if T <= 16 else 32 if T <= 32 else 64

@@ -7,9 +7,11 @@ Order of work for the T tokens of a step (tensorline/paged.py:248-275):
   attention over the pages            query at position p reads keys lo..p of its own request
                                       (paged.py:237, paged_attn.py:43), scale d^-1/2 (paged.py:119)
   y = o Wo^T                          no bias
-The number of heads, of KV heads, the head size, the biases, the window and the position
-encoding are parameters.  A run entry that reads another entry's cache (`cache.owner` false)
-computes its own queries and writes no keys or values.
+The number of heads, of KV heads, the head size, the biases, the window, the position encoding
+(with its pairing of dimensions) and an optional RMS norm of every q and k head before the rotation
+(`qk_norm_eps`; weights `q_norm.weight`, `k_norm.weight` of the head size) are parameters; the
+fused kernel takes all of them as arguments.  A run entry that reads another entry's cache
+(`cache.owner` false) computes its own queries and writes no keys or values.
 """
 from __future__ import annotations
 
@@ -23,8 +25,11 @@ from .linear import SplitSum, matmul
 
 @register_mixer("paged_attention")
 class PagedAttention(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None):
+                 qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None,
+                 qk_norm_eps: float | None = None):
         super().__init__(rt)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
@@ -34,7 +39,8 @@ class PagedAttention(Part):
         self.qkv_bias, self.window = qkv_bias, window
         self.scale = head_dim ** -0.5 if scale is None else scale          # tensorline/paged.py:119
         self.position = POSITION_ENCODINGS.build(position, rt, head_dim=head_dim)
-        self.w_qkv = self.b_qkv = self.w_o = None
+        self.qk_norm_eps = qk_norm_eps
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     def cache_need(self):
         return PagedKV(self.nkv, self.d, self.window)
@@ -46,6 +52,9 @@ class PagedAttention(Part):
         if self.qkv_bias:
             out.update({f"{prefix}.q_proj.bias": TensorSpec((nq * d,)), f"{prefix}.k_proj.bias": TensorSpec((nkv * d,)),
                         f"{prefix}.v_proj.bias": TensorSpec((nkv * d,))})
+        if self.qk_norm_eps is not None:
+            out.update({f"{prefix}.q_norm.weight": TensorSpec((d,), init="ones"),
+                        f"{prefix}.k_norm.weight": TensorSpec((d,), init="ones")})
         return out
 
     def bind(self, weights, prefix):
@@ -57,19 +66,25 @@ class PagedAttention(Part):
             if self.b_qkv.dtype not in (torch.float32, torch.bfloat16):
                 self.b_qkv = self.b_qkv.float()
         self.w_o = self._compute_copy(weights[f"{prefix}.o_proj.weight"])
+        if self.qk_norm_eps is not None:
+            self.q_norm = weights[f"{prefix}.q_norm.weight"].float().contiguous()
+            self.k_norm = weights[f"{prefix}.k_norm.weight"].float().contiguous()
 
     def forward(self, h, ctx, cache):
         nq, nkv, d = self.nq, self.nkv, self.d
         T = h.shape[0]
-        inv_freq, rot = self.position.rotary()
-        qkv = matmul(h, self.w_qkv, may_defer=rot == d and d % 16 == 0)
+        rotary = self.position.rotary()
+        inv_freq, rot = rotary.inv_freq, rotary.rot
+        plain = rotary.pairing == "half" and self.q_norm is None          # what the kernel's fast path covers
+        qkv = matmul(h, self.w_qkv, may_defer=plain and rot == d and d % 16 == 0)
         pieces = None
         if isinstance(qkv, SplitSum):                    # a split-K product: the rotary kernel sums its pieces
             pieces = qkv.pieces
             qkv = torch.empty(qkv.shape, dtype=h.dtype, device=h.device)
         table = ctx.tables[cache.group]
         ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
-                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces)
+                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces, pairing=rotary.pairing,
+                          q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0)
         o = torch.empty((T, nq * d), dtype=h.dtype, device=h.device)
         self.attend(qkv, o, ctx, cache, table)
         return matmul(o, self.w_o, may_defer=True)             # the block's next norm adds it up

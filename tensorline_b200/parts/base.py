@@ -12,15 +12,23 @@ Interfaces (all tensors on the device; T tokens of the step flattened on axis 0)
 * Norm            `add_norm(x, pending, rows=None) -> h`: x (float32 residual stream, [T, H]) +=
                   pending (may be None), h = norm(x) in the activation type.  With `rows`
                   (int32 indices) only those rows are produced and x is left alone.
-* PositionEncoding `rotary() -> (inv_freq float32 [rot/2], rot) | None` for encodings that rotate
-                  q and k inside the mixer; `on_embedding(x, ctx)` for encodings added to the
-                  embedded tokens.  Either may be a no-op.
+* PositionEncoding `rotary() -> Rotary(inv_freq float32 [rot/2], rot, pairing)` for encodings that
+                  rotate q and k inside the mixer (`pairing`: which two dimensions form a pair);
+                  `on_embedding(x, ctx)` for encodings added to the embedded tokens.  Either may
+                  be a no-op (`rot` = 0).
 * Mixer           `cache_need() -> PagedKV | SlotState | None`; `forward(h, ctx, cache) -> y`;
                   `cache` is what the cache manager keeps for this run entry (`KVCacheView`,
                   `StateView` or None), `ctx` the step's `StepContext`.
 * FeedForward     `forward(h, ctx) -> y`.
 * Block           `forward(x, pending, ctx, cache) -> pending`: runs its norms, mixer and
                   feed-forward; the sum into the residual stream x happens inside the norms.
+* Embedding       `forward(ids) -> x`: the float32 residual stream [T, H]; `weight` is the table
+                  (a tied head reads it).
+* Head            `bind(weights, prefix, embedding)`; `forward(h) -> logits` float32 [R, V].
+
+A part whose `forward` reads the step from device tensors only (never from the host lists of the
+`StepContext`, never synchronising) sets `graph_capturable = True`: a model made of such parts
+decodes from CUDA graphs.
 
 Every part also declares its tensors, `expected_tensors(prefix) -> {name: TensorSpec}`, and
 takes them with `bind(weights, prefix)`.
@@ -53,6 +61,8 @@ class Runtime:
 
 
 class Part:
+    graph_capturable = False            # True: forward() can be captured in a CUDA graph (see the module text)
+
     def __init__(self, rt: Runtime):
         self.rt = rt
 
@@ -91,17 +101,34 @@ class Registry:
         return sorted(self._kinds)
 
 
+@dataclass(frozen=True)
+class Rotary:
+    """What a rotating position encoding hands to the mixer's fused kernel: angle of pair i at position
+    p is p * inv_freq[i]; the first `rot` dimensions of a head are rotated.  `pairing` "half": pair i is
+    dimensions (i, i + rot/2) (tensorline/fused.py:47-51); "interleaved": (2i, 2i + 1)."""
+    inv_freq: torch.Tensor
+    rot: int
+    pairing: str = "half"
+
+    def __iter__(self):                 # (inv_freq, rot) = encoding.rotary() still unpacks
+        return iter((self.inv_freq, self.rot))
+
+
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
 
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
 
 
 @dataclass
@@ -120,6 +147,7 @@ class StateView:
     state: torch.Tensor
 
 
-__all__ = ["PartSpec", "Runtime", "Part", "Registry", "NORMS", "POSITION_ENCODINGS", "MIXERS", "FEED_FORWARDS",
-           "BLOCKS", "register_norm", "register_position_encoding", "register_mixer", "register_feed_forward",
-           "register_block", "KVCacheView", "StateView", "TensorSpec"]
+__all__ = ["PartSpec", "Runtime", "Part", "Registry", "Rotary", "NORMS", "POSITION_ENCODINGS", "MIXERS", "FEED_FORWARDS",
+           "BLOCKS", "EMBEDDINGS", "HEADS", "register_norm", "register_position_encoding", "register_mixer",
+           "register_feed_forward", "register_block", "register_embedding", "register_head", "KVCacheView",
+           "StateView", "TensorSpec"]

@@ -42,6 +42,10 @@ class PreNormBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def graph_capturable(self) -> bool:
+        return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2, self.ff))
+
     def forward(self, x, pending, ctx, cache):
         h = self.norm1.add_norm(x, pending)
         a = self.mixer.forward(h, ctx, cache)

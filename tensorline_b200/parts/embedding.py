@@ -4,11 +4,14 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from .base import Part, Runtime, TensorSpec
+from .base import Part, Runtime, TensorSpec, register_embedding, register_head
 from .linear import matmul
 
 
+@register_embedding("token_table")
 class Embedding(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, vocab: int, dim: int):
         super().__init__(rt)
         self.vocab, self.dim = vocab, dim
@@ -27,9 +30,11 @@ class Embedding(Part):
         return x
 
 
+@register_head("linear")
 class LMHead(Part):
     """logits = h W^T in float32, no bias.  Tied: W is the embedding table; a stored
     `lm_head.weight` is then ignored."""
+    graph_capturable = True
 
     def __init__(self, rt: Runtime, vocab: int, dim: int, tied: bool):
         super().__init__(rt)

@@ -18,6 +18,8 @@ GATE_BLOCK = 64
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu"):
         super().__init__(rt)
         if activation != "silu":

@@ -10,13 +10,15 @@ from .linear import SplitSum
 
 @register_norm("rms_norm")
 class RMSNorm(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, dim: int, eps: float):
         super().__init__(rt)
         self.dim, self.eps = dim, eps
         self.weight = None
 
     def expected_tensors(self, prefix):
-        return {f"{prefix}.weight": TensorSpec((self.dim,))}
+        return {f"{prefix}.weight": TensorSpec((self.dim,), init="ones")}
 
     def bind(self, weights, prefix):
         self.weight = weights[f"{prefix}.weight"].contiguous()      # stays in its stored type

@@ -10,11 +10,13 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, Runtime, register_position_encoding
+from .base import Part, Rotary, Runtime, register_position_encoding
 
 
 @register_position_encoding("rotary_half")
 class RotaryHalf(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, head_dim: int, theta: float, rotary_dim: int | None = None):
         super().__init__(rt)
         rot = head_dim if rotary_dim is None else rotary_dim
@@ -25,7 +27,7 @@ class RotaryHalf(Part):
         self.inv_freq = (float(theta) ** (-i / rot)).to(torch.float32).to(rt.device)
 
     def rotary(self):
-        return self.inv_freq, self.rot
+        return Rotary(self.inv_freq, self.rot, "half")
 
     def on_embedding(self, x, ctx):
         return None
@@ -33,12 +35,14 @@ class RotaryHalf(Part):
 
 @register_position_encoding("none")
 class NoPositionEncoding(Part):
+    graph_capturable = True
+
     def __init__(self, rt: Runtime, **_):
         super().__init__(rt)
         self._empty = torch.zeros(0, dtype=torch.float32, device=rt.device)
 
     def rotary(self):
-        return self._empty, 0
+        return Rotary(self._empty, 0)
 
     def on_embedding(self, x, ctx):
         return None

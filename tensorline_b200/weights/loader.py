@@ -32,6 +32,7 @@ class TensorSpec:
     shape: tuple
     kind: str = "float"           # "float" (bfloat16 / float16 / float32 as stored) or "int"
     optional: bool = False        # absent is fine (e.g. an output head that is tied)
+    init: str = "normal"          # how a random model draws it: "normal" N(0, std), "ones" 1 + N(0, norm_std), "zeros"
 
 
 _FLOATS = (torch.bfloat16, torch.float16, torch.float32, torch.float64)

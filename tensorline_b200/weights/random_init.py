@@ -1,7 +1,8 @@
 """Random weights: write a model folder (config.json, model.safetensors) from a configuration
 and a seed.
 
-Every weight and bias is drawn from N(0, std); norm weights are 1, or 1 + N(0, norm_std).
+Every weight and bias is drawn from N(0, std); tensors whose part declares them as scales
+around one (`TensorSpec.init == "ones"`: norm weights) are 1, or 1 + N(0, norm_std).
 Values are generated tensor by tensor with a generator seeded from (seed, tensor name), so a
 tensor's values depend neither on the order of generation nor on what else the model holds.
 They are stored in bfloat16 (or float32 on request), as published checkpoints of this
@@ -36,8 +37,7 @@ def random_tensor(seed: int, name: str, shape, std: float, mean: float = 0.0) ->
 
 
 def write_random_model(folder, config, expected: dict, *, seed: int = 0, std: float = 0.02,
-                       norm_std: float = 0.0, store_dtype: torch.dtype = torch.bfloat16,
-                       is_norm=lambda name: "norm" in name) -> Path:
+                       norm_std: float = 0.0, store_dtype: torch.dtype = torch.bfloat16) -> Path:
     """`config`: a typed configuration with `to_json_dict()`; `expected`: name -> TensorSpec
     as the model declares them.  Optional tensors are not written."""
     folder = Path(folder)
@@ -48,8 +48,10 @@ def write_random_model(folder, config, expected: dict, *, seed: int = 0, std: fl
             continue
         if spec.kind == "int":
             raise ValueError(f"'{name}': no rule to draw an integer table")
-        if is_norm(name):
+        if spec.init == "ones":
             t = random_tensor(seed, name, spec.shape, norm_std, 1.0)
+        elif spec.init == "zeros":
+            t = torch.zeros(tuple(spec.shape), dtype=torch.float32)
         else:
             t = random_tensor(seed, name, spec.shape, std)
         tensors[name] = t.to(store_dtype)

@@ -10,40 +10,40 @@ from tensorline_b200.cache import CacheError, CacheManager, PagedKV, PagePool, S
 def test_pool_refcount_lru_and_eviction():
     """The scenario of tzar-beep/Tensorline's tests/test_prefix_cache.py:8-22."""
     a = PagePool(4)
-    x = a.allocate(2)
+    x = a.take(2)
     h0 = page_hash(None, [1, 2])
-    a.register(x[0], h0, None, [1, 2])
-    a.free(x)
+    a.publish(x[0], h0, None, [1, 2])
+    a.drop(x)
     assert a.num_free == 4 and a.num_cached == 1            # freed but still published
-    assert a.lookup(h0, None, [1, 2]) == x[0] and a.num_free == 3
-    assert a.lookup(h0) == x[0]                             # shared: count 2
-    a.free([x[0]])
+    assert a.adopt(h0, None, [1, 2]) == x[0] and a.num_free == 3
+    assert a.adopt(h0) == x[0]                             # shared: count 2
+    a.drop([x[0]])
     assert a.num_free == 3
-    a.free([x[0]])
+    a.drop([x[0]])
     assert a.num_free == 4
-    a.allocate(4)                                           # pressure evicts it
-    assert a.num_cached == 0 and a.lookup(h0) is None
+    a.take(4)                                           # pressure evicts it
+    assert a.num_cached == 0 and a.adopt(h0) is None
     a.check()
 
 
 def test_hash_chains_over_the_whole_prefix_and_hits_are_verified():
     assert page_hash(page_hash(None, [1]), [2]) != page_hash(page_hash(None, [9]), [2])
     a = PagePool(2)
-    (p,) = a.allocate(1)
+    (p,) = a.take(1)
     h = page_hash(None, [4, 5])
-    a.register(p, h, None, [4, 5])
-    assert a.lookup(h, None, [4, 6]) is None                # same hash claimed, other tokens: a miss
+    a.publish(p, h, None, [4, 5])
+    assert a.adopt(h, None, [4, 6]) is None                # same hash claimed, other tokens: a miss
 
 
 def test_double_free_and_foreign_pages_raise():
     a = PagePool(3)
-    x = a.allocate(1)
-    a.free(x)
+    x = a.take(1)
+    a.drop(x)
     with pytest.raises(CacheError, match="double free"):
-        a.free(x)
+        a.drop(x)
     with pytest.raises(CacheError, match="outside"):
-        a.free([7])
-    assert a.allocate(4) is None and a.num_free == 3        # all or nothing
+        a.drop([7])
+    assert a.take(4) is None and a.num_free == 3        # all or nothing
 
 
 def _manager(window=None, pages=12, page=4, seqs=4, sharing=True, state=False):
@@ -58,7 +58,7 @@ def test_groups_by_need_and_table_rows():
     m = _manager(window=6)
     assert len(m.groups) == 2 and m.groups[0].window is None and m.groups[1].window == 6
     assert m.group_of == {0: 0, 1: 1, 2: 1}
-    assert not m.prefix_caching                             # a window group: no sharing
+    assert m.prefix_caching                                 # window groups share prefixes too
     assert m.admit("r") == 0 and m.grow("r", 0, 9)
     assert len(m.pages("r", 0)) == 3 and len(m.pages("r", 1)) == 3
     slot = m.slot("r")
@@ -107,12 +107,44 @@ def test_prefix_sharing_counts_and_fully_cached_prompt():
     m.check()
 
 
-@pytest.mark.parametrize("window,sharing,seed", [(None, True, 0), (None, False, 1), (7, True, 2), (3, False, 3), (None, True, 4)])
-def test_random_orders_never_lose_a_page(window, sharing, seed):
+def test_window_group_shares_the_pages_its_window_still_reaches():
+    """Two groups, all keys and a window of 6 keys, pages of 4.  A request whose first 12 tokens are
+    published takes, in the window group, only the pages a query at position 12 can read (keys 7..11:
+    pages 1 and 2); if one of those has been used up meanwhile the hit shrinks to what both groups serve."""
+    needs = {0: PagedKV(1, 16, None), 1: PagedKV(1, 16, 6)}
+    m = CacheManager(needs, page_size=4, num_pages={None: 8, 6: 4}, max_num_seqs=3, max_model_len=32)
+    assert m.groups[0].pool.num_pages == 8 and m.groups[1].pool.num_pages == 4
+    toks = list(range(50, 64))
+    assert m.admit("a", toks) == 0 and m.grow("a", 0, 14)
+    m.advance("a", 14, toks)                                # three full pages offered in both groups
+    wa = m.pages("a", 1)                                    # a's next query (14) reads keys 9..: pages 0, 1 are passed
+    assert wa[:2] == [-1, -1] and wa[2] >= 0
+    assert m.admit("b", toks[:12] + [1, 2, 3]) == 12
+    assert m.pages("b", 0) == m.pages("a", 0)[:3]
+    wb = m.pages("b", 1)                                    # page 1 is revived from the idle ones, page 2 is shared with a
+    assert wb[0] == -1 and wb[1] >= 0 and wb[2] == wa[2] and m.groups[1].pool.refcount(wb[2]) == 2
+    slot = m.slot("b")
+    assert m.groups[1].table[slot, 0] == m.groups[1].scratch_page
+    m.check()
+    m.release("a"); m.release("b")
+    assert m.num_free_pages(0) == 8 and m.num_free_pages(1) == 4
+    # the window group's pool is used up by someone else: its published pages are gone, the full group's are not
+    assert m.admit("c") == 0 and m.grow("c", 0, 4)
+    m.release("c")                                          # took the window group's longest-idle page: page 0 of a
+    assert m.admit("d", toks[:12] + [9]) == 12              # page 0 is not needed at position 12
+    m.release("d")
+    assert m.admit("e") == 0 and m.grow("e", 0, 16)          # now every page of the window group is rewritten
+    m.release("e")
+    assert m.admit("f", toks[:12] + [9]) == 0               # the full group alone cannot restore the prefix
+    m.check()
+
+
+@pytest.mark.parametrize("window,sharing,state,seed", [(None, True, True, 0), (None, False, True, 1), (7, True, False, 2),
+                                                        (3, False, True, 3), (None, True, False, 4), (5, True, False, 5)])
+def test_random_orders_never_lose_a_page(window, sharing, state, seed):
     rng = random.Random(seed)
-    m = _manager(window=window, pages=10, page=4, seqs=3, sharing=sharing, state=True)
-    if window is not None:
-        assert not m.prefix_caching
+    m = _manager(window=window, pages=10, page=4, seqs=3, sharing=sharing, state=state)
+    assert m.prefix_caching == (sharing and not state)
     live = {}                                                # rid -> [tokens, computed]
     prompts = [[rng.randrange(5) for _ in range(rng.randrange(1, 30))] for _ in range(6)]
     nxt = 0

@@ -24,7 +24,7 @@ def big():
     g = torch.Generator(device="cuda").manual_seed(5)
     weights = {}
     for name, spec in expected_tensors(cfg).items():
-        if "norm" in name:
+        if spec.init == "ones":
             weights[name] = (1 + 0.1 * torch.randn(spec.shape, device="cuda", generator=g)).to(torch.bfloat16)
         else:
             weights[name] = (0.02 * torch.randn(spec.shape, device="cuda", generator=g)).to(torch.bfloat16)

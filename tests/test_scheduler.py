@@ -3,14 +3,18 @@ chunked prefill, decoding, finishing, and what happens when pages run out."""
 import pytest
 
 from tensorline_b200.cache import CacheManager, PagedKV
-from tensorline_b200.engine.scheduler import Request, RequestDoesNotFit, Scheduler
+from tensorline_b200.engine.scheduler import Plan, Request, RequestDoesNotFit, Scheduler, Slice
 from tensorline_b200.sampling import SamplingParams
 
 
-def make(pages=16, page=4, seqs=4, budget=8, max_len=64, sharing=False, window=None):
+def make(pages=16, page=4, seqs=4, budget=8, max_len=64, sharing=False, window=None, **kw):
     cache = CacheManager({0: PagedKV(1, 16, window)}, page_size=page, num_pages=pages, max_num_seqs=seqs,
                          max_model_len=max_len, prefix_caching=sharing)
-    return Scheduler(cache, max_num_seqs=seqs, max_batched_tokens=budget, max_model_len=max_len), cache
+    return Scheduler(cache, max_num_seqs=seqs, max_batched_tokens=budget, max_model_len=max_len, **kw), cache
+
+
+def shape(plan):
+    return [(s.request.rid, s.count) for s in plan]
 
 
 def req(rid, n, max_tokens=4, first=0):
@@ -24,8 +28,8 @@ def run(s, token=lambda r: 1000 + r.num_generated, limit=500):
         if not s.has_work():
             return plans
         plan = s.schedule()
-        plans.append([(r.rid, n) for r, n in plan])
-        done_prefill = [r for r, n in plan if r.num_computed + n == len(r.tokens)]
+        plans.append(shape(plan))
+        done_prefill = [sl.request for sl in plan if sl.wants_logits]
         s.computed(plan)
         for r in done_prefill:
             s.accept(r, token(r))
@@ -37,14 +41,14 @@ def test_budget_cuts_prompts_into_portions_and_decodes_beside_them():
     s, cache = make(budget=8)
     a, b = req(0, 13), req(1, 5)
     s.add(a); s.add(b)
-    assert [(r.rid, n) for r, n in s.schedule()] == [(0, 8)]           # b waits: the budget is spent
-    s.computed([(a, 8)])
+    assert shape(s.schedule()) == [(0, 8)]           # b waits: the budget is spent
+    s.computed([Slice(a, 0, 8)])
     plan = s.schedule()
-    assert [(r.rid, n) for r, n in plan] == [(0, 5), (1, 3)]           # rest of a, then what is left for b
+    assert shape(plan) == [(0, 5), (1, 3)]           # rest of a, then what is left for b
     s.computed(plan)
     s.accept(a, 7)
     plan = s.schedule()
-    assert [(r.rid, n) for r, n in plan] == [(0, 1), (1, 2)]           # a decodes beside b's portion
+    assert shape(plan) == [(0, 1), (1, 2)]           # a decodes beside b's portion
     assert s.max_running_seen == 2
 
 
@@ -99,7 +103,8 @@ def test_request_that_can_never_fit_fails_instead_of_hanging():
     s, cache = make(pages=2, page=4, budget=64)
     big = req(0, 9)                                                    # needs 3 pages, the pool has 2
     s.add(big)
-    assert s.schedule() == [] and s.failed == [big]
+    plan = s.schedule()
+    assert not plan and plan.failed == [big] and s.failed == [big]
     assert isinstance(big.error, RequestDoesNotFit) and big.done and not s.has_work()
     grows = req(1, 7, max_tokens=5)                                    # fits now, outgrows the pool while decoding
     s.add(grows)
@@ -113,7 +118,7 @@ def test_waiting_head_blocks_until_pages_free_up():
     a, b = req(0, 12, max_tokens=2), req(1, 8, max_tokens=2)
     s.add(a); s.add(b)
     plan = s.schedule()
-    assert [(r.rid, n) for r, n in plan] == [(0, 12)] and list(s.waiting) == [b]
+    assert shape(plan) == [(0, 12)] and list(s.waiting) == [b]
     assert not cache.holds(1)                                          # it holds nothing while it waits
     run(s)
     assert a.done and b.done and b.error is None
@@ -128,7 +133,7 @@ def test_shared_prefix_counts_cached_tokens_once():
     b.tokens = list(a.tokens[:10])
     s.add(b)
     plan = s.schedule()
-    assert [(r.rid, n) for r, n in plan] == [(1, 2)] and b.stats.cached_tokens == 8
+    assert shape(plan) == [(1, 2)] and b.stats.cached_tokens == 8
     assert s.prefix_hit_tokens == 8 and s.prompt_tokens_total == 20
 
 
@@ -144,3 +149,65 @@ def test_abort_and_fail_all_release_everything():
     assert {r.rid for r in failed} == {1, 2} and all(isinstance(r.error, RuntimeError) for r in failed)
     assert cache.num_free_pages() == cache.num_pages and cache.num_free_slots == 4
     cache.check()
+
+
+def test_plan_is_typed_and_names_what_happened():
+    s, cache = make(pages=4, page=4, budget=64)
+    a, b = req(0, 6, max_tokens=8), req(1, 6, max_tokens=8, first=50)
+    s.add(a); s.add(b)
+    plan = s.schedule()
+    assert isinstance(plan, Plan) and plan.admitted == [a, b] and plan.num_tokens == 12
+    assert [(sl.start, sl.count, sl.wants_logits) for sl in plan] == [(0, 6, True), (0, 6, True)]
+    assert plan.kinds() == (0, 12)
+    s.computed(plan)
+    s.accept(a, 7); s.accept(b, 7)
+    plan = s.schedule()
+    assert plan.kinds() == (2, 0) and not plan.preempted
+    s.computed(plan)
+    s.accept(a, 7); s.accept(b, 7)
+    plan = s.schedule()                                  # position 7 of both: the last place in their pages
+    s.computed(plan)
+    s.accept(a, 7); s.accept(b, 7)
+    plan = s.schedule()                                  # a needs a third page: b, the newest, gives way
+    assert plan.preempted == [b] and shape(plan) == [(0, 1)] and list(s.waiting) == [b] and b.num_computed == 0
+
+
+def test_preemption_policy_is_a_parameter():
+    """With "least_computed" the request that is cheapest to recompute gives way, not the newest."""
+    for policy, victim in (("newest", 1), ("least_computed", 0), (lambda running: running[0], 0)):
+        s, cache = make(pages=6, page=4, budget=64, preemption=policy)
+        a, b = req(0, 3, max_tokens=20), req(1, 13, max_tokens=20, first=50)
+        s.add(a); s.add(b)
+        gone = []
+        for _ in range(12):
+            plan = s.schedule()
+            gone += [r.rid for r in plan.preempted]
+            if gone:
+                break
+            s.computed(plan)
+            for sl in plan:
+                if sl.wants_logits:
+                    s.accept(sl.request, 9)
+        assert gone == [victim], policy
+        cache.check()
+
+
+def test_window_prompt_is_cut_to_the_room_there_is():
+    """Window 24, pages of 8, a pool of 6 pages, a prompt of 200 tokens under a budget of 128: a portion of
+    128 would need pages for window + 128 tokens; the request is alone, so its portions are cut to the
+    room the pool has (48 tokens first, then what the passed pages give back) instead of failing."""
+    s, cache = make(pages=6, page=8, budget=128, max_len=512, window=24)
+    r = req(0, 200, max_tokens=3)
+    s.add(r)
+    plans = run(s)
+    assert r.error is None and r.done and r.num_generated == 3
+    sizes = [n for p in plans for rid, n in p]
+    assert sizes[0] == 48 and sum(sizes[:-2]) == 200 and max(sizes) <= 48 and s.preemptions == 0
+    assert cache.num_free_pages() == 6
+    # two such requests: the older one is served, the newer one waits or gives way, both finish
+    s, cache = make(pages=6, page=8, budget=128, max_len=512, window=24)
+    a, b = req(0, 150, max_tokens=2), req(1, 90, max_tokens=2, first=500)
+    s.add(a); s.add(b)
+    run(s)
+    assert a.error is None and b.error is None and a.num_generated == 2 and b.num_generated == 2
+    assert cache.num_free_pages() == 6

@@ -59,3 +59,22 @@ def test_skipped_requests_get_no_tile():
     assert [v & 0xFFFF for v in order] == sorted((v & 0xFFFF for v in order), reverse=True)
     # one request left and others skipped: still an explicit order (the kernel's own would include them)
     assert tile_order([0, 1, 101], [4000, 0], 1, 64, "cpu", skip=frozenset({0})).tolist() == [(1 << 16) | 1, 1 << 16]
+
+
+def test_key_ranges_of_a_decode_step_never_exceed_the_block_table_copy():
+    """A decode block copies its range's block-table entries to shared memory, DECODE_MAX_TABLE_ENTRIES at most.
+    Whatever page size, context and batch the engine's options allow, the planned ranges stay within that and
+    cover the whole span (small pages at long contexts used to plan one range of 4,096 pages and fail at launch)."""
+    from tensorline_b200.ops_attention import DECODE_MAX_TABLE_ENTRIES, KEY_TILE, plan_splits
+    for page in (1, 2, 4, 8, 16, 32, 64):
+        for span in (1, 63, 64, 65, 4096, 16384, 32768, 65536, 131072, 1 << 20):
+            for batch in (1, 2, 8, 32, 64, 256):
+                for nkv, group, d in ((4, 7, 128), (8, 5, 128), (1, 3, 32), (2, 20, 64)):
+                    chunk, splits = plan_splits(batch, nkv, group, span, d, page_size=page, sms=148)
+                    assert chunk % KEY_TILE == 0 and chunk > 0 and splits >= 1
+                    assert chunk // page <= DECODE_MAX_TABLE_ENTRIES, (page, span, batch, chunk)
+                    assert chunk * splits >= span, (page, span, batch, chunk, splits)
+                    assert chunk * (splits - 1) < -(-span // KEY_TILE) * KEY_TILE          # no empty range
+    # the cases that used to fail: the GPU is full, so one range took the whole span
+    assert plan_splits(64, 4, 7, 32768, 128, page_size=8, sms=148) == (16384, 2)
+    assert plan_splits(64, 4, 7, 65536, 128, page_size=16, sms=148) == (32768, 2)
