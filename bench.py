@@ -163,8 +163,7 @@ def timed_decode(eng, batch, ctx0, steps, warmup, vocab, sampler=None):
         for i, (rid, _) in enumerate(reqs):
             assert cache.grow(rid, pos, pos + 1)
             entries.append(StepEntry(rid, [nxt[k][i]], [0]))
-        assert runner._can_replay(entries)
-        runner._run_graph(entries)
+        runner.step_graph(entries)
         pos += 1
 
     for k in range(warmup):

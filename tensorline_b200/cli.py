@@ -34,7 +34,7 @@ def _generate_parser() -> argparse.ArgumentParser:
     ap.add_argument("--num-blocks", type=int, default=None, help="KV pages (default: fit 60%% of free memory)")
     ap.add_argument("--kv-cache-gb", type=float, default=None, help="KV cache size (default: 60%% of free memory)")
     ap.add_argument("--no-cuda-graphs", action="store_true", help="run decode steps eagerly")
-    ap.add_argument("--no-overlap", action="store_true", help="accepted; steps here are read back one by one")
+    ap.add_argument("--no-overlap", action="store_true", help="read every decode step back before the next one is launched")
     ap.add_argument("--graph-warmup-tokens", type=int, default=512,
                     help="accepted; decode graphs here do not depend on the context length")
     ap.add_argument("--no-prefix-caching", action="store_true", help="never reuse KV pages across requests")

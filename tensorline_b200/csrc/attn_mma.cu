@@ -78,6 +78,7 @@ struct AttnArgs {
     // prefill only: the tiles in the order in which blocks take them, (request << 16 | tile), longest first over
     // all requests; null: one request after the other from the end
     const int* order;
+    TlLimits lim;                      // for the checking build; zeros: nothing known, nothing checked
 };
 
 // A [ROWS][DP] tile of keys (or values) of one KV head is filled by 128 threads in chunks of 16
@@ -107,7 +108,7 @@ struct TileMap {
 // `pages` points at the KV head's part of page 0.
 template <int ROWS>
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const int* tab, size_t page_stride,
-                                             int key0, int last_key, const TileMap<ROWS>& map) {
+                                             int key0, int last_key, const TileMap<ROWS>& map, const TlLimits& L, int kernel) {
     const int keys_valid = last_key - key0;               // keys 0..keys_valid of the tile exist
 #pragma unroll
     for (int i = 0; i < TileMap<ROWS>::ITERS; ++i) {
@@ -115,7 +116,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* pages, const
         const int key = map.src[i] >> 26;
         const bool valid = key <= keys_valid;
         const bf16* src = pages;
-        if (valid) src = pages + (size_t)tab[(map.src[i] >> 20) & 63] * page_stride + (map.src[i] & 0xFFFFF);
+        if (valid) src = pages + (size_t)tl_checked(tab[(map.src[i] >> 20) & 63], L.total_pages, L, kernel) * page_stride + (map.src[i] & 0xFFFFF);
         cp_async16(dst + map.dst[i], src, valid);
     }
 }
@@ -258,8 +259,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
     const int rows_total = qlen * g, row0 = tile * BM;
     const int row_end = min(row0 + BM, rows_total);
-    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* tab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_PREFILL) * A.max_pages;
     const int pos_hi = sp + (row_end - 1) / g;
+    tl_checked(pos_hi / A.page_size, A.max_pages, A.lim, TL_K_PREFILL);     // the last table entry this tile reads
     const int pos_first = sp + row0 / g;
     const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
@@ -278,8 +280,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int ppt = BN / A.page_size;                       // pages per tile
     const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
     const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
-    load_kv_tile(sK, kbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map);
-    load_kv_tile(sV, vbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map);
+    load_kv_tile(sK, kbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+    load_kv_tile(sV, vbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map, A.lim, TL_K_PREFILL);
     cp_async_commit();
 
     int pos_r[2], lo_r[2];
@@ -304,8 +306,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         cp_async_wait<0>();
         __syncthreads();                                   // tile kt is in; everyone is done with tile kt-1
         if (kt < kt_hi) {
-            load_kv_tile(sK + (buf ^ 1) * BN * DP, kbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map);
-            load_kv_tile(sV + (buf ^ 1) * BN * DP, vbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map);
+            load_kv_tile(sK + (buf ^ 1) * BN * DP, kbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+            load_kv_tile(sV + (buf ^ 1) * BN * DP, vbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map, A.lim, TL_K_PREFILL);
         }
         cp_async_commit();
         // skip tiles wholly outside this warp's rows (above the diagonal or behind the window)
@@ -366,13 +368,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     if (k_begin >= len) return;                            // an empty split: the combine step skips it too
     const int k_end = min(len, k_begin + A.chunk);
     const int n_stage = (k_end - k_begin + BN - 1) / BN;
-    const int* gtab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* gtab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_DECODE) * A.max_pages;
     const int qrow = A.q_start[b];
     // this block's part of the request's block table, copied once
     int* stab = reinterpret_cast<int*>(smem_raw + DECODE_TAB_OFFSET);
     const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
     const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
-    for (int i = tid; i < n_stage * ppt; i += 128) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
+    for (int i = tid; i < n_stage * ppt; i += 128)
+        stab[i] = i < n_pages ? gtab[tl_checked(first_page + i, A.max_pages, A.lim, TL_K_DECODE)] : 0;
     TileMap<BN> map;
     map.init(tid, A.page_size);
     const size_t page_stride = (size_t)A.nkv * A.page_size * D;
@@ -396,8 +399,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
         if (st < n_stage) {
-            load_kv_tile(sK + st * BN * DP, kbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map);
-            load_kv_tile(sV + st * BN * DP, vbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map);
+            load_kv_tile(sK + st * BN * DP, kbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map, A.lim, TL_K_DECODE);
+            load_kv_tile(sV + st * BN * DP, vbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map, A.lim, TL_K_DECODE);
         }
         cp_async_commit();
     }
@@ -419,8 +422,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         __syncthreads();
         if (st + DEC_STAGES - 1 < n_stage) {
             const int nst = st + DEC_STAGES - 1, nb_ = nst % DEC_STAGES;
-            load_kv_tile(sK + nb_ * BN * DP, kbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map);
-            load_kv_tile(sV + nb_ * BN * DP, vbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map);
+            load_kv_tile(sK + nb_ * BN * DP, kbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map, A.lim, TL_K_DECODE);
+            load_kv_tile(sV + nb_ * BN * DP, vbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map, A.lim, TL_K_DECODE);
         }
         cp_async_commit();
         const int buf = st % DEC_STAGES;
@@ -564,11 +567,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (!CLUSTER && k_begin >= len) return;
     const int k_end = max(k_begin, min(len, k_begin + A.chunk));
     const int n_stage = (k_end - k_begin + BN - 1) / BN;  // 0: an empty range (CLUSTER only)
-    const int* gtab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* gtab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_DECODE_TMA) * A.max_pages;
     const int qrow = A.q_start[b];
     const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
     const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
-    for (int i = tid; i < n_stage * ppt; i += TMA_DEC_THREADS) stab[i] = i < n_pages ? gtab[first_page + i] : 0;
+    for (int i = tid; i < n_stage * ppt; i += TMA_DEC_THREADS)
+        stab[i] = i < n_pages ? tl_checked(gtab[tl_checked(first_page + i, A.max_pages, A.lim, TL_K_DECODE_TMA)], A.lim.total_pages,
+                                           A.lim, TL_K_DECODE_TMA) : 0;
     if (tid == 0) {
         for (int s_ = 0; s_ < DEC_STAGES; ++s_) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + s_)), "r"(TMA_COPY_WARPS));
@@ -849,6 +854,8 @@ int set_attrs() {
 }  // namespace
 
 TL_EXPORT int tl_attn_head_dim() { return D; }
+// 1 if this library was compiled as the checking build (-DTL_CHECK=1).
+TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
 TL_EXPORT int tl_attn_decode_max_table() { return DECODE_MAX_TAB; }
 
@@ -856,7 +863,8 @@ TL_EXPORT int tl_attn_decode_max_table() { return DECODE_MAX_TAB; }
 TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                               const int* table, int max_pages, int page_size, const int* q_start,
                               const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
-                              float scale, int total_tiles, const int* order, cudaStream_t stream) {
+                              float scale, int total_tiles, const int* order, int table_rows, int total_pages, int* fault,
+                              cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
     if (nq % nkv || BN % page_size) return 1;
     int e = set_attrs();
@@ -866,6 +874,7 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.order = order;
+    A.lim = TlLimits{table_rows, total_pages, fault};
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
@@ -881,7 +890,7 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
                              const int* table, int max_pages, int page_size, const int* q_start,
                              const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
                              float scale, int chunk, int splits, float* part_o, float* part_ml,
-                             cudaStream_t stream) {
+                             int table_rows, int total_pages, int* fault, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (nq % nkv || BN % page_size || chunk % BN || splits < 1 || (splits > 1 && (!part_o || !part_ml))) return 1;
     int e = set_attrs();
@@ -893,6 +902,7 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
+    A.lim = TlLimits{table_rows, total_pages, fault};
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
@@ -933,7 +943,7 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
                                  long long total_pages, const int* table, int max_pages, int page_size,
                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
                                  int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
-                                 int* status, int cluster_merge, cudaStream_t stream) {
+                                 int* status, int cluster_merge, int table_rows, int* fault, cudaStream_t stream) {
 #if HEAD_DIM % 64 == 0
     if (B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
@@ -975,6 +985,7 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
+    A.lim = TlLimits{table_rows, (int)total_pages, fault};
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;

@@ -174,6 +174,7 @@ struct TcAttnArgs {
     // the tiles in the order in which blocks take them, (request << 16 | tile), longest first over all requests;
     // null: one request after the other from the end
     const int* order;
+    TlLimits lim;                      // for the checking build; zeros: nothing known, nothing checked
 };
 
 // One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
@@ -212,11 +213,12 @@ __device__ __forceinline__ void load_q_rows(uint32_t dst_tile, const bf16* q, in
 // page numbers are read once (one per lane) and handed around with shuffles, so no copy waits on a
 // table read of its own.
 __device__ __forceinline__ void load_kv(uint32_t dst, const bf16* pages, const int* tab, int ps_shift, size_t page_stride,
-                                        int key0, int last_key, int lane) {
+                                        int key0, int last_key, int lane, const TlLimits& L) {
     constexpr int CH = D / 8;
     const int ps_mask = (1 << ps_shift) - 1;
     int my_page = 0;
-    if (lane < (BN >> ps_shift) && key0 + (lane << ps_shift) <= last_key) my_page = tab[(key0 >> ps_shift) + lane];
+    if (lane < (BN >> ps_shift) && key0 + (lane << ps_shift) <= last_key)
+        my_page = tl_checked(tab[(key0 >> ps_shift) + lane], L.total_pages, L, TL_K_TC_PREFILL);
 #pragma unroll
     for (int i = 0; i < BN * CH / 32; ++i) {
         const int idx = lane + 32 * i;
@@ -260,8 +262,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
     const int rows_total = qlen * g, row0 = tile * BM;
     const int row_end = min(row0 + BM, rows_total);
-    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* tab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_TC_PREFILL) * A.max_pages;
     const int pos_hi = sp + (row_end - 1) / g, pos_first = sp + row0 / g;
+    tl_checked(pos_hi / A.page_size, A.max_pages, A.lim, TL_K_TC_PREFILL);  // the last table entry this tile reads
     const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN, n_kt = kt_hi - kt_lo + 1;
 
@@ -446,7 +449,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
                 if (!ok) break;
             }
-            load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, (kt_lo + j) * BN, pos_hi, lane);
+            load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, (kt_lo + j) * BN, pos_hi, lane, A.lim);
             cp_async_wait_all();
             fence_async_proxy();
             mbar_arrive(bar_full + sl);
@@ -536,7 +539,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     if (b >= A.B) return;
     const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
     const int rows_total = qlen * g;
-    const int* tab = A.table + (size_t)A.slots[b] * A.max_pages;
+    const int* tab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_TC2_PREFILL) * A.max_pages;
     // the two tiles: rows, and the range of key tiles each of them reads
     int row0[QT], kt_first[QT], kt_last[QT];
 #pragma unroll
@@ -769,7 +772,8 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 int page[8];
 #pragma unroll
                 for (int pg = 0; pg < 8; ++pg)              // the tile's page numbers, all requested before the wait
-                    if (pg < ppt) page[pg] = tab[min((((kt_lo + j) * BN) >> ps_shift) + pg, A.max_pages - 1)];
+                    if (pg < ppt) page[pg] = tl_checked(tab[min((((kt_lo + j) * BN) >> ps_shift) + pg, A.max_pages - 1)],
+                                                        A.lim.total_pages, A.lim, TL_K_TC2_PREFILL);
                 if (j >= 2) {
                     ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
                     if (!ok) break;
@@ -822,12 +826,15 @@ bool g_attr_done[TL_MAX_DEVICES] = {};
 }  // namespace
 
 TL_EXPORT int tl_attn_tc_head_dim() { return D; }
+// 1 if this library was compiled as the checking build (-DTL_CHECK=1).
+TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 
 // total_tiles = sum over requests of ceil(q_len * g / 128).  `status`: device int, zero before the call.
 TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                  const int* table, int max_pages, int page_size, const int* q_start,
                                  const int* start_pos, const int* slots, int B, int nq, int nkv, int window,
-                                 float scale, int total_tiles, int* status, const int* order, cudaStream_t stream) {
+                                 float scale, int total_tiles, int* status, const int* order, int table_rows, int total_pages,
+                                 int* fault, cudaStream_t stream) {
     if (total_tiles <= 0 || B <= 0) return 0;
     if (nq % nkv || page_size <= 0 || (page_size & (page_size - 1)) || page_size * 32 < BN || page_size > 64 || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
     const int dev = tl_device_index();
@@ -843,6 +850,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
+    A.lim = TlLimits{table_rows, total_pages, fault};
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(A);
     return tl_launch_status();
@@ -854,7 +862,8 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
 TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                   long long total_pages, const int* table, int max_pages, int page_size,
                                   const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
-                                  int window, float scale, int total_tiles, int* status, const int* order, cudaStream_t stream) {
+                                  int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                                  int* fault, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
@@ -885,6 +894,7 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
+    A.lim = TlLimits{table_rows, (int)total_pages, fault};
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
     return tl_launch_status();

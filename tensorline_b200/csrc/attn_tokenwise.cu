@@ -19,13 +19,13 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
                                       const TA* __restrict__ k_pages, const TA* __restrict__ v_pages,
                                       const int* __restrict__ table, int max_pages, int page_size,
                                       const int* __restrict__ pos, const int* __restrict__ req_slot,
-                                      int nq, int nkv, int d, int window, float scale) {
+                                      int nq, int nkv, int d, int window, float scale, const TlLimits L) {
     __shared__ float qs[ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kh = h / (nq / nkv);
     const int p = pos[t];
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int* tab = table + (size_t)req_slot[t] * max_pages;
+    const int* tab = table + (size_t)tl_checked(req_slot[t], L.table_rows, L, TL_K_TOKENWISE) * max_pages;
     const TA* qrow = q + (size_t)t * q_stride + (size_t)h * d;
     for (int e = lane; e < d; e += 32) qs[e] = to_f<TA>(qrow[e]);
     __syncwarp();
@@ -42,7 +42,7 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
         size_t row = 0;
         float s = -INFINITY;
         if (valid) {
-            const int page = tab[j / page_size];
+            const int page = tl_checked(tab[tl_checked(j / page_size, max_pages, L, TL_K_TOKENWISE)], L.total_pages, L, TL_K_TOKENWISE);
             row = (((size_t)page * nkv + kh) * page_size + (j % page_size)) * d;
             const TA* kr = k_pages + row;
             float dot = 0.f;
@@ -82,17 +82,19 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
 TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_dtype,
                                 const void* k_pages, const void* v_pages, const int* table, int max_pages,
                                 int page_size, const int* pos, const int* req_slot, int T, int nq, int nkv,
-                                int d, int window, float scale, cudaStream_t stream) {
+                                int d, int window, float scale, int table_rows, int total_pages, int* fault,
+                                cudaStream_t stream) {
+    const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
     if (d > ATT_MAX_D || nq % nkv) return 1;
     dim3 grid(T, nq);
     if (act_dtype == TL_F32)
         attn_tokenwise_kernel<float><<<grid, 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             (const float*)k_pages, (const float*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale);
+            nq, nkv, d, window, scale, L);
     else
         attn_tokenwise_kernel<bf16><<<grid, 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             (const bf16*)k_pages, (const bf16*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale);
+            nq, nkv, d, window, scale, L);
     return tl_launch_status();
 }

@@ -29,6 +29,10 @@ CSRC = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 
+# The checking build: TENSORLINE_B200_CHECK=1 compiles every library with -DTL_CHECK=1 (bounds checks on every
+# block-table and page index inside the kernels, see common.cuh); it is a library of its own beside the ordinary one.
+CHECK_BUILD = os.environ.get("TENSORLINE_B200_CHECK", "0") == "1"
+
 _loaded: dict = {}
 _lock = threading.Lock()
 
@@ -72,9 +76,16 @@ def _digest(sources, flags) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(name: str, sources, defines: dict | None = None, extra_flags=()) -> tuple:
-    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted((defines or {}).items())] + list(extra_flags)
+def library_path(name: str, sources, defines: dict | None = None, extra_flags=(), check: bool | None = None) -> tuple:
+    """(path, flags, already built).  `check`: the checking build of the library (None: as the environment says)."""
+    check = CHECK_BUILD if check is None else check
+    defines = dict(defines or {})
+    if check:
+        defines["TL_CHECK"] = 1
+    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted(defines.items())] + list(extra_flags)
     tag = _digest(sources, flags)
+    if check:
+        name = name + "_chk"
     fname = f"lib{name}_{tag}.so"
     for d in (CSRC / "_build", Path(tempfile.gettempdir()) / f"tensorline_b200_build_{os.getuid()}"):
         if (d / fname).is_file():
@@ -82,11 +93,14 @@ def library_path(name: str, sources, defines: dict | None = None, extra_flags=()
     return build_dir() / fname, flags, False
 
 
-def build_library(name: str, sources, defines: dict | None = None, extra_flags=(), verbose: bool = True) -> Path:
+def build_library(name: str, sources, defines: dict | None = None, extra_flags=(), verbose: bool = True,
+                  check: bool | None = None) -> Path:
     """Compile (if not yet built) and return the path of the shared library."""
-    path, flags, exists = library_path(name, sources, defines, extra_flags)
+    path, flags, exists = library_path(name, sources, defines, extra_flags, check)
     if exists:
         return path
+    if CHECK_BUILD if check is None else check:
+        name = name + "_chk"
     nvcc = _nvcc()
     tmp = path.with_suffix(f".tmp{os.getpid()}.so")
     cmd = [nvcc] + flags + ["-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in sources]

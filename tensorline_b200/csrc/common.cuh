@@ -92,6 +92,36 @@ static inline int tl_num_sms() {
     return count[dev];
 }
 
+// The checking build (-DTL_CHECK=1) stands in for a memory checker: every kernel that indexes the block tables
+// or the pages checks the request slot against the table's rows, the page index against the table's width and
+// the page number against the pool, with the limits its launcher was given.  On a violation it records
+// (code 100, kernel, value, limit) in the four ints at `fault`, and reads or writes the sink page / the padding
+// row instead: nothing outside the tensors is touched, no trap, no assert.  Without the define the checks
+// compile to nothing.
+struct TlLimits {
+    int table_rows;      // rows of the block table (request slots + the padding row); 0: unknown, not checked
+    int total_pages;     // first dimension of the page tensors (pool + the sink page); 0: unknown, not checked
+    int* fault;          // four device ints; null: not recorded
+};
+#ifdef TL_CHECK
+#define TL_CHECKING 1
+#else
+#define TL_CHECKING 0
+#endif
+enum { TL_K_ROPE = 1, TL_K_TOKENWISE = 2, TL_K_PREFILL = 3, TL_K_DECODE = 4, TL_K_DECODE_TMA = 5, TL_K_TC_PREFILL = 6,
+       TL_K_TC2_PREFILL = 7 };
+// `v` if 0 <= v < limit (or nothing is known or checked), else limit - 1 after recording the violation.
+__device__ __forceinline__ int tl_checked(int v, int limit, const TlLimits& L, int kernel) {
+#if TL_CHECKING
+    if (limit > 0 && (v < 0 || v >= limit)) {
+        if (L.fault && atomicCAS(L.fault, 0, 100) == 0) { L.fault[1] = kernel; L.fault[2] = v; L.fault[3] = limit; }
+        return limit - 1;
+    }
+#endif
+    return v;
+}
+TL_EXPORT int tl_check_build();
+
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
 // the kernel before it in the stream is still running; its blocks run their set-up and then stop in
 // grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched

@@ -8,6 +8,9 @@
 // The residual stream x is float in both engines, so the residual sum is a 32-bit sum.
 #include "common.cuh"
 
+// 1 if this library was compiled as the checking build (-DTL_CHECK=1).
+TL_EXPORT int tl_check_build() { return TL_CHECKING; }
+
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ x, const TW* __restrict__ table,

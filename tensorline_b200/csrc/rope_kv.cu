@@ -23,7 +23,8 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
                                const int* __restrict__ table, int max_pages, int page_size,
                                const float* __restrict__ inv_freq, int rot, int nq, int nkv, int d,
                                TA* __restrict__ k_pages, TA* __restrict__ v_pages, int interleaved,
-                               const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps) {
+                               const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps,
+                               const TlLimits L) {
     __shared__ float red[33];
     const int t = blockIdx.x, hh = blockIdx.y;
     const int p = pos[t];
@@ -31,7 +32,9 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
     TA* row = qkv + (size_t)t * (nq + 2 * nkv) * d + (size_t)hh * d;
     TA* dst = row;                                               // q is rotated in place
     if (hh >= nq) {
-        const int page = table[(size_t)req_slot[t] * max_pages + p / page_size];
+        const int slot = tl_checked(req_slot[t], L.table_rows, L, TL_K_ROPE);
+        const int page = tl_checked(table[(size_t)slot * max_pages + tl_checked(p / page_size, max_pages, L, TL_K_ROPE)],
+                                    L.total_pages, L, TL_K_ROPE);
         const int kh = hh < nq + nkv ? hh - nq : hh - nq - nkv;
         dst = (hh < nq + nkv ? k_pages : v_pages) +
               (((size_t)page * nkv + kh) * page_size + (p % page_size)) * d;
@@ -92,7 +95,7 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
                                    const int* __restrict__ table, int max_pages, int page_size,
                                    const float* __restrict__ inv_freq, int nq, int nkv, int d,
                                    bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int heads,
-                                   const float* __restrict__ pieces, int splits, size_t plane) {
+                                   const float* __restrict__ pieces, int splits, size_t plane, const TlLimits L) {
     // `pieces` [splits][T][(nq + 2 nkv) d] float: the projection as a split-K product left it.  The pieces are
     // summed in split order and rounded to bfloat16 first, as the separate summing pass would have stored them
     // in qkv; q still goes to qkv, which is then output only.
@@ -107,7 +110,9 @@ __global__ void rope_kv_vec_kernel(bf16* __restrict__ qkv, const TW* __restrict_
     }
     size_t page_base = 0;
     if (heads > nq) {
-        const int page = table[(size_t)req_slot[t] * max_pages + p / page_size];
+        const int slot = tl_checked(req_slot[t], L.table_rows, L, TL_K_ROPE);
+        const int page = tl_checked(table[(size_t)slot * max_pages + tl_checked(p / page_size, max_pages, L, TL_K_ROPE)],
+                                    L.total_pages, L, TL_K_ROPE);
         page_base = ((size_t)page * nkv * page_size + (p % page_size)) * d;
     }
     grid_dependency_wait();                              // angles and the page are ready when the projection ends
@@ -182,7 +187,8 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
                                int page_size, const float* inv_freq, int rot, int nq, int nkv, int d,
                                void* k_pages, void* v_pages, int write_kv, int T, const float* pieces, int splits,
                                long long plane, int interleaved, const float* q_norm, const float* k_norm,
-                               float norm_eps, cudaStream_t stream) {
+                               float norm_eps, int table_rows, int total_pages, int* fault, cudaStream_t stream) {
+    const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
     const int heads = write_kv ? nq + 2 * nkv : nq;
@@ -196,7 +202,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
         const int threads = items < 1024 ? ((items + 31) / 32) * 32 : 1024;
         const size_t smem = (size_t)d * sizeof(float);
 #define VROPE(TW, P) launch_after_wait(rope_kv_vec_kernel<TW, P>, dim3(T), dim3(threads), smem, stream, (bf16*)qkv, (const TW*)bias, \
-            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads, pieces, splits, (size_t)plane)
+            pos, req_slot, table, max_pages, page_size, inv_freq, nq, nkv, d, (bf16*)k_pages, (bf16*)v_pages, heads, pieces, splits, (size_t)plane, L)
         if (bias_dtype == TL_F32) return pieces ? VROPE(float, true) : VROPE(float, false);
         return pieces ? VROPE(bf16, true) : VROPE(bf16, false);
 #undef VROPE
@@ -206,7 +212,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
     const int threads = half < 256 ? ((half + 31) / 32) * 32 : 256;
 #define LAUNCH(TA, TW) rope_kv_kernel<TA, TW><<<grid, threads, 0, stream>>>( \
         (TA*)qkv, (const TW*)bias, pos, req_slot, table, max_pages, page_size, inv_freq, rot, nq, nkv, d, \
-        (TA*)k_pages, (TA*)v_pages, interleaved, q_norm, k_norm, norm_eps)
+        (TA*)k_pages, (TA*)v_pages, interleaved, q_norm, k_norm, norm_eps, L)
     if (act_dtype == TL_F32) { if (bias_dtype == TL_F32) LAUNCH(float, float); else LAUNCH(float, bf16); }
     else                     { if (bias_dtype == TL_F32) LAUNCH(bf16, float);  else LAUNCH(bf16, bf16); }
 #undef LAUNCH

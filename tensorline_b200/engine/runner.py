@@ -287,21 +287,38 @@ class ModelRunner:
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
-            before = ops.launch_count()
+            before, counts = ops.launch_count(), ops.kernel_counts.copy()
             with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="thread_local"):
                 logits = run()
             per_replay = ops.launch_count() - before
+            kernels = dict(ops.kernel_counts - counts)
         finally:
             if gc_was_on:
                 gc.enable()
         hosts = [host] + [host.clone().pin_memory() for _ in range(3)]
-        g = _DecodeGraph(graph, buf, hosts, [None] * len(hosts), logits, tokens, nb, launches=per_replay)
+        g = _DecodeGraph(graph, buf, hosts, [None] * len(hosts), logits, tokens, nb, launches=per_replay, kernels=kernels)
         self._graphs[nb] = g
         return g
 
     # ------------------------------------------------------------------ decode without waiting for the tokens
     def can_replay(self, entries) -> bool:
         return self._can_replay(list(entries))
+
+    def graph_kernels(self, batch: int) -> dict:
+        """Kernel variants inside the decode graph that serves `batch` requests: name -> calls per replay
+        (captures the graph if it does not exist yet)."""
+        nb = self._bucket(batch)
+        return dict((self._graphs.get(nb) or self._capture(nb)).kernels)
+
+    def step_graph(self, entries) -> torch.Tensor:
+        """`step` for entries that `can_replay`: the same batch through the captured decode graph of its
+        batch-size bucket.  Returns the logits [len(entries), vocab] as a view of the graph's output buffer
+        (valid until the next replay of that bucket)."""
+        entries = list(entries)
+        if not self._can_replay(entries):
+            raise ValueError("step_graph takes single tokens of running requests that all want their logits, "
+                             "with graphs switched on")
+        return self._run_graph(entries).logits[:len(entries)]
 
     @torch.inference_mode()
     def launch_decode(self, entries, ids_from=None, draw=None):
@@ -405,3 +422,4 @@ class _DecodeGraph:
     batch: int
     turn: int = 0
     launches: int = 0                   # kernels of this package inside one replay
+    kernels: dict = field(default_factory=dict)         # the same by kernel variant: name -> calls

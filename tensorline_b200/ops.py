@@ -6,11 +6,12 @@ stand-in: a CPU tensor or a missing library raises.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 
 import torch
 
-from .csrc.build import load_library
+from .csrc.build import CHECK_BUILD, load_library
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu"]
 
@@ -21,8 +22,8 @@ _SIGNATURES = {
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _P],
     "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
-                         _I, _P, _P, _F, _P],
-    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+                         _I, _P, _P, _F, _I, _I, _P, _P],
+    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
@@ -69,6 +70,7 @@ def _stream():
 
 
 _launches = 0
+kernel_counts: collections.Counter = collections.Counter()      # calls per kernel variant, by the name its launcher gives
 
 
 def launch_count() -> int:
@@ -87,6 +89,7 @@ def _check(status: int, what: str, launches: int = 1) -> None:
     if status != 0:
         raise KernelError(f"{what}: CUDA error {status} at launch")
     _launches += launches
+    kernel_counts[what] += 1
 
 
 # ---------------------------------------------------------------------------------------------
@@ -102,14 +105,15 @@ STATUS_ROLES = {1: "tcgen05 product: the copy thread waited for a free stage", 2
 
 
 def device_status(device) -> torch.Tensor:
-    """int32 [1 + N_COUNTERS] on `device`: [0] is the status word (0 = no wait ran out), the rest are the
-    per-tile arrival counters of split products (zero between calls)."""
+    """int32 [1 + N_COUNTERS + 4] on `device`: [0] is the status word (0 = no wait ran out), then the per-tile
+    arrival counters of split products (zero between calls), then the four ints in which the checking build of the
+    kernels records an index out of its bounds (code, kernel, value, limit)."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
     t = _status.get(device)
     if t is None:
-        t = torch.zeros(1 + N_COUNTERS, dtype=torch.int32, device=device)
+        t = torch.zeros(1 + N_COUNTERS + 4, dtype=torch.int32, device=device)
         _status[device] = t
     return t
 
@@ -122,10 +126,27 @@ def raise_device_status(device, code: int) -> None:
                       "the step's output is not valid")
 
 
+KERNEL_NAMES = {1: "rotary + page write", 2: "exact-order attention", 3: "mma.sync prompt attention", 4: "decode attention",
+                5: "TMA decode attention", 6: "tcgen05 prompt attention", 7: "two-tile tcgen05 prompt attention"}
+
+
+def fault_words(device):
+    """Device address of the four ints of the checking build, or None when the kernels are the ordinary build."""
+    if not CHECK_BUILD:
+        return None
+    return device_status(device).data_ptr() + 4 * (1 + N_COUNTERS)
+
+
 def check_device_status(device=None) -> None:
-    """Raise if any kernel launched so far gave up on a wait (synchronises; reads one word per device
-    that has one)."""
+    """Raise if any kernel launched so far gave up on a wait or, in the checking build, met an index out of
+    its bounds (synchronises; reads a few words per device that has them)."""
     for dev, t in list(_status.items()):
+        if CHECK_BUILD:
+            code, kernel, value, limit = t[1 + N_COUNTERS:].tolist()
+            if code:
+                t[1 + N_COUNTERS:].zero_()
+                raise KernelError(f"bounds check on {dev}: the {KERNEL_NAMES.get(kernel, kernel)} kernel met index {value}, "
+                                  f"which is outside [0, {limit}); the access went to the sink instead")
         code = int(t[0].item())
         if code:
             raise_device_status(dev, code)
@@ -259,7 +280,7 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
         _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(inv_freq), rot, nq, nkv, d,
         _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T,
         _ptr(pieces), splits, plane, int(pairing == "interleaved"), _ptr(q_norm), _ptr(k_norm), float(norm_eps),
-        _stream()), "rope_kv_write")
+        table.shape[0], k_pages.shape[0] if write_kv else 0, fault_words(qkv.device), _stream()), "rope_kv_write")
 
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -275,7 +296,8 @@ def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: t
     _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
     _check(core().tl_attn_tokenwise(_ptr(q), q_stride, _ptr(out), dtype_code(q.dtype), _ptr(k_pages), _ptr(v_pages),
                                     _ptr(table), table.shape[1], page_size, _ptr(pos), _ptr(req_slot), T, nq, nkv, d,
-                                    int(window or 0), float(scale), _stream()), "attn_tokenwise")
+                                    int(window or 0), float(scale), table.shape[0], k_pages.shape[0], fault_words(out.device),
+                                    _stream()), "attn_tokenwise")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> None:

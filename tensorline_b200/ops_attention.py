@@ -34,12 +34,12 @@ def attn_lib(head_dim: int):
         if os.environ.get("TL_DEC_STAGES"):
             defines["TL_DEC_STAGES"] = int(os.environ["TL_DEC_STAGES"])
         lib = load_library(f"tl_attn_hd{head_dim}", ["attn_mma.cu"], defines)
-        lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P]
+        lib.tl_attn_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _I, _I, _P, _P]
         lib.tl_attn_prefill.restype = ctypes.c_int
-        lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
+        lib.tl_attn_decode.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _I, _P, _P]
         lib.tl_attn_decode.restype = ctypes.c_int
         lib.tl_attn_decode_tma.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
-                                           _F, _I, _I, _P, _P, _P, _I, _P]
+                                           _F, _I, _I, _P, _P, _P, _I, _I, _P, _P]
         lib.tl_attn_decode_tma.restype = ctypes.c_int
         if lib.tl_attn_decode_max_table() != DECODE_MAX_TABLE_ENTRIES:
             raise KernelError(f"the attention library copies {lib.tl_attn_decode_max_table()} block-table entries a block, "
@@ -66,10 +66,10 @@ def attn_tc_lib(head_dim: int):
         if head_dim % 64 or not 64 <= head_dim <= 256:
             raise KernelError(f"head_dim {head_dim}: the tcgen05 attention kernel takes 64, 128, 192 or 256")
         lib = load_library(f"tl_attn_tc_hd{head_dim}", ["attn_tc.cu"], {"HEAD_DIM": head_dim})
-        lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P, _P]
+        lib.tl_attn_tc_prefill.argtypes = [_P, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P, _I, _I, _P, _P]
         lib.tl_attn_tc_prefill.restype = ctypes.c_int
         lib.tl_attn_tc2_prefill.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _F,
-                                            _I, _P, _P, _P]
+                                            _I, _P, _P, _I, _P, _P]
         lib.tl_attn_tc2_prefill.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
@@ -96,6 +96,7 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
                                              _ptr(status_word(q.device)), _ptr(order) if order is not None else None,
+                                             table.shape[0], k_pages.shape[0], ops.fault_words(q.device),
                                              _stream()), "attn_tc_prefill")
 
 
@@ -143,7 +144,7 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
                                             _ptr(status_word(q.device)), _ptr(order) if order is not None else None,
-                                            _stream())
+                                            table.shape[0], ops.fault_words(q.device), _stream())
     if rc == 2:
         return False
     _check(rc, "attn_tc2_prefill")
@@ -190,7 +191,8 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
     _check(attn_lib(d).tl_attn_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                        table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                        nq, nkv, int(window or 0), float(scale), tiles,
-                                       _ptr(order) if order is not None else None, _stream()), "attn_prefill")
+                                       _ptr(order) if order is not None else None, table.shape[0], k_pages.shape[0],
+                                       ops.fault_words(q.device), _stream()), "attn_prefill")
 
 
 TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.async loads only (A/B timing)
@@ -223,15 +225,18 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), chunk, splits,
                                             _ptr(part_o) if splits > 1 and not use_cluster else None,
                                             _ptr(part_ml) if splits > 1 and not use_cluster else None,
-                                            _ptr(status_word(q.device)), int(use_cluster), _stream())
+                                            _ptr(status_word(q.device)), int(use_cluster), table.shape[0],
+                                            ops.fault_words(q.device), _stream())
         if rc != 2:                                    # 2: this build or these sizes do not take the TMA path
-            _check(rc, "attn_decode_tma", launches=2 if splits > 1 and not use_cluster else 1)
+            _check(rc, "attn_decode_tma" + ("+cluster" if use_cluster else "+combine" if splits > 1 else ""),
+                   launches=2 if splits > 1 and not use_cluster else 1)
             return
     _check(attn_lib(d).tl_attn_decode(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                       table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                       nq, nkv, int(window or 0), float(scale), chunk, splits,
                                       _ptr(part_o) if splits > 1 else None, _ptr(part_ml) if splits > 1 else None,
-                                      _stream()), "attn_decode", launches=2 if splits > 1 else 1)
+                                      table.shape[0], k_pages.shape[0], ops.fault_words(q.device),
+                                      _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
 def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale) -> None:

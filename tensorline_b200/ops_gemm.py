@@ -105,7 +105,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), N if pieces else out.stride(0),
                             T, N, K, swap, bn, splits, _ptr(partial), _ptr(st),
                             (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, int(gated), int(use_cluster), _stream()),
-           "gemm_tc", launches=1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2)
+           f"gemm_tc<{bn}>" + ("+gated" if gated else "") + ("+cluster" if use_cluster else "") + ("+pieces" if pieces else "")
+           + ("" if swap else "+rows"), launches=1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2)
     return partial if pieces else out
 
 

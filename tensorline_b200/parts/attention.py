@@ -19,7 +19,7 @@ import torch
 
 from .. import ops
 from ..cache import PagedKV
-from .base import POSITION_ENCODINGS, Part, PartSpec, Runtime, TensorSpec, register_mixer
+from .base import POSITION_ENCODINGS, Part, PartSpec, Rotary, Runtime, TensorSpec, register_mixer
 from .linear import SplitSum, matmul
 
 
@@ -74,6 +74,8 @@ class PagedAttention(Part):
         nq, nkv, d = self.nq, self.nkv, self.d
         T = h.shape[0]
         rotary = self.position.rotary()
+        if not isinstance(rotary, Rotary):               # a plain (inv_freq, rot) pair means rotate-half pairing
+            rotary = Rotary(*rotary)
         inv_freq, rot = rotary.inv_freq, rotary.rot
         plain = rotary.pairing == "half" and self.q_norm is None          # what the kernel's fast path covers
         qkv = matmul(h, self.w_qkv, may_defer=plain and rot == d and d % 16 == 0)

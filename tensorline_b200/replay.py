@@ -1,6 +1,6 @@
 """Trace replay: feed given token ids through a model step by step and write logits.
 
-    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--graphs]
 
 Steps come on standard input, one JSON object a line:
 
@@ -12,7 +12,10 @@ in which logits are wanted, `OUT/<step>.f32` holds them as little-endian float32
 [wanted, vocab], in the order of the entries and of `want`.  After every step a line
 `done <step>` is printed and flushed.  `end` names the requests that are finished after the step;
 their pages and slots are given back and used again.  The cache pool holds `--max-tokens` tokens
-(each live request's count rounded up to whole pages), and not one page more.
+(each live request's count rounded up to whole pages), and not one page more.  With `--graphs`, a
+step whose entries are all single tokens of running requests with `want` [0] (a decode step) is
+replayed from the CUDA graph of its batch-size bucket, as generation does; every other step runs
+as it is.
 """
 from __future__ import annotations
 
@@ -22,7 +25,7 @@ import sys
 from pathlib import Path
 
 
-def make_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = 16, max_live: int = 8):
+def make_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = 16, max_live: int = 8, graphs: bool = False):
     import torch
 
     from .cache import CacheManager
@@ -39,7 +42,9 @@ def make_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = 16, 
     num_pages = max(1, -(-max_tokens // page_size))
     cache = CacheManager(model.cache_needs(), page_size=page_size, num_pages=num_pages, max_num_seqs=max_live,
                          max_model_len=num_pages * page_size, prefix_caching=False)
-    return ModelRunner(model, cache), cfg
+    runner = ModelRunner(model, cache)
+    runner.use_graphs = bool(graphs)
+    return runner, cfg
 
 
 class TraceSession:
@@ -67,7 +72,11 @@ class TraceSession:
                 raise RuntimeError(f"step {rec['step']}: request {rid!r} needs pages for {start + len(toks)} tokens "
                                    f"but the pool of {cache.num_pages} pages (--max-tokens) is exhausted")
             entries.append(StepEntry(rid, toks, list(e.get("want", []))))
-        logits = runner.step(entries)
+        if runner.can_replay(entries):                   # graphs on and a pure decode step
+            logits = runner.step_graph(entries).clone()
+        else:
+            logits = runner.step(entries)
+        runner.check_device_status()
         for e in entries:
             cache.advance(e.rid, runner.positions[e.rid], None)
         for rid in rec.get("end", []):
@@ -85,12 +94,13 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (rounded up per request to whole pages)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--graphs", action="store_true", help="replay decode steps from CUDA graphs, as generation does")
     a = ap.parse_args(argv)
     if a.page_size < 1 or 64 % a.page_size:
         ap.error("--page-size must divide 64")
     out = Path(a.out)
     out.mkdir(parents=True, exist_ok=True)
-    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size)
+    runner, _ = make_runner(a.model, a.dtype, a.max_tokens, page_size=a.page_size, graphs=a.graphs)
     session = TraceSession(runner)
     for line in sys.stdin:
         line = line.strip()

@@ -25,3 +25,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def device_status_is_clean_after_every_gpu_test(request):
+    """No kernel of a GPU test may have given up on a wait, nor (in the checking build) met an index outside its
+    bounds, without the test having seen it."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if torch.cuda.is_available():
+        from tensorline_b200 import ops
+        ops.check_device_status()

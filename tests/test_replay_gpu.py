@@ -40,12 +40,15 @@ def model(request, tmp_path_factory):
     return dict(name=name, folder=folder, reqs=reqs, want=want, page=PAGE_SIZE[name], vocab=V)
 
 
-def replay(model, dtype, steps, max_tokens):
-    """Runs trace records through the engine's own trace session; returns {(rid, position): logits}."""
+def replay(model, dtype, steps, max_tokens, graphs=False, before=None, after=None):
+    """Runs trace records through the engine's own trace session; returns {(rid, position): logits}.
+    `before(runner)` / `after(runner)` run around the steps (the graph tests plant and check bystanders)."""
     from tensorline_b200.replay import TraceSession, make_runner
-    runner, _ = make_runner(model["folder"], dtype, max_tokens, page_size=model["page"])
+    runner, _ = make_runner(model["folder"], dtype, max_tokens, page_size=model["page"], graphs=graphs)
     session = TraceSession(runner)
     got, pos = {}, {}
+    if before:
+        before(runner)
     for rec in steps:
         logits = session.run_step(rec).double().cpu()
         row = 0
@@ -59,6 +62,8 @@ def replay(model, dtype, steps, max_tokens):
         for rid in rec["end"]:
             pos.pop(rid, None)
         runner.cache.check()
+    if after:
+        after(runner)
     assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups), "pages leaked"
     return got
 
@@ -173,6 +178,101 @@ def test_first_tokens_and_long_decoding(model, dtype):
     got = replay(m2, dtype, steps, max_tokens=160)
     check(m2, dtype, got, "token by token")
     assert sorted(p for _, p in got) == list(range(151))
+
+
+def steps_decode_together(model, rids, tail):
+    """The requests `rids`: prompts in portions that share steps, then the last `tail` tokens of all of them one
+    by one in common steps of single tokens; requests end at different steps, so the batch shrinks."""
+    reqs = model["reqs"]
+    steps, done = [], {r: 0 for r in rids}
+    heads = {r: max(1, len(reqs[r]) - tail - i) for i, r in enumerate(rids)}      # decoding starts at different places
+    while any(done[r] < heads[r] for r in rids):
+        entries = []
+        for r in rids:
+            n = min(11, heads[r] - done[r])
+            if n > 0:
+                entries.append({"id": r, "tokens": reqs[r][done[r]:done[r] + n], "want": list(range(n))})
+                done[r] += n
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    decode_steps = 0
+    while any(done[r] < len(reqs[r]) for r in rids):
+        entries, end = [], []
+        for r in rids:
+            if done[r] < len(reqs[r]):
+                entries.append({"id": r, "tokens": [reqs[r][done[r]]], "want": [0]})
+                done[r] += 1
+                if done[r] == len(reqs[r]):
+                    end.append(r)
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        decode_steps += 1
+    return steps, decode_steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_agree_with_eager_steps_and_the_plain_model_and_touch_no_other_page(model, dtype):
+    """Decode steps replayed from CUDA graphs (tzar-beep/Tensorline's tests/test_cuda_graphs.py:20-45): three live
+    requests in the bucket of four (one padding row), then six in the bucket of eight, shrinking as requests end.
+    Every logit against the plain model; in 32-bit bit-equal to the same steps run eagerly.  A bystander request that
+    is live but in no step, and a page filled with a sentinel that no stepped request owns, must come out bit for bit
+    as they went in: padding rows write to the sink page only."""
+    rids = [r for r in model["reqs"] if len(model["reqs"][r]) >= 17]
+    name = model["name"]
+    watched = {}
+
+    def plant(runner):
+        from tensorline_b200.engine.runner import StepEntry
+        from tensorline_b200.parts import KVCacheView
+        cache = runner.cache
+        cache.admit("bystander"); runner.start_request("bystander", 0)
+        toks = random_tokens(model["vocab"], 2 * model["page"] + 1, seed=5)
+        assert cache.grow("bystander", 0, len(toks))
+        runner.step([StepEntry("bystander", toks, [])])
+        cache.admit("sentinel"); runner.start_request("sentinel", 0)
+        assert cache.grow("sentinel", 0, 1)
+        for cid, view in runner.caches.items():
+            if isinstance(view, KVCacheView):
+                g = view.group
+                for p in cache.pages("sentinel", g):
+                    view.k[p].fill_(7.0); view.v[p].fill_(-7.0)
+                pages = [p for p in cache.pages("bystander", g) + cache.pages("sentinel", g) if p >= 0]
+                watched[cid] = (pages, view.k[pages].clone(), view.v[pages].clone())
+
+    def verify(runner):
+        assert watched
+        for cid, (pages, k, v) in watched.items():
+            view = runner.caches[cid]
+            assert torch.equal(view.k[pages], k) and torch.equal(view.v[pages], v), f"cache {cid}: a bystander page changed"
+        for rid in ("bystander", "sentinel"):
+            runner.cache.release(rid); runner.end_request(rid)
+        assert runner.graph_replays >= 1
+
+    spare = (2 * model["page"] + 1 + model["page"] - 1) // model["page"] * model["page"] + model["page"]
+    for group, tail in ((rids[:3], 32), (rids[:6] if len(rids) >= 6 else rids, 10)):
+        if len(group) < 3:
+            continue
+        steps, decode_steps = steps_decode_together(dict(model), group, tail)
+        assert decode_steps >= tail
+        room = sum(-(-len(model["reqs"][r]) // model["page"]) * model["page"] for r in group) + spare
+        m2 = dict(model, reqs={r: model["reqs"][r] for r in group})
+        eager = replay(m2, dtype, steps, room)
+        counted = {}
+
+        def verify_and_count(runner):
+            verify(runner)
+            counted["replays"] = runner.graph_replays
+            counted["buckets"] = sorted(runner._graphs)
+        graphed = replay(m2, dtype, steps, room, graphs=True, before=plant, after=verify_and_count)
+        assert counted["replays"] >= decode_steps
+        assert len(group) in (3, 5, 6, 7) and max(counted["buckets"]) > len(group)      # padding rows were there
+        check(m2, dtype, graphed, f"graphs, {len(group)} requests, {name}")
+        assert graphed.keys() == eager.keys()
+        if dtype == "float32":
+            for key in graphed:
+                assert torch.equal(graphed[key], eager[key]), f"graph replay differs from the eager step at {key}"
+        else:
+            scale = max(float(w.abs().max()) for w in model["want"].values())
+            worst = max(float((graphed[k] - eager[k]).abs().max()) for k in graphed)
+            assert worst <= BF16_MODEL_REL * scale
 
 
 def test_pool_that_is_too_small_is_reported(model):

@@ -21,6 +21,8 @@ def _define():
 
     @register_mixer("toy_decaying_sum")
     class DecayingSum(Part):
+        graph_capturable = True          # a step of single tokens is served from device tensors only (see forward)
+
         def __init__(self, rt, hidden, decay):
             super().__init__(rt)
             self.hidden, self.decay = hidden, decay
@@ -35,6 +37,11 @@ def _define():
             self.w = self._compute_copy(weights[f"{prefix}.mix.weight"])
 
         def forward(self, h, ctx, cache):
+            if ctx.decode_only:                              # one token a request: all requests at once, by slot, on the
+                idx = ctx.slots.long()                       # device (this is what a CUDA graph captures; padding rows
+                s = self.decay * cache.state.index_select(0, idx) + h.float()      # carry the spare slot)
+                cache.state.index_copy_(0, idx, s)
+                return matmul(s.to(h.dtype), self.w)
             sums = torch.empty((h.shape[0], self.hidden), dtype=torch.float32, device=h.device)
             for b in range(ctx.B):                           # tokens of a request in order; state carried on
                 slot, s = ctx.h_slots[b], None
@@ -129,3 +136,28 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
     cache.release("a"); runner.end_request("a")
     again = whole("c", a)
     assert_close(again, want_a, "state slot reused", **tol)
+
+
+def test_toy_state_model_decodes_through_cuda_graphs(tmp_path):
+    """State of fixed size lives at fixed addresses indexed by slot, so the model with the toy mixer is captured
+    like any other: the engine with graphs and overlapped scheduling gives the tokens of the engine without, under
+    queueing (slots are reused) and with a preemption (state is rebuilt from the first token)."""
+    from tensorline_b200 import Engine, SamplingParams
+    from tensorline_b200.models import expected_tensors
+    from tensorline_b200.weights import write_random_model
+    ToyConfig = _define()
+    cfg = ToyConfig("ToyStateLM", 120, 32, 0.9)
+    folder = write_random_model(tmp_path / "toy", cfg, expected_tensors(cfg), seed=5, std=0.2)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 120, (n,), generator=g).tolist() for n in (9, 2, 14, 5, 11)]
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    outs = {}
+    for graphs in (False, True):
+        eng = Engine(str(folder), dtype="float32", block_size=4, num_blocks=12, max_num_seqs=3, max_model_len=48,
+                     cuda_graphs=graphs, overlap=graphs)
+        assert eng.runner._graphable
+        outs[graphs] = [o.token_ids for o in eng.generate(prompts, sp)]
+        st = eng.stats()
+        assert (st["graph_replays"] > 0) == graphs and (st["overlapped_steps"] > 0) == graphs
+        assert st["free_pages"] == st["num_pages"] and st["preemptions"] > 0 and st["max_running_seen"] == 3
+    assert outs[True] == outs[False] and all(len(t) == 10 for t in outs[True])

@@ -79,7 +79,7 @@ def _define():
             self.dim, self.eps = dim, eps
 
         def expected_tensors(self, prefix):
-            return {f"{prefix}.weight": TensorSpec((self.dim,)), f"{prefix}.bias": TensorSpec((self.dim,))}
+            return {f"{prefix}.weight": TensorSpec((self.dim,), init="ones"), f"{prefix}.bias": TensorSpec((self.dim,))}
 
         def bind(self, weights, prefix):
             self.w, self.b = weights[f"{prefix}.weight"].float(), weights[f"{prefix}.bias"].float()
@@ -227,3 +227,191 @@ def test_toy_feed_forward_position_encoding_and_norm(dtype, tmp_path):
         else:
             err = (res - want[rid]).abs().amax(-1) / want[rid].abs().amax()
             assert float(err.median()) < 0.03 and float((err < 0.06).double().mean()) >= 0.8, err
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# A second toy architecture: an embedding that scales its rows, an output head with a bias and a soft cap, a rotary
+# encoding over interleaved pairs of half the head's dimensions, and an RMS norm of every q and k head before the
+# rotation.  All four are options of other published decoders; none is this engine's architecture.  The embedding,
+# the head and the encoding are classes of THIS file; pairing and q/k norm are arguments of the package's fused kernel.
+
+H2, V2, HEADS2, KV2, D2, ROT2, CAP, THETA2 = 48, 70, 4, 2, 16, 8, 5.0, 50.0
+
+
+def _define_scaled():
+    from tensorline_b200 import ops
+    from tensorline_b200.models import LayerSpec, ModelSpec, RunEntry, register_architecture
+    from tensorline_b200.parts import (Part, PartSpec, Rotary, TensorSpec, register_embedding, register_head,
+                                       register_position_encoding)
+    from tensorline_b200.parts.linear import matmul
+
+    @register_embedding("toy_scaled_table")
+    class ScaledTable(Part):
+        graph_capturable = True
+
+        def __init__(self, rt, vocab, dim):
+            super().__init__(rt)
+            self.vocab, self.dim = vocab, dim
+
+        def expected_tensors(self, prefix):
+            return {f"{prefix}.weight": TensorSpec((self.vocab, self.dim))}
+
+        def bind(self, weights, prefix):
+            self.weight = self._compute_copy(weights[f"{prefix}.weight"])
+
+        def forward(self, ids):
+            x = torch.empty((ids.numel(), self.dim), dtype=torch.float32, device=ids.device)
+            ops.embed(x, self.weight, ids)
+            return x.mul_(self.dim ** 0.5)
+
+    @register_head("toy_capped")
+    class CappedHead(Part):
+        graph_capturable = True
+
+        def __init__(self, rt, vocab, dim, tied, cap):
+            super().__init__(rt)
+            self.vocab, self.dim, self.tied, self.cap = vocab, dim, tied, cap
+
+        def expected_tensors(self, prefix):
+            return {f"{prefix}.weight": TensorSpec((self.vocab, self.dim), optional=self.tied),
+                    f"{prefix}.bias": TensorSpec((self.vocab,))}
+
+        def bind(self, weights, prefix, embedding=None):
+            self.weight = embedding.weight if self.tied else self._compute_copy(weights[f"{prefix}.weight"])
+            self.bias = weights[f"{prefix}.bias"].float()
+
+        def forward(self, h):
+            z = matmul(h, self.weight, out_dtype=torch.float32) + self.bias
+            return self.cap * torch.tanh(z / self.cap)
+
+    @register_position_encoding("toy_rotary_interleaved")
+    class RotaryInterleaved(Part):
+        graph_capturable = True
+
+        def __init__(self, rt, head_dim, theta, rotary_dim):
+            super().__init__(rt)
+            i = torch.arange(0, rotary_dim, 2, dtype=torch.float64)
+            self.rot = rotary_dim
+            self.inv_freq = (float(theta) ** (-i / rotary_dim)).to(torch.float32).to(rt.device)
+
+        def rotary(self):
+            return Rotary(self.inv_freq, self.rot, "interleaved")
+
+        def on_embedding(self, x, ctx):
+            return None
+
+    @dataclass(frozen=True)
+    class ScaledConfig:
+        architecture: str
+
+        @classmethod
+        def from_dict(cls, raw, where="config.json"):
+            return cls(raw["architectures"][0])
+
+        def to_json_dict(self):
+            return {"architectures": [self.architecture]}
+
+    def describe(cfg):
+        rms = PartSpec("rms_norm", {"dim": H2, "eps": 1e-5})
+        ff = PartSpec("gated_mlp", {"hidden": H2, "intermediate": 56})
+        attn = PartSpec("paged_attention", {"hidden": H2, "num_heads": HEADS2, "num_kv_heads": KV2, "head_dim": D2,
+                                            "qkv_bias": True, "qk_norm_eps": 1e-4,
+                                            "position": PartSpec("toy_rotary_interleaved", {"theta": THETA2, "rotary_dim": ROT2})})
+        block = PartSpec("pre_norm", {"mixer": attn, "feed_forward": ff, "norm1": rms, "norm2": rms})
+        return ModelSpec(vocab_size=V2, hidden_size=H2, layers=tuple(LayerSpec(block, f"model.layers.{i}") for i in range(2)),
+                         run=(RunEntry(0), RunEntry(1)), final_norm=rms, tie_word_embeddings=True,
+                         embedding=PartSpec("toy_scaled_table"), head=PartSpec("toy_capped", {"cap": CAP}))
+
+    register_architecture("ToyScaledLM", ScaledConfig, describe)
+    return ScaledConfig
+
+
+def _plain_scaled(w, ids):
+    f = lambda name: w[name].double()
+    n = len(ids)
+    x = f("model.embed_tokens.weight")[ids] * H2 ** 0.5
+
+    def rms(v, weight, eps):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
+
+    i = torch.arange(0, ROT2, 2, dtype=torch.float64)
+    inv_freq = (THETA2 ** (-i / ROT2)).to(torch.float32)
+    angle = (torch.arange(n, dtype=torch.float32)[:, None] * inv_freq[None, :]).double()
+    cos, sin = torch.cos(angle), torch.sin(angle)
+
+    def rotate(t):                                               # [n, heads, D2]: pairs (2i, 2i + 1) of the first ROT2 dims
+        out = t.clone()
+        a, b = t[..., 0:ROT2:2], t[..., 1:ROT2:2]
+        out[..., 0:ROT2:2] = a * cos[:, None, :] - b * sin[:, None, :]
+        out[..., 1:ROT2:2] = b * cos[:, None, :] + a * sin[:, None, :]
+        return out
+
+    mask = torch.tril(torch.ones(n, n, dtype=torch.bool))
+    for layer in range(2):
+        p = f"model.layers.{layer}"
+        h = rms(x, f(p + ".input_layernorm.weight"), 1e-5)
+        a = p + ".self_attn"
+        q = (h @ f(a + ".q_proj.weight").T + f(a + ".q_proj.bias")).view(n, HEADS2, D2)
+        k = (h @ f(a + ".k_proj.weight").T + f(a + ".k_proj.bias")).view(n, KV2, D2)
+        v = (h @ f(a + ".v_proj.weight").T + f(a + ".v_proj.bias")).view(n, KV2, D2)
+        q = rotate(rms(q, f(a + ".q_norm.weight"), 1e-4))
+        k = rotate(rms(k, f(a + ".k_norm.weight"), 1e-4))
+        out = torch.empty(n, HEADS2, D2, dtype=torch.float64)
+        for hd in range(HEADS2):
+            s = (q[:, hd] @ k[:, hd // (HEADS2 // KV2)].T) * D2 ** -0.5
+            out[:, hd] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, hd // (HEADS2 // KV2)]
+        x = x + out.reshape(n, HEADS2 * D2) @ f(a + ".o_proj.weight").T
+        h = rms(x, f(p + ".post_attention_layernorm.weight"), 1e-5)
+        g, u = h @ f(p + ".mlp.gate_proj.weight").T, h @ f(p + ".mlp.up_proj.weight").T
+        x = x + (g / (1 + torch.exp(-g)) * u) @ f(p + ".mlp.down_proj.weight").T
+    z = rms(x, f("model.norm.weight"), 1e-5) @ f("model.embed_tokens.weight").T + f("lm_head.bias")
+    return CAP * torch.tanh(z / CAP)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_embedding_head_pairing_and_qk_norm(dtype, tmp_path):
+    """Portions beside single tokens, then the last tokens decoded through CUDA graphs, against the float64 loop."""
+    from tensorline_b200.cache import CacheManager
+    from tensorline_b200.engine.runner import ModelRunner, StepEntry
+    from tensorline_b200.models import expected_tensors, load_model
+    from tensorline_b200.parts import Runtime
+    from tensorline_b200.weights import write_random_model
+    from tensorline_b200.weights.safetensors_io import SafetensorsFile
+    ScaledConfig = _define_scaled()
+    cfg = ScaledConfig("ToyScaledLM")
+    expected = expected_tensors(cfg)
+    assert "lm_head.bias" in expected and "model.layers.1.self_attn.k_norm.weight" in expected
+    assert expected["lm_head.weight"].optional                  # tied: the table is the embedding's
+    folder = write_random_model(tmp_path / "toy2", cfg, expected, seed=11, std=0.15, norm_std=0.2)
+    model, _ = load_model(folder, Runtime(torch.device("cuda"), dtype, 4))
+    assert model.graph_capturable()
+    cache = CacheManager(model.cache_needs(), page_size=4, num_pages=30, max_num_seqs=3, max_model_len=64)
+    runner = ModelRunner(model, cache)
+    runner.use_graphs = True
+    st = SafetensorsFile(folder / "model.safetensors")
+    weights = {name: st.tensor(name).clone() for name in st.names()}
+    g = torch.Generator().manual_seed(2)
+    seqs = {"a": torch.randint(0, V2, (25,), generator=g).tolist(), "b": torch.randint(0, V2, (18,), generator=g).tolist()}
+    want = {rid: _plain_scaled(weights, torch.tensor(toks)) for rid, toks in seqs.items()}
+    for rid in seqs:
+        cache.admit(rid); runner.start_request(rid)
+    got, done = {"a": [], "b": []}, {"a": 0, "b": 0}
+    plan = [[("a", 7)], [("a", 2), ("b", 9)], [("b", 1), ("a", 1)], [("a", 9), ("b", 2)]] + [[("a", 1), ("b", 1)]] * 6
+    for step in plan:
+        entries = []
+        for rid, n in step:
+            cache.grow(rid, done[rid], done[rid] + n)
+            entries.append(StepEntry(rid, seqs[rid][done[rid]:done[rid] + n], list(range(n))))
+            done[rid] += n
+        out = runner.step_graph(entries).clone() if runner.can_replay(entries) else runner.step(entries)
+        row = 0
+        for rid, n in step:
+            got[rid].append(out[row:row + n]); row += n
+    assert runner.graph_replays == 7 and done == {"a": 25, "b": 18}
+    for rid in seqs:
+        res = torch.cat(got[rid]).double().cpu()
+        if dtype == torch.float32:
+            assert_close(res, want[rid], f"scaled toy model, request {rid}", rtol=1e-4, atol=1e-4)
+        else:
+            err = float((res - want[rid]).abs().max())
+            assert err <= 0.05 * float(want[rid].abs().max()), f"request {rid}: {err:.3e}"

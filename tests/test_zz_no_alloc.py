@@ -6,8 +6,9 @@ runtime's memory plan, or on a path where an allocation may block, or they are C
 allocator.  For them the scratch of the split-KV kernel is a fixed array inside the library.  This
 test calls that entry point through its exported C symbol, twice in a row with different shapes (the
 array keeps the first call's contents, which the second call must not see), and compares its output
-with the ordinary entry point's, which gets torch-allocated scratch.  It also checks that a request
-beyond the array's size is refused with a message.  The file name makes pytest collect it last.
+with the ordinary entry point's, which gets torch-allocated scratch, and with the attention formula
+written out in float64.  It also checks that a request beyond the array's size is refused with a
+message, and a context that ends exactly at chunk * splits.  The file name makes pytest collect it last.
 """
 import ctypes
 
@@ -34,6 +35,21 @@ def _setup(B, ctx_lens, nq, nkv, d, ps, seed):
         used += need
     q = (torch.randn(B, nq * d, generator=g) * 2).to(torch.bfloat16).cuda()
     return q, kp, vp, table_tensor(rows, max_pages, num_pages), num_pages
+
+
+def _plain_rows(q, kp, vp, table, ps, ctx_lens, nq, nkv, d):
+    """softmax(q k^T / sqrt(d)) v over the keys 0..ctx_len of each request, float64 (tensorline/paged_attn.py:33-57)."""
+    out = torch.zeros(len(ctx_lens), nq * d, dtype=torch.float64)
+    qf, kf, vf, tab = q.double().cpu(), kp.double().cpu(), vp.double().cpu(), table.cpu()
+    for b, last in enumerate(ctx_lens):
+        pos = torch.arange(last + 1)
+        pages, offs = tab[b, pos // ps].long(), pos % ps
+        for h in range(nq):
+            kh = h // (nq // nkv)
+            k, v = kf[pages, kh, offs], vf[pages, kh, offs]
+            s = (k @ qf[b, h * d:(h + 1) * d]) * d ** -0.5
+            out[b, h * d:(h + 1) * d] = torch.softmax(s, 0) @ v
+    return out
 
 
 def _static_call(lib, q, out, kp, vp, table, ps, B, ctx_lens, nq, nkv, d, chunk, splits):
@@ -66,6 +82,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         assert rc == 0, msg
         assert float(want.float().abs().max()) > 0.1
         assert_close(got, want, f"static scratch, B={B}", **BF16)
+        assert_close(got, _plain_rows(q, kp, vp, table, ps, ctx_lens, nq, nkv, d), f"static scratch against the formula, B={B}", **BF16)
     # one range per request needs no scratch at all
     q, kp, vp, table, _ = _setup(2, [100, 30], nq, nkv, d, ps, 3)
     want, got = (torch.zeros(2, nq * d, dtype=torch.bfloat16, device="cuda") for _ in range(2))
@@ -74,6 +91,13 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
     rc, msg = _static_call(lib, q, got, kp, vp, table, ps, 2, [100, 30], nq, nkv, d, 128, 1)
     assert rc == 0, msg
     assert_close(got, want, "static scratch, one range", **BF16)
+    assert_close(got, _plain_rows(q, kp, vp, table, ps, [100, 30], nq, nkv, d), "static scratch against the formula, one range", **BF16)
+    # the key ranges must cover the longest context: one that ends exactly at chunk * splits is read to its last key
+    q, kp, vp, table, _ = _setup(2, [255, 17], nq, nkv, d, ps, 5)
+    got = torch.zeros(2, nq * d, dtype=torch.bfloat16, device="cuda")
+    rc, msg = _static_call(lib, q, got, kp, vp, table, ps, 2, [255, 17], nq, nkv, d, 64, 4)       # 4 ranges of 64 = 256 keys
+    assert rc == 0, msg
+    assert_close(got, _plain_rows(q, kp, vp, table, ps, [255, 17], nq, nkv, d), "context ending at chunk * splits", **BF16)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
