@@ -11,6 +11,7 @@ Its server, quantization, speculation and multi-model options (--host, --port, -
     tensorline --model DIR --prompt-ids 1,2,3 --max-tokens 16
     tensorline random-weights --config config.json --out DIR --seed 0
     tensorline replay --model DIR --dtype float32 --out DIR --max-tokens 4096 < trace.jsonl
+    tensorline bench [--model 7b|14b|32b] [--workload decode|mix] [--profile] ...
 """
 from __future__ import annotations
 
@@ -116,6 +117,9 @@ def main(argv=None) -> int:
     if argv and argv[0] == "replay":
         from .replay import main as replay_main
         return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        from .benchmark import main as bench_main
+        return bench_main(argv[1:])
     if argv and argv[0] == "generate":
         argv = argv[1:]
     return cmd_generate(argv)

@@ -112,6 +112,7 @@ class Engine:
         self.overlap = bool(o.overlap and o.cuda_graphs)
         self._ahead: _StepInFlight | None = None
         self.overlapped_steps = 0
+        self.last_step_kind = "idle"                     # what the last step() held: "decode", "prompt", "mixed" or "idle"
 
     # ------------------------------------------------------------------ requests
     def _encode(self, prompt):
@@ -193,10 +194,12 @@ class Engine:
         try:
             if self._ahead is not None:
                 if not self._may_run_ahead(self._ahead):
+                    self.last_step_kind = "idle"         # only reads the step in flight back
                     return self.flush()
                 earlier = self._ahead
                 self._ahead = self._start_decode(earlier.requests, after=earlier)
                 self.overlapped_steps += 1
+                self.last_step_kind = "decode"
                 return self._collect(earlier)
             return self._scheduled_step()
         except Exception as e:                           # tensorline/batch_engine.py:568-576
@@ -209,6 +212,8 @@ class Engine:
         sch = self.scheduler
         plan = sch.schedule()
         self._sync_runner()
+        ones, rest = plan.kinds()
+        self.last_step_kind = "idle" if not plan else "decode" if not rest else "prompt" if not ones else "mixed"
         if not plan:
             return []
         entries = []

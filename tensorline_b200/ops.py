@@ -90,6 +90,8 @@ def _check(status: int, what: str, launches: int = 1) -> None:
         raise KernelError(f"{what}: CUDA error {status} at launch")
     _launches += launches
     kernel_counts[what] += 1
+    if _profile is not None:
+        mark(what)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -164,6 +166,42 @@ def num_sms(device=None) -> int:
 
 
 _sm_counts: dict = {}
+
+
+# ---------------------------------------------------------------------------------------------
+# Profile: an event after every launch; the time between two events goes to the later one's name.
+
+_profile = None
+
+
+def start_profile() -> None:
+    global _profile
+    torch.cuda.synchronize()
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    _profile = [("start", first)]
+
+
+def mark(name: str) -> None:
+    """Inside a profile: everything launched since the last mark belongs to `name` (the launchers of this package
+    call it themselves; callers of library kernels call it after them)."""
+    if _profile is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        _profile.append((name, ev))
+
+
+def stop_profile() -> dict:
+    """name -> (calls, milliseconds) since `start_profile`."""
+    global _profile
+    marks, _profile = _profile, None
+    torch.cuda.synchronize()
+    out: dict = {}
+    for (_, before), (name, ev) in zip(marks, marks[1:]):
+        name = name.split("<")[0].split("+")[0] if name.startswith(("gemm_tc", "attn_")) else name
+        calls, ms = out.get(name, (0, 0.0))
+        out[name] = (calls + 1, ms + before.elapsed_time(ev))
+    return out
 
 
 def _contig(t: torch.Tensor, name: str) -> None:

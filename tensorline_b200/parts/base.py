@@ -113,6 +113,9 @@ class Rotary:
     def __iter__(self):                 # (inv_freq, rot) = encoding.rotary() still unpacks
         return iter((self.inv_freq, self.rot))
 
+    def __getitem__(self, i):
+        return (self.inv_freq, self.rot)[i]
+
 
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")

@@ -59,6 +59,6 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
         from .. import ops_gemm
         y = ops_gemm.gemm_tc(x, w, out_dtype or x.dtype, pieces=may_defer)
         return SplitSum(y, out_dtype or x.dtype) if y.dim() == 3 else y
-    if out_dtype is not None and out_dtype != x.dtype:
-        return torch.mm(x, w.t(), out_dtype=out_dtype)
-    return torch.mm(x, w.t())
+    y = torch.mm(x, w.t(), out_dtype=out_dtype) if out_dtype is not None and out_dtype != x.dtype else torch.mm(x, w.t())
+    ops.mark("library product")
+    return y

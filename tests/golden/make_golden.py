@@ -8,12 +8,23 @@ operations in a layer, the residual folded into the norms, the rotate-half pairi
 into pages, the three attention paths (decode, fresh prompt, resumed portion) with their masks, the
 scale and the grouping of query heads.
 
-What does NOT come from it: tzar-beep/Tensorline has no model definition of its own; it re-drives
-the sub-modules of a model object built by an installed package (tensorline/paged.py:13-14,
-:172-188).  No installed package's model code is used here.  The object handed to `PagedModel` is a
-shim defined below whose sub-modules (RMSNorm, the rotary table, the SwiGLU feed-forward, the linear
-projections) are written from the formulas, in float32.  So the golden values rest on the
-reference's code for everything it owns and on the formulas for the rest.
+tzar-beep/Tensorline has no model definition of its own; it re-drives the sub-modules of a model
+object that ITS OWN loader builds through an installed package (tensorline/engine.py:63-66,
+tensorline/paged.py:13-14, :172-188).  Two sets of values are written for every model:
+
+* `as_it_runs`: the reference exactly as it runs.  A model folder with the seeded weights, a
+  config.json and a word-level tokenizer is written here; the reference's own `Engine(folder,
+  device="cpu", dtype="float32")` loads it (its code, its imports; this script imports no installed
+  package's model code and reads none); the loaded object goes to `PagedModel` as the reference's
+  `BatchEngine` does (tensorline/batch_engine.py:87-88).  RMSNorm, SwiGLU and the rotary table are
+  then whatever the reference really executes, not this repository's reading of them.  For the
+  window model (Tiny B) the reference's paged path has no window (tensorline/paged.py:230-237), so
+  its one-request engine is used instead: `Engine.stream` (tensorline/engine.py:86-120), greedy,
+  through its public interface; the generated token ids are stored.
+* `shim`: `PagedModel` over a stand-in object whose sub-modules are written from the formulas in
+  float32 (kept as a second, independent entry).
+
+tests/test_plain.py checks the plain implementation against both.
 
 Usage (from the repository root, with the reference project's folder as argument):
     python tests/golden/make_golden.py /path/to/Tensorline
@@ -108,41 +119,93 @@ class ShimModel(nn.Module):
         self.lm_head = _linear(head)
 
 
+def add_loader_files(folder, raw: dict) -> None:
+    """What the reference's loader needs beside config.json and model.safetensors: a `model_type` key and a
+    tokenizer.  The tokenizer is word level: token id i is the word "t<i>", words are split on white space."""
+    cfg = json.loads((Path(folder) / "config.json").read_text())
+    cfg.update(model_type="qwen2", torch_dtype="float32", bos_token_id=raw["eos_token_id"])
+    (Path(folder) / "config.json").write_text(json.dumps(cfg))
+    V = raw["vocab_size"]
+    tok = {"version": "1.0", "truncation": None, "padding": None, "added_tokens": [], "normalizer": None,
+           "pre_tokenizer": {"type": "WhitespaceSplit"}, "post_processor": None, "decoder": None,
+           "model": {"type": "WordLevel", "vocab": {f"t{i}": i for i in range(V)}, "unk_token": "t0"}}
+    (Path(folder) / "tokenizer.json").write_text(json.dumps(tok))
+    (Path(folder) / "tokenizer_config.json").write_text(json.dumps(
+        {"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": f"t{raw['eos_token_id']}", "unk_token": "t0",
+         "model_max_length": 4096}))
+
+
+def three_schedules(PagedModel, SeqChunk, model, ids, table, bs) -> dict:
+    """Logits at the last position from the reference's paged model: the prompt whole, in portions of three
+    tokens (resumed portions through the pages), and 20 tokens then one by one (its decode path)."""
+    rows = {}
+    pm = PagedModel(model, num_blocks=16, block_size=bs)
+    rows["whole"] = pm.forward([SeqChunk(ids, 0, table, True)])[0]
+    pm = PagedModel(model, num_blocks=16, block_size=bs)
+    for s in range(0, len(ids), 3):
+        last = pm.forward([SeqChunk(ids[s:s + 3], s, table, True)])[0]
+    rows["chunks_of_3"] = last
+    pm = PagedModel(model, num_blocks=16, block_size=bs)
+    pm.forward([SeqChunk(ids[:20], 0, table, False)])
+    for s in range(20, len(ids)):
+        last = pm.forward([SeqChunk(ids[s:s + 1], s, table, True)])[0]
+    rows["decode_tail"] = last
+    return rows
+
+
 def main(ref_root: str) -> None:
     sys.path.insert(0, ref_root)
-    from tensorline.paged import PagedModel, SeqChunk          # the reference's own code
+    from tensorline.engine import Engine as ReferenceEngine    # the reference's own loader and one-request engine
+    from tensorline.engine import GenStats, SamplingParams
+    from tensorline.paged import PagedModel, SeqChunk          # the reference's own paged model
 
     out = {}
-    for name in ("A", "B_FULL"):                                # the reference has no window: full attention only
+    for name in ("A", "B_FULL"):                                # the reference's paged path has no window
         with tempfile.TemporaryDirectory() as tmp:
             folder = write_tiny(name, tmp, seed=0)
             plain = PlainQwen2(folder)
-            shim = ShimModel(folder).eval()
             bs = PAGE_SIZE[name]
             ids = random_tokens(CONFIGS[name]["vocab_size"], 29, seed=11)
             table = [5, 2, 7, 0, 9, 11, 3, 1][: -(-len(ids) // bs)]
             ref_all = forward(plain, ids)
-            rows = {}
-            pm = PagedModel(shim, num_blocks=16, block_size=bs)
-            rows["whole"] = pm.forward([SeqChunk(ids, 0, table, True)])[0]
-            pm = PagedModel(shim, num_blocks=16, block_size=bs)
-            for s in range(0, len(ids), 3):                     # resumed portions through the pages
-                last = pm.forward([SeqChunk(ids[s:s + 3], s, table, True)])[0]
-            rows["chunks_of_3"] = last
-            pm = PagedModel(shim, num_blocks=16, block_size=bs)
-            pm.forward([SeqChunk(ids[:20], 0, table, False)])
-            for s in range(20, len(ids)):                       # then token by token (the decode path)
-                last = pm.forward([SeqChunk(ids[s:s + 1], s, table, True)])[0]
-            rows["decode_tail"] = last
             weights = read_safetensors(folder / "model.safetensors")
             checksum = float(sum(v.double().abs().sum() for v in weights.values()))
             rec = {"ids": ids, "weights_abs_sum": checksum, "position": len(ids) - 1, "logits": {}}
-            for k, v in rows.items():
-                diff = float((v.double() - ref_all[-1]).abs().max())
-                print(f"{name} {k}: reference vs plain max abs diff {diff:.3e} (logit scale {float(ref_all[-1].abs().max()):.3f})")
-                assert diff < 2e-5, "the plain implementation and the reference disagree"
-                rec["logits"][k] = [round(float(x), 7) for x in v.tolist()]
+            shim = ShimModel(folder).eval()
+            add_loader_files(folder, CONFIGS[name])
+            loaded = ReferenceEngine(str(folder), device="cpu", dtype="float32")
+            for how, model in (("as_it_runs", loaded.model), ("shim", shim)):
+                with torch.inference_mode():
+                    rows = three_schedules(PagedModel, SeqChunk, model, ids, table, bs)
+                for k, v in rows.items():
+                    diff = float((v.double() - ref_all[-1]).abs().max())
+                    print(f"{name} {how} {k}: reference vs plain max abs diff {diff:.3e} "
+                          f"(logit scale {float(ref_all[-1].abs().max()):.3f})")
+                    assert diff < 2e-5, "the plain implementation and the reference disagree"
+                    rec["logits"][f"{how}/{k}"] = [round(float(x), 7) for x in v.tolist()]
             out[name] = rec
+    # The window model: the reference's one-request engine, greedy, through its public interface.
+    with tempfile.TemporaryDirectory() as tmp:
+        from tests.plain.qwen2_plain import greedy_generate
+        folder = write_tiny("B", tmp, seed=0)
+        plain = PlainQwen2(folder)
+        no_window = PlainQwen2(write_tiny("B_FULL", Path(tmp) / "full", seed=0))      # the same weights, all keys visible
+        weights = read_safetensors(folder / "model.safetensors")
+        checksum = float(sum(v.double().abs().sum() for v in weights.values()))
+        add_loader_files(folder, CONFIGS["B"])
+        loaded = ReferenceEngine(str(folder), device="cpu", dtype="float32")
+        rec = {"weights_abs_sum": checksum, "window": CONFIGS["B"]["sliding_window"], "greedy": []}
+        for n, seed in ((40, 21), (57, 22)):                   # prompts longer than the window of 24
+            prompt = random_tokens(CONFIGS["B"]["vocab_size"], n, seed=seed)
+            text = "".join(loaded.stream(" ".join(f"t{t}" for t in prompt),
+                                         SamplingParams(max_tokens=24, stop_token_ids={-1}), GenStats()))
+            got = [int(w[1:]) for w in text.split()]
+            mine = greedy_generate(plain, prompt, 24)
+            print(f"B window, prompt of {n}: reference {got[:8]}..., plain {mine[:8]}..., equal: {got == mine}")
+            assert got == mine, "the plain window model and the reference's engine disagree"
+            assert greedy_generate(no_window, prompt, 24) != got, "the window changes nothing here: the comparison pins nothing"
+            rec["greedy"].append({"prompt": prompt, "tokens": got})
+        out["B"] = rec
     path = Path(__file__).with_name("reference_logits.json")
     path.write_text(json.dumps(out))
     print("wrote", path, path.stat().st_size, "bytes")

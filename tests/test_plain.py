@@ -12,17 +12,38 @@ from tests.tiny import random_tokens, write_tiny
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "reference_logits.json").read_text())
 
 
-@pytest.mark.parametrize("name", sorted(GOLDEN))
+@pytest.mark.parametrize("name", ["A", "B_FULL"])
 def test_plain_matches_the_reference_projects_outputs(name, tmp_path):
+    """Against the reference as it really runs (its own loader's model object under its paged model: `as_it_runs/*`)
+    and against its paged model over a stand-in written from the formulas (`shim/*`), three schedules each."""
     rec = GOLDEN[name]
     folder = write_tiny(name, tmp_path / "m", seed=0)
     weights = plain.read_safetensors(folder / "model.safetensors")
     checksum = float(sum(v.double().abs().sum() for v in weights.values()))
     assert checksum == pytest.approx(rec["weights_abs_sum"], rel=1e-12), "the seeded weights changed"
     logits = plain.forward(plain.PlainQwen2(folder), rec["ids"])[rec["position"]]
+    assert sorted(rec["logits"]) == sorted(f"{how}/{cut}" for how in ("as_it_runs", "shim")
+                                           for cut in ("whole", "chunks_of_3", "decode_tail"))
     for how, ref in rec["logits"].items():
         ref = torch.tensor(ref, dtype=torch.float64)
         assert float((logits - ref).abs().max()) < 2e-5, how          # the reference ran in float32
+
+
+def test_plain_window_model_generates_what_the_reference_engine_generated(tmp_path):
+    """Tiny B (layers 1 and 2 see the last 24 keys): greedy tokens of the reference's one-request engine, as stored
+    by tests/golden/make_golden.py, for prompts longer than the window; the same weights without the window give
+    other tokens, so the comparison pins `sliding_window` and `max_window_layers`."""
+    rec = GOLDEN["B"]
+    folder = write_tiny("B", tmp_path / "m", seed=0)
+    weights = plain.read_safetensors(folder / "model.safetensors")
+    assert float(sum(v.double().abs().sum() for v in weights.values())) == pytest.approx(rec["weights_abs_sum"], rel=1e-12)
+    m = plain.PlainQwen2(folder)
+    full = plain.PlainQwen2(write_tiny("B_FULL", tmp_path / "f", seed=0))
+    assert rec["window"] == 24 and len(rec["greedy"]) == 2
+    for case in rec["greedy"]:
+        assert len(case["prompt"]) > rec["window"]
+        assert plain.greedy_generate(m, case["prompt"], len(case["tokens"])) == case["tokens"]
+        assert plain.greedy_generate(full, case["prompt"], len(case["tokens"])) != case["tokens"]
 
 
 def test_window_layer_sees_only_its_window(tmp_path):
