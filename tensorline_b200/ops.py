@@ -103,7 +103,10 @@ def _check(status: int, what: str, launches: int = 1) -> None:
 N_COUNTERS = 8192
 _status: dict = {}
 STATUS_ROLES = {1: "tcgen05 product: the copy thread waited for a free stage", 2: "tcgen05 product: the MMA thread waited for a stage's copies",
-                3: "tcgen05 product: the epilogue waited for the accumulator", 20: "decode attention: a wait for a stage of keys and values"}
+                3: "tcgen05 product: the epilogue waited for the accumulator",
+                31: "two-block product: a copy thread waited for a free stage", 32: "two-block product: the MMA thread waited for a free accumulator",
+                33: "two-block product: the MMA thread waited for a stage's copies", 34: "two-block product: the epilogue waited for the accumulator",
+                20: "decode attention: a wait for a stage of keys and values"}
 
 
 def device_status(device) -> torch.Tensor:
@@ -115,7 +118,8 @@ def device_status(device) -> torch.Tensor:
         device = torch.device("cuda", torch.cuda.current_device())
     t = _status.get(device)
     if t is None:
-        t = torch.zeros(1 + N_COUNTERS + 4, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):                # an ordinary tensor: it is cleared in place from anywhere
+            t = torch.zeros(1 + N_COUNTERS + 4, dtype=torch.int32, device=device)
         _status[device] = t
     return t
 

@@ -110,6 +110,48 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     return partial if pieces else out
 
 
+_lib2 = None
+
+
+def lib2():
+    """The two-block (cta_group::2) persistent product for steps of many tokens (`csrc/gemm_tc2.cu`)."""
+    global _lib2
+    if _lib2 is None:
+        l = load_library("tl_gemm_tc2", ["gemm_tc2.cu"])
+        l.tl_gemm_tc2.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]
+        l.tl_gemm_tc2.restype = ctypes.c_int
+        _lib2 = l
+    return _lib2
+
+
+def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, gated: bool = False,
+             out: torch.Tensor | None = None, max_pairs: int = 0) -> torch.Tensor:
+    """x [T, K] times w [N, K]^T on pairs of thread blocks (256 x 256 tiles, persistent, double-buffered
+    accumulators).  `gated`: w holds gate and up rows interleaved in blocks of 64 (N % 128 == 0); the result is
+    silu(gate) * up, [T, N / 2] bfloat16, formed in the epilogue."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc2: bfloat16 operands only")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not x.is_contiguous() or not w.is_contiguous():
+        raise KernelError("gemm_tc2: x [T, K] and w [N, K] must be contiguous with equal K")
+    if K % 8:
+        raise KernelError(f"gemm_tc2: K = {K} must be a multiple of 8 (TMA needs 16-byte rows)")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tc2: output is bfloat16 or float32")
+    if gated and (N % 128 or out_dtype != torch.bfloat16):
+        raise KernelError("gemm_tc2: the gated epilogue needs N % 128 == 0 and bfloat16 output")
+    cols = N // 2 if gated else N
+    if out is None:
+        out = torch.empty((T, cols), dtype=out_dtype, device=x.device)
+    elif out.shape != (T, cols) or out.dtype != out_dtype or out.stride(1) != 1:
+        raise KernelError("gemm_tc2: out must be [T, N] (gated: [T, N / 2]) of the output type with unit inner stride")
+    st = status_word(x.device)
+    _check(lib2().tl_gemm_tc2(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K,
+                              int(gated), _ptr(st), int(max_pairs), _stream()), "gemm_tc2" + ("+gated" if gated else ""))
+    return out
+
+
 def can_gate(T: int, N: int, K: int) -> bool:
     """Whether the plan for these sizes allows the gated epilogue."""
     swap, _, splits = plan(T, N, K)

@@ -9,8 +9,12 @@ F32 = dict(rtol=2e-5, atol=2e-5)
 # to bfloat16 (2^-9 relative) after float32 accumulation of bfloat16 products.
 BF16 = dict(rtol=1.6e-2, atol=1.6e-2)
 # Whole model in bfloat16 against the float64 plain model: largest logit error, as a share of the
-# largest |logit| of the sequence.
+# largest |logit| of the sequence.  Measured over whole, decoded and cut replays of four sequences per
+# model: Tiny A 0.0021, Tiny B 0.0156, B without its window 0.0148, Tiny C 0.0093 (B's weights are drawn
+# four times wider than A's, so that attention scores spread over several units).  The bounds are about
+# twice the measurement; 0.03 is the bound for a model that has none of its own.
 BF16_MODEL_REL = 0.03
+BF16_MODEL_REL_OF = {"A": 0.005, "B": 0.03, "B_FULL": 0.03, "C": 0.02}
 
 
 def scatter_pages(k, v, page_size, num_pages, seed=0, dtype=None, device="cuda"):

@@ -64,23 +64,24 @@ _LAST_LOGITS: dict = {}         # (plain model, sequence) -> the plain model's l
 
 
 def follows_where_decided(plain, prompt, tokens) -> int:
-    """bfloat16 rule: the engine's token must be the plain model's wherever the plain model's lead over the
-    runner-up is more than twice the stated logit tolerance; the comparison follows the engine's tokens until the
-    first undecided position.  Returns the number of positions compared."""
+    """The bfloat16 rule, at every generated position: given the tokens before it (the engine's own), the engine's
+    token must be one the plain model could have picked within the stated logit tolerance: its plain logit lies
+    within twice the tolerance of the plain model's largest.  Where the plain model's lead over its runner-up is
+    larger than that (a decided position) this means the very same token.  Returns the number of decided positions."""
     from tests.gpu_helpers import BF16_MODEL_REL
-    seq, compared = list(prompt), 0
+    seq, decided = list(prompt), 0
     for tok in tokens:
         key = (id(plain), tuple(seq))
         if key not in _LAST_LOGITS:
             _LAST_LOGITS[key] = forward(plain, seq)[-1]
         logits = _LAST_LOGITS[key]
+        slack = 2 * BF16_MODEL_REL * float(logits.abs().max())
         top = torch.topk(logits, 2).values
-        if float(top[0] - top[1]) <= 2 * BF16_MODEL_REL * float(logits.abs().max()):
-            break
-        assert tok == int(logits.argmax()), f"position {len(seq)}: engine {tok}, plain {int(logits.argmax())}"
-        compared += 1
+        assert float(logits[tok]) >= float(top[0]) - slack, \
+            f"position {len(seq)}: engine picked {tok} (plain logit {float(logits[tok]):.4f}), plain {int(logits.argmax())} ({float(top[0]):.4f})"
+        decided += float(top[0] - top[1]) > slack
         seq.append(tok)
-    return compared
+    return decided
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -97,8 +98,8 @@ def test_greedy_generation_equals_the_plain_model(tiny, regime, dtype):
     if dtype == "float32":
         assert [o.token_ids for o in outs] == want
     else:
-        compared = sum(follows_where_decided(plain, p, o.token_ids) for p, o in zip(prompts, outs))
-        assert compared >= n_new
+        decided = sum(follows_where_decided(plain, p, o.token_ids) for p, o in zip(prompts, outs))
+        assert decided >= n_new // 2, "too few positions where the plain model is decided: the comparison says little"
     assert all(o.finish_reason == "length" and o.stats.completion_tokens == n_new for o in outs)
     st = eng.stats()
     assert st["free_pages"] == st["num_pages"], "pages leaked"
@@ -176,7 +177,7 @@ def test_shared_prefix_is_served_from_the_cache_and_changes_nothing(tmp_path, na
         assert [o.token_ids for o in first + outs] == [o.token_ids for o in ref]
         assert [o.token_ids for o in ref] == [greedy_generate(plain, p, 12) for p in prompts]
     else:                                                    # a cached prefix was computed in another batch: rounding may differ
-        assert sum(follows_where_decided(plain, p, o.token_ids) for p, o in zip(prompts, first + outs)) >= 12
+        assert sum(follows_where_decided(plain, p, o.token_ids) for p, o in zip(prompts, first + outs)) >= 6
     assert first[0].stats.cached_tokens == 0 and all(o.stats.cached_tokens == 32 for o in outs)
     again = eng.generate([prompts[1]], params(12))[0]        # found whole in the cache: the last page is computed again
     assert 0 < again.stats.cached_tokens < len(prompts[1])
