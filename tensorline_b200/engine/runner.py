@@ -158,45 +158,52 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     def build_context(self, entries) -> StepContext:
-        ps = self.page_size
-        ids, pos, req_slot, q_start, start_pos, slots, want_rows = [], [], [], [0], [], [], []
-        max_q = max_ctx = 0
-        for e in entries:
-            n = len(e.tokens)
-            if n < 1:
-                raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
-            start = self.positions[e.rid]
-            slot = self.cache.slot(e.rid)
+        """The step's description, packed on the host into one int32 array and copied to the device in one transfer:
+        per token its id, position and request slot; per request its first row, first position and slot; the wanted rows."""
+        B = len(entries)
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        if B and int(lens.min()) < 1:
+            bad = entries[int(lens.argmin())]
+            raise ValueError(f"request {bad.rid!r}: an entry needs at least one token")
+        q_start = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(lens, out=q_start[1:])
+        T = int(q_start[-1])
+        start_pos = np.fromiter((self.positions[e.rid] for e in entries), dtype=np.int64, count=B)
+        slots = np.fromiter((self.cache.slot(e.rid) for e in entries), dtype=np.int64, count=B)
+        want_rows = []
+        for i, e in enumerate(entries):
             room = self.cache.capacity(e.rid)
-            if start + n > room:
-                raise RuntimeError(f"request {e.rid!r}: positions up to {start + n} but pages for {room}; "
+            if start_pos[i] + lens[i] > room:
+                raise RuntimeError(f"request {e.rid!r}: positions up to {start_pos[i] + lens[i]} but pages for {room}; "
                                    "grow its cache before the step")
-            row0 = len(ids)
-            ids.extend(int(t) for t in e.tokens)
-            pos.extend(range(start, start + n))
-            req_slot.extend([slot] * n)
-            q_start.append(row0 + n)
-            start_pos.append(start)
-            slots.append(slot)
             for w in e.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {n} tokens")
-                want_rows.append(row0 + w)
-            max_q = max(max_q, n)
-            max_ctx = max(max_ctx, start + n)
-        T, B = len(ids), len(entries)
-        if T and (min(ids) < 0 or max(ids) >= self.vocab_size):
+                if not 0 <= w < lens[i]:
+                    raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {lens[i]} tokens")
+                want_rows.append(int(q_start[i]) + w)
+        R = len(want_rows)
+        packed = np.empty(3 * T + 3 * B + 1 + R, dtype=np.int32)
+        cut = np.cumsum([0, T, T, T, B + 1, B, B, R])
+        for i, e in enumerate(entries):
+            packed[q_start[i]:q_start[i + 1]] = e.tokens
+        ids = packed[:T]
+        if T and (int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size):
             raise ValueError(f"token id outside [0, {self.vocab_size})")
-        packed = np.asarray(ids + pos + req_slot + q_start + start_pos + slots + want_rows, dtype=np.int32)
+        row_of = np.repeat(np.arange(B), lens)
+        packed[cut[1]:cut[2]] = start_pos[row_of] + (np.arange(T) - q_start[row_of])
+        packed[cut[2]:cut[3]] = slots[row_of]
+        packed[cut[3]:cut[4]] = q_start
+        packed[cut[4]:cut[5]] = start_pos
+        packed[cut[5]:cut[6]] = slots
+        packed[cut[6]:cut[7]] = want_rows
         dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
-        cut = np.cumsum([0, T, T, T, B + 1, B, B, len(want_rows)])
         parts = [dev[cut[i]:cut[i + 1]] for i in range(7)]
         self._sync_tables()
+        ends = start_pos + lens
         return StepContext(T=T, B=B, ids=parts[0], pos=parts[1], req_slot=parts[2], q_start=parts[3],
                            start_pos=parts[4], slots=parts[5], want_rows=parts[6], tables=self.tables,
-                           page_size=ps, decode_only=all(len(e.tokens) == 1 for e in entries), max_q_len=max_q,
-                           max_ctx=max_ctx, h_q_start=q_start, h_start_pos=start_pos, h_slots=slots,
-                           force_exact_attention=self.force_exact_attention)
+                           page_size=self.page_size, decode_only=bool(B) and int(lens.max()) == 1, max_q_len=int(lens.max()) if B else 0,
+                           max_ctx=int(ends.max()) if B else 0, h_q_start=q_start.tolist(), h_start_pos=start_pos.tolist(),
+                           h_slots=slots.tolist(), force_exact_attention=self.force_exact_attention)
 
     @torch.inference_mode()
     def step(self, entries) -> torch.Tensor:

@@ -27,6 +27,20 @@ def use_tc(tokens: int, n: int, k: int) -> bool:
     return TC_ENABLED and tokens <= TC_MAX_TOKENS and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0
 
 
+# The two-block (cta_group::2) product with the activation in its epilogue takes the gate|up product of long steps.
+# Measured against the library product followed by the activation kernel at the 7B / 14B / 32B shapes: 0.997 / 0.98 /
+# 1.01 at 512 tokens, 1.02 / 0.99 / 1.00 at 1,024, 1.03 / 1.05 / 1.08 at 1,536, 1.04 / 1.02 / 1.07 at 2,048, 1.08 /
+# 1.05 / 1.11 at 4,096; it works on tiles of 256 tokens, so a step that fills its last tile badly stays with the library.
+PAIR_ENABLED = os.environ.get("TENSORLINE_B200_TC_PAIR_PRODUCT", "1") != "0"
+PAIR_MIN_TOKENS = int(os.environ.get("TENSORLINE_B200_TC_PAIR_MIN_TOKENS", 1280))
+PAIR_MAX_WASTE = 1.10
+
+
+def use_pair_product(tokens: int, n: int, k: int) -> bool:
+    return (TC_ENABLED and PAIR_ENABLED and tokens >= PAIR_MIN_TOKENS and -(-tokens // 256) * 256 <= PAIR_MAX_WASTE * tokens
+            and n * k >= TC_MIN_WEIGHT_ELEMENTS and k % 8 == 0)
+
+
 class SplitSum:
     """A product whose split-K pieces [S, T, N] (float32) have not been added up yet.  A consumer that
     reads its input once anyway (the residual add + norm) sums them on the way and saves the pass that

@@ -2,8 +2,8 @@
 
 tzar-beep/Tensorline calls the installed package's module for this (tensorline/paged.py:276;
 shapes tensorline/manager.py:53-54).  Here gate and up are one product against the stacked
-[2I, H] matrix, the activation in float32 (a kernel of its own, or the epilogue of the tcgen05
-product for steps of few tokens), then the down product.
+[2I, H] matrix, the activation in float32 (the epilogue of the tcgen05 products for steps of few
+tokens and for long steps, a kernel of its own in between), then the down product.
 """
 from __future__ import annotations
 
@@ -11,7 +11,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_feed_forward
-from .linear import matmul, use_tc
+from .linear import matmul, use_pair_product, use_tc
 
 GATE_BLOCK = 64
 
@@ -52,6 +52,10 @@ class GatedMLP(Part):
             if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
                 m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=True)
                 return matmul(m, self.w_down, may_defer=True)
+        if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
+            from .. import ops_gemm
+            m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=True)          # long steps: pairs of blocks, activation in the epilogue
+            return matmul(m, self.w_down, may_defer=True)
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)
         ops.silu_mul(gu, m, block=self.block)

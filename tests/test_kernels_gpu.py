@@ -550,3 +550,53 @@ def test_tcgen05_matrix_product_refuses_unaligned_k():
     w = torch.zeros(128, 36, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(ops.KernelError, match="multiple of 8"):
         ops_gemm.gemm_tc(x, w)
+
+
+TC2_CASES = [  # tokens, N, K: ragged edges in every dimension, one tile, many tiles a pair, fewer tiles than pairs
+    (256, 256, 64), (300, 384, 200), (65, 136, 72), (513, 640, 1032), (1000, 5000, 520), (2048, 4608, 3584), (96, 20000, 264),
+]
+
+
+@pytest.mark.parametrize("case", TC2_CASES, ids=[f"T{c[0]}N{c[1]}K{c[2]}" for c in TC2_CASES])
+def test_two_block_tcgen05_matrix_product(case):
+    """The cta_group::2 kernel (pairs of blocks on 256 x 256 tiles, persistent, double-buffered accumulators)
+    against float64: float32 and bfloat16 outputs, and with so few pairs that every pair runs many tiles through
+    both accumulator buffers."""
+    from tensorline_b200 import ops_gemm
+    T, N, K = case
+    x = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    w = rnd(N, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()
+    want = x.double() @ w.double().T
+    y32 = ops_gemm.gemm_tc2(x, w, torch.float32)
+    y16 = ops_gemm.gemm_tc2(x, w, torch.bfloat16)
+    few = ops_gemm.gemm_tc2(x, w, torch.float32, max_pairs=3)
+    ops_gemm.check_status()
+    assert torch.equal(few, y32)                              # a tile's result does not depend on which pair ran it, or when
+    assert_close(y32, want, "float32 out", rtol=1e-4, atol=1e-4 * float(want.abs().max()))
+    assert_close(y16, want, "bfloat16 out", rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    strided = torch.zeros(T, N + 24, dtype=torch.bfloat16, device="cuda")
+    ops_gemm.gemm_tc2(x, w, out=strided[:, 8:8 + N])          # rows further apart than they are wide, unaligned start
+    assert torch.equal(strided[:, 8:8 + N], y16) and not bool(strided[:, :8].any()) and not bool(strided[:, 8 + N:].any())
+
+
+@pytest.mark.parametrize("T,I,K", [(256, 128, 128), (700, 576, 328), (2048, 1216, 904), (70, 64, 64)])
+def test_two_block_product_with_the_activation_in_its_epilogue(T, I, K):
+    """silu(gate) * up formed in the epilogue from weights whose gate and up rows alternate in blocks of 64 gives
+    bit for bit what the product followed by the activation kernel gives (both round gate and up to bfloat16
+    first), and agrees with float64."""
+    from tensorline_b200 import ops, ops_gemm
+    x = rnd(T, K, seed=3, dtype=torch.bfloat16).cuda()
+    g = rnd(I, K, seed=4, scale=0.2, dtype=torch.bfloat16)
+    u = rnd(I, K, seed=5, scale=0.2, dtype=torch.bfloat16)
+    w = torch.stack((g.view(I // 64, 64, K), u.view(I // 64, 64, K)), dim=1).reshape(2 * I, K).contiguous().cuda()
+    got = ops_gemm.gemm_tc2(x, w, gated=True)
+    ops_gemm.check_status()
+    gu = ops_gemm.gemm_tc2(x, w)
+    two_pass = torch.empty(T, I, dtype=torch.bfloat16, device="cuda")
+    ops.silu_mul(gu, two_pass, block=64)
+    assert torch.equal(got, two_pass)
+    gd, ud = x.double().cpu() @ g.double().T, x.double().cpu() @ u.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    assert_close(got, want, "gated two-block product", rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+    with pytest.raises(ops.KernelError, match="gated"):
+        ops_gemm.gemm_tc2(x, w[:64], gated=True)               # 64 rows: a gate block without its up block
