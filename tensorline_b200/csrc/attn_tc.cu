@@ -802,11 +802,329 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Key tiles of 128 with P kept in tensor memory (head sizes 64 and 128, pages of 8 to 64 tokens).
+//
+// The kernel above is bound by shared memory: every key-tile step the softmax writes P there and P V reads it
+// back, and tiles of 64 keys read Q twice as often as tiles of 128 would.  Here a tile's S (128 rows x 128 keys,
+// float) is one slot of tensor memory, and the softmax writes P back INTO that slot as packed bfloat16 (64 of
+// its 128 columns); O += P V then takes P as its tensor-memory operand.  P never touches shared memory, which
+// holds only Q (2 tiles), K and V (2 stages of 128 keys each).  Tensor memory: S/P of the two query tiles at
+// columns 0 and 128, their O behind them: all 512 columns.  With one S slot a tile, S(i + 1) of a tile can only
+// be issued once P(i) V has read P(i): a tile's products and softmax alternate, and the block's two query tiles
+// keep the tensor core busy in turns.  A row's 128 scores are read from tensor memory twice (once for the
+// maximum, once for the exponentials) in parts of 32, so a softmax thread needs no more registers than before.
+constexpr int BN3 = 128;
+constexpr int KV3_BYTES = BN3 * D * 2;
+constexpr int SMEM3_TILES = QT * Q_BYTES + 2 * KV3_BYTES + 2 * KV3_BYTES;
+constexpr int SMEM3_BYTES = SMEM3_TILES + 1024 + 256;
+constexpr uint32_t TMEM3_COLS = 512;
+constexpr uint32_t S3_COL = 0, O3_COL = QT * BN3;
+static_assert(O3_COL + QT * D <= 512, "S and O of both tiles must fit the tensor memory");
+static_assert(SMEM3_BYTES <= 227 * 1024, "shared memory");
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P: one row a lane, two bfloat16 a column) comes from tensor memory.
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t (&u)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                   "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+                   "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
+                   "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS2, 1)
+attn_tc3_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs A) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sQ = smem_addr(base), sK = sQ + QT * Q_BYTES, sV = sK + 2 * KV3_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + SMEM3_TILES);
+    uint64_t* bar_s = bars;          // [tile] S is complete (commit)
+    uint64_t* bar_p = bars + 2;      // [tile] the tile's 128 rows have written P over S
+    uint64_t* bar_o = bars + 4;      // [tile] O += P V is complete (commit): the S/P slot is free, O is at rest
+    uint64_t* bar_k = bars + 6;      // [slot] K has landed (TMA bytes)
+    uint64_t* bar_v = bars + 8;      // [slot] V has landed
+    uint64_t* bar_kfree = bars + 10; // [slot] both S issuers are done with this K slot
+    uint64_t* bar_vfree = bars + 12; // [slot] both P V issuers are done with this V slot
+    uint64_t* bar_q = bars + 14;     // both Q tiles are in shared memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
+
+    int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
+    if (A.order != nullptr) {
+        const int packed = A.order[blockIdx.x / A.nkv];
+        b = packed >> 16; tile = packed & 0xFFFF;
+    } else {
+        for (; b < A.B; ++b) {
+            const int nt = ((A.q_start[b + 1] - A.q_start[b]) * g + QT * BM - 1) / (QT * BM);
+            if (tile < nt) break;
+            tile -= nt;
+        }
+    }
+    if (b >= A.B) return;
+    const int qs = A.q_start[b], qlen = A.q_start[b + 1] - qs, sp = A.start_pos[b];
+    const int rows_total = qlen * g;
+    const int* tab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_TC2_PREFILL) * A.max_pages;
+    int row0[QT], kt_first[QT], kt_last[QT];
+#pragma unroll
+    for (int t = 0; t < QT; ++t) {
+        row0[t] = (tile * QT + t) * BM;
+        if (row0[t] < rows_total) {
+            const int row_end = min(row0[t] + BM, rows_total);
+            const int pos_first = sp + row0[t] / g, pos_last = sp + (row_end - 1) / g;
+            const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
+            kt_first[t] = key_lo / BN3; kt_last[t] = pos_last / BN3;
+        } else {                                           // no rows: reads nothing
+            kt_first[t] = 1; kt_last[t] = 0;
+        }
+    }
+    const int kt_lo = kt_first[0], kt_hi = max(kt_last[0], kt_last[1]), n_kt = kt_hi - kt_lo + 1;
+    auto reads = [&](int t, int j) { return kt_lo + j >= kt_first[t] && kt_lo + j <= kt_last[t]; };
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_s + i, 1); mbar_init(bar_p + i, 128); mbar_init(bar_o + i, 1);
+            mbar_init(bar_k + i, 1); mbar_init(bar_v + i, 1); mbar_init(bar_kfree + i, 2); mbar_init(bar_vfree + i, 2);
+        }
+        mbar_init(bar_q, QT * BM);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(TMEM3_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------ softmax and epilogue: thread = row of tile t
+        const int t = warp >> 2, r = tid & 127;
+        const int R = row0[t] + r;
+        const int pos_r = R < rows_total ? sp + R / g : -1; // -1: no key is visible
+        const int lo_r = A.window > 0 ? max(0, pos_r - A.window + 1) : 0;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_addr + S3_COL + t * BN3, o_addr = lane_addr + O3_COL + t * D;
+        const int n_mine = kt_last[t] - kt_first[t] + 1;   // <= 0: this tile has no rows
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        load_q_rows(sQ + t * Q_BYTES, A.q, A.q_stride, qs, kh * g, g, row0[t], rows_total, r);
+        cp_async_wait_all();
+        fence_async_proxy();
+        mbar_arrive(bar_q);
+
+        for (int i = 0; i < n_mine && ok; ++i) {
+            const int key0 = (kt_first[t] + i) * BN3;
+            ok = mbar_wait(bar_s + t, i & 1, abort_flag, A.status, 1);                   // S(i) is ready; P(i-1) V is complete
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool all_visible = key0 + BN3 - 1 <= pos_r && key0 >= lo_r;
+            // first reading: the row's largest score
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c0 = 0; c0 < BN3; c0 += 64) {
+                float s[64];
+                tmem_ld32(s_addr + c0, reinterpret_cast<float(&)[32]>(s[0]));
+                tmem_ld32(s_addr + c0 + 32, reinterpret_cast<float(&)[32]>(s[32]));
+                tmem_ld_wait();
+                if (!all_visible) {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int j = key0 + c0 + c;
+                        if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
+                    }
+                }
+                mx = fmaxf(mx, row_max(s));
+            }
+            mx *= A.scale_log2;
+            const bool raise = mx > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mx != -INFINITY);
+            const float m_new = raise ? fmaxf(mx, m_ref) : m_ref;
+            const bool fix_o = raise && i > 0 && m_ref != -INFINITY;        // O holds earlier tiles of this row, at rest
+            if (__any_sync(0xffffffffu, fix_o)) {
+                const float alpha = fix_o ? fast_exp2(m_ref - m_new) : 1.0f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(o_addr + c0, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] *= alpha;
+                    tmem_st32(o_addr + c0, o);
+                }
+            }
+            m_ref = m_new;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // second reading: exponentials, packed two a column over the first half of the slot.  Keys 0..63 go to
+            // columns 0..31 after columns 0..63 were read; keys 64..127 to columns 32..63, which were read before.
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c0 = 0; c0 < BN3; c0 += 64) {
+                float s[64];
+                tmem_ld32(s_addr + c0, reinterpret_cast<float(&)[32]>(s[0]));
+                tmem_ld32(s_addr + c0 + 32, reinterpret_cast<float(&)[32]>(s[32]));
+                tmem_ld_wait();
+                uint32_t packed[32];
+#pragma unroll
+                for (int c = 0; c < 64; c += 2) {
+                    float p0 = fast_exp2(fmaf(s[c], A.scale_log2, -m_use)), p1 = fast_exp2(fmaf(s[c + 1], A.scale_log2, -m_use));
+                    if (!all_visible) {
+                        const int j = key0 + c0 + c;
+                        if (!(j <= pos_r && j >= lo_r)) p0 = 0.f;
+                        if (!(j + 1 <= pos_r && j + 1 >= lo_r)) p1 = 0.f;
+                    }
+                    l4[(c >> 1) & 3] += p0 + p1;
+                    packed[c >> 1] = pack_bf16(p0, p1);
+                }
+                tmem_st32_nowait(s_addr + (c0 >> 1), packed);
+            }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar_p + t);
+        }
+        // ------------------------------------------------------------ epilogue: the tile's last P V has finished
+        if (ok && n_mine > 0 && mbar_wait(bar_o + t, (n_mine - 1) & 1, abort_flag, A.status, 4)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = nullptr;
+            if (R < rows_total) dst = A.out + ((size_t)(qs + R / g) * A.nq + (kh * g + R % g)) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float o[32];
+                tmem_ld32(o_addr + c0, o);
+                tmem_ld_wait();
+                if (dst) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(o[c] * inv, o[c + 1] * inv); v.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
+                        v.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv); v.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = v;
+                    }
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------------------------------------ MMA issuers: one thread each in warps 8..11
+        // (S of tile 0, S of tile 1, P V of tile 0, P V of tile 1).  Every issuer walks all key tiles, also those
+        // its query tile does not read, and hands each K (V) slot back with one of the two arrivals its barrier counts.
+        if (lane == 0) {
+            const int t = warp & 1;
+            bool ok = true;
+            if (warp < 10) {
+                constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN3 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                ok = mbar_wait(bar_q, 0, abort_flag, A.status, 11, true);
+                int i = 0;                                  // products issued for this tile
+                for (int j = 0; j < n_kt && ok; ++j) {
+                    const int sl = j & 1;
+                    ok = mbar_wait(bar_k + sl, (j >> 1) & 1, abort_flag, A.status, 5, true);        // K(j) is in
+                    if (!ok) break;
+                    if (!reads(t, j)) { mbar_arrive(bar_kfree + sl); continue; }
+                    if (i >= 1) {                           // the slot is free once P(i-1) V has read P(i-1)
+                        ok = mbar_wait(bar_o + t, (i - 1) & 1, abort_flag, A.status, 6, true);
+                        if (!ok) break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t k_addr = sK + sl * KV3_BYTES;
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k)
+                        umma(tmem + S3_COL + t * BN3, desc_kmajor(sQ + t * Q_BYTES + (k >> 2) * BM * 128 + (k & 3) * 32),
+                             desc_kmajor(k_addr + (k >> 2) * BN3 * 128 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+                    umma_commit(bar_s + t);
+                    umma_commit(bar_kfree + sl);
+                    ++i;
+                }
+            } else {
+                constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                int i = 0;
+                for (int j = 0; j < n_kt && ok; ++j) {
+                    const int sl = j & 1;
+                    ok = mbar_wait(bar_v + sl, (j >> 1) & 1, abort_flag, A.status, 7, true);        // V(j) is in
+                    if (!ok) break;
+                    if (!reads(t, j)) { mbar_arrive(bar_vfree + sl); continue; }
+                    ok = mbar_wait(bar_p + t, i & 1, abort_flag, A.status, 8, true);                // P is written
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t v_addr = sV + sl * KV3_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BN3 / 16; ++k)      // O_t += P V(j): 16 keys = 8 columns of P a product
+                        umma_a_tmem(tmem + O3_COL + t * D, tmem + S3_COL + t * BN3 + k * 8,
+                                    desc_mnmajor(v_addr + k * 16 * 128, BN3 * 128), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_o + t);
+                    umma_commit(bar_vfree + sl);
+                    ++i;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ copies: one thread of warp 12 issues the TMA
+        // boxes of K, one of warp 13 those of V, up to two tiles ahead
+        if (lane == 0) {
+            const bool is_k = warp == 12;
+            const CUtensorMap* map = is_k ? &map_k : &map_v;
+            asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+            uint64_t* bar_free = is_k ? bar_kfree : bar_vfree;
+            uint64_t* bar_full = is_k ? bar_k : bar_v;
+            const uint32_t tiles = is_k ? sK : sV;
+            int ps_shift = 0;
+            while ((1 << ps_shift) < A.page_size) ++ps_shift;
+            const int ppt = BN3 >> ps_shift;                // pages per key tile: 2 to 16
+            bool ok = true;
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int sl = j & 1;
+                int page[16];
+#pragma unroll
+                for (int pg = 0; pg < 16; ++pg)             // the tile's page numbers, all requested before the wait
+                    if (pg < ppt) page[pg] = tl_checked(tab[min((((kt_lo + j) * BN3) >> ps_shift) + pg, A.max_pages - 1)],
+                                                        A.lim.total_pages, A.lim, TL_K_TC2_PREFILL);
+                if (j >= 2) {
+                    ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
+                    if (!ok) break;
+                }
+                mbar_expect_tx(bar_full + sl, KV3_BYTES);
+#pragma unroll
+                for (int pg = 0; pg < 16; ++pg) {
+                    if (pg >= ppt) break;
+                    const int row = (page[pg] * A.nkv + kh) << ps_shift;
+#pragma unroll
+                    for (int db = 0; db < D / 64; ++db)
+                        tma_box(tiles + sl * KV3_BYTES + db * (BN3 * 128) + ((pg << ps_shift) * 128), map, bar_full + sl, db * 64, row);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM3_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 bool g_attr2_done[TL_MAX_DEVICES] = {};
+bool g_attr3_done[TL_MAX_DEVICES] = {};
 
 // The cache tensor [pages, nkv, page, D] as rows of D elements; a box is one page of one KV head, 64 wide.
 int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_size) {
@@ -897,6 +1215,53 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     A.lim = TlLimits{table_rows, (int)total_pages, fault};
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
     attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    return tl_launch_status();
+#else
+    return 2;
+#endif
+}
+
+// Two query tiles (256 rows) per block, key tiles of 128, P kept in tensor memory; K, V loaded by TMA.  total_tiles = sum over
+// requests of ceil(q_len * g / 256); `total_pages`: first dimension of the cache tensors.  Returns 2 if this build
+// or these sizes do not take this kernel (head size above 128, pages of fewer than 8 tokens, unaligned pages).
+TL_EXPORT int tl_attn_tc3_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                  long long total_pages, const int* table, int max_pages, int page_size,
+                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                  int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                                  int* fault, cudaStream_t stream) {
+#if HEAD_DIM <= 128
+    if (total_tiles <= 0 || B <= 0) return 0;
+    if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
+    if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
+    if (nq % nkv || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+            qres != cudaDriverEntryPointSuccess) return 100;
+        g_encode = (EncodeTiledFn)fn;
+    }
+    const int dev = tl_device_index();
+    if (dev < 0) return 1;
+    if (!g_attr3_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc3_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM3_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        g_attr3_done[dev] = true;
+    }
+    CUtensorMap mk, mv;
+    const long long rows = total_pages * nkv * page_size;
+    int e;
+    if ((e = make_pages_map(&mk, k_pages, rows, page_size))) return e;
+    if ((e = make_pages_map(&mv, v_pages, rows, page_size))) return e;
+    TcAttnArgs A{};
+    A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
+    A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
+    A.table = table; A.max_pages = max_pages; A.page_size = page_size;
+    A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
+    A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
+    A.lim = TlLimits{table_rows, (int)total_pages, fault};
+    dim3 grid((unsigned)total_tiles * (unsigned)nkv);
+    attn_tc3_prefill_kernel<<<grid, THREADS2, SMEM3_BYTES, stream>>>(mk, mv, A);
     return tl_launch_status();
 #else
     return 2;
