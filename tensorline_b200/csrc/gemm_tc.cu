@@ -123,21 +123,114 @@ struct GemmArgs {
                           // up features of the same 64 columns; out[b, 64 tile + j] = silu(gate) * up, [RB, RA / 2]
     long long wait_cycles;   // how long a wait on a barrier may take before the block gives up
     int drop_last_load;      // tests only: the copy thread leaves out its last stage, so the MMA thread's wait runs out
+    // The residual add folded into the product that makes the addend (swap, cluster_reduce): the block that finishes a
+    // share of the tile adds the bfloat16-rounded sums into the float residual stream res_x [RB, res_ld] in place and
+    // leaves the sum of squares of the new values of every (token, 128-row tile) in ssq_out [RB, tiles of RA].
+    float* res_x; int res_ld; float* ssq_out;
+    // The norm folded into the product that reads its result (swap): the B operand is not loaded by TMA but made by the
+    // epilogue warps from the float residual stream nx [rows, K]: h = cast(cast(x * rstd) * w), rstd of a row from the
+    // nparts partial sums of squares nssq [rows, nparts] (summed in a fixed order), K and eps.
+    const float* nx; const float* nssq; int nparts; const void* nw; int nw_f32; float neps;
 };
+
+// The B operand (activations, BN tokens x 64 k a stage) made from the residual stream instead of loaded.  The copy thread
+// brings the raw material of a stage to shared memory by TMA beside the weight tile (a [BN, 64] box of the float stream and
+// the 64 norm weights of the k range, onto a barrier of their own); the four epilogue warps, idle while the products run,
+// normalise it with the row's rstd (cast to bfloat16 before the weight multiply and after it, as the norm kernel does) and
+// write the tile in the layout TMA would have left for a bfloat16 matrix (rows of 128 bytes, 16-byte chunks swizzled by
+// the row within its group of 8), then hand the stage to the MMA thread.  Only shared memory is read here: loading the
+// stream with ordinary loads made every block wait on the same few cache lines (1,000 to 2,800 cycles a tile, measured).
+constexpr int RAW_W_BYTES = 256;                                         // 64 norm weights of a stage, float at most
+template <int BN> __host__ __device__ constexpr int raw_stage_bytes() { return BN * BK * 4 + RAW_W_BYTES; }
+
+template <int BN, int STAGES>
+__device__ __forceinline__ void make_b_tiles(const GemmArgs& G, unsigned char* tiles, unsigned char* raw, uint64_t* full_bar,
+                                             uint64_t* raw_bar, float* rstd_s, volatile int* abort_flag, int b0, int kt_begin, int n_kt) {
+    constexpr int A_BYTES = BM * BK * 2, STAGE_BYTES = A_BYTES + BN * BK * 2, RAW_BYTES = raw_stage_bytes<BN>();
+    constexpr int CHUNKS = BN * 8 / 128 > 0 ? BN * 8 / 128 : 1;          // 16-byte chunks of the tile a thread writes
+    const int e = (int)threadIdx.x - 64;                                 // 0..127
+    // rstd of every token: eight lanes a token, each sums the partial sums p = lane, lane + 8, ... (loads independent of one
+    // another), then the eight are added in a fixed order
+    for (int t0 = 0; t0 < BN; t0 += 16) {
+        const int tl = t0 + (e >> 3), b = b0 + tl, l8 = e & 7;
+        float ss = 0.f;
+        const bool live = tl < BN && b < G.RB;
+        if (live) {
+            const float* src = G.nssq + (size_t)b * G.nparts;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            int p = l8;
+            for (; p + 24 < G.nparts; p += 32) { s0 += src[p]; s1 += src[p + 8]; s2 += src[p + 16]; s3 += src[p + 24]; }
+            for (; p < G.nparts; p += 8) s0 += src[p];
+            ss = (s0 + s1) + (s2 + s3);
+        }
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (l8 == 0 && tl < BN) rstd_s[tl] = live ? 1.0f / sqrtf(ss / (float)G.K + G.neps) : 0.f;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    for (int i = 0; i < n_kt; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(raw_bar + s, (i / STAGES) & 1, abort_flag, G.status, 4, G.wait_cycles)) return;   // the stage's raw material is in
+        const unsigned char* rx = raw + s * RAW_BYTES;
+        const unsigned char* rw = rx + BN * BK * 4;
+        unsigned char* bt = tiles + s * STAGE_BYTES + A_BYTES;
+        const int k0 = (kt_begin + i) * BK;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int item = e + 128 * c, b = item >> 3, ch = item & 7;
+            if (b >= BN) continue;
+            uint32_t packed[4] = {0u, 0u, 0u, 0u};
+            if (k0 + ch * 8 < G.K) {                                     // K % 8 == 0: a chunk is whole or absent (absent: zeros)
+                const float rs = rstd_s[b];
+                const float4 x0 = *reinterpret_cast<const float4*>(rx + b * (BK * 4) + ch * 32);
+                const float4 x1 = *reinterpret_cast<const float4*>(rx + b * (BK * 4) + ch * 32 + 16);
+                const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                float ws[8];
+                if (G.nw_f32) {
+                    const float4 w0 = *reinterpret_cast<const float4*>(rw + ch * 32), w1 = *reinterpret_cast<const float4*>(rw + ch * 32 + 16);
+                    ws[0] = w0.x; ws[1] = w0.y; ws[2] = w0.z; ws[3] = w0.w; ws[4] = w1.x; ws[5] = w1.y; ws[6] = w1.z; ws[7] = w1.w;
+                } else {
+                    const uint4 wq = *reinterpret_cast<const uint4*>(rw + ch * 16);
+                    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wq);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { ws[2 * j] = __low2float(w2[j]); ws[2 * j + 1] = __high2float(w2[j]); }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float n0 = __bfloat162float(__float2bfloat16_rn(xs[2 * j] * rs)), n1 = __bfloat162float(__float2bfloat16_rn(xs[2 * j + 1] * rs));
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(n0 * ws[2 * j], n1 * ws[2 * j + 1]);
+                    packed[j] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+            }
+            const uint32_t dst = smem_addr(bt + (b >> 3) * 1024 + (b & 7) * 128 + ((ch ^ (b & 7)) << 4));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3]) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes before the MMA reads them
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (e == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(full_bar + s)) : "memory");
+    }
+}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs G) {
+    // (with a made B operand, map_b describes the float residual stream: boxes of [BN rows, 64 floats], no swizzle)
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    constexpr int RAW_BYTES = BN <= 64 ? raw_stage_bytes<BN>() : 0;
+    const bool made_b = BN <= 64 && G.nx != nullptr;     // the raw material of the B tiles has a ring of its own behind the stages
+    unsigned char* raw = tiles + STAGES * STAGE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(raw + (made_b ? STAGES * RAW_BYTES : 0));
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* done_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    uint64_t* raw_bar = done_bar + 1;                    // [STAGES] the stage's raw material has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_bar + STAGES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = abort_flag + 1;
+    float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(last_flag) + 1);      // [BN] with a made B operand
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * BM, b0 = blockIdx.y * BN, split = blockIdx.z;
@@ -148,7 +241,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, 1); mbar_init(empty_bar + s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, made_b ? 2 : 1); mbar_init(empty_bar + s, 1); mbar_init(raw_bar + s, 1); }
         mbar_init(done_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -161,14 +254,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // With the residual add folded in, a thread's first four values of the stream are fetched as soon as the kernel in front
+    // has finished, long before the accumulators are summed: the add then costs no round trip of its own.
+    float4 x_first = make_float4(0.f, 0.f, 0.f, 0.f);
+    int x_first_idx = -1;
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         // The weights are nobody's output: the first ring of weight tiles is requested before the wait for the
         // kernel that writes the activations, so the stream from memory is already running when that kernel ends.
         const int ahead = (n_kt < STAGES ? n_kt : STAGES) - ((G.drop_last_load && n_kt <= STAGES) ? 1 : 0);
+        const uint32_t tx_bytes = made_b ? A_BYTES : STAGE_BYTES;      // made: the epilogue warps write the B tiles
+        const int w_elem = G.nw_f32 ? 4 : 2;
+        auto load_raw = [&](int s, int kt) {             // the float stream's [BN, 64] box and the k range's norm weights
+            const int k0 = kt * BK, wn = min(BK, G.K - k0) * w_elem;
+            unsigned char* rx = raw + s * RAW_BYTES;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(raw_bar + s)), "r"((uint32_t)(BN * BK * 4 + wn)) : "memory");
+            tma_load_2d(rx, &map_b, raw_bar + s, k0, b0);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(rx + BN * BK * 4)), "l"((const unsigned char*)G.nw + (size_t)k0 * w_elem), "r"((uint32_t)wn),
+                           "r"(smem_addr(raw_bar + s)) : "memory");
+        };
         for (int i = 0; i < ahead; ++i) {
-            mbar_expect_tx(full_bar + i, STAGE_BYTES);
+            mbar_expect_tx(full_bar + i, tx_bytes);
             unsigned char* st = tiles + i * STAGE_BYTES;
             if (G.swap) tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
             else        tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
@@ -177,16 +285,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         grid_dependency_trigger();
         for (int i = 0; i < ahead; ++i) {
             unsigned char* st = tiles + i * STAGE_BYTES;
-            if (G.swap) tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
-            else        tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
+            if (made_b)      load_raw(i, kt_begin + i);
+            else if (G.swap) tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
+            else             tma_load_2d(st, &map_a, full_bar + i, (kt_begin + i) * BK, a0);
         }
         for (int i = ahead; i < n_kt - G.drop_last_load; ++i) {
             const int s = i % STAGES;
             if (!mbar_wait(empty_bar + s, ((i / STAGES) - 1) & 1, abort_flag, G.status, 1, G.wait_cycles)) break;
-            mbar_expect_tx(full_bar + s, STAGE_BYTES);
+            mbar_expect_tx(full_bar + s, tx_bytes);
             unsigned char* st = tiles + s * STAGE_BYTES;
             tma_load_2d(st, &map_a, full_bar + s, (kt_begin + i) * BK, a0);
-            tma_load_2d(st + A_BYTES, &map_b, full_bar + s, (kt_begin + i) * BK, b0);
+            if (made_b) load_raw(s, kt_begin + i);
+            else        tma_load_2d(st + A_BYTES, &map_b, full_bar + s, (kt_begin + i) * BK, b0);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
@@ -209,6 +319,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp >= 2) {
         // ---------------------------------------------------------------- epilogue: 4 warps, 32 lanes of TMEM each
         grid_dependency_wait();                          // the output may still be read by the kernel before
+        if (G.res_x != nullptr && G.cluster_reduce) {
+            const int nz = (int)gridDim.z, ntok = min(BN, G.RB - b0);
+            const int share = ((ntok + nz - 1) / nz) * BM, lo = split * share, hi = min(ntok * BM, lo + share);
+            const int idx = lo + 4 * ((int)threadIdx.x - 64);
+            if (idx < hi) {
+                const int tok = idx / BM, a = a0 + (idx - tok * BM);
+                if (a + 3 < G.RA) { x_first = *reinterpret_cast<const float4*>(G.res_x + (size_t)(b0 + tok) * G.res_ld + a); x_first_idx = idx; }
+            }
+        }
+        if constexpr (BN <= 64) {                        // the few-token order only
+            if (made_b) make_b_tiles<BN, STAGES>(G, tiles, raw, full_bar, raw_bar, rstd_s, abort_flag, b0, kt_begin, n_kt);
+        }
         if (mbar_wait(done_bar, 0, abort_flag, G.status, 3, G.wait_cycles)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quarter = warp & 3;                // the TMEM lanes a warp may read: 32 * (warp % 4)
@@ -332,7 +454,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (warp >= 2 && !*abort_flag) {
             const float* red = reinterpret_cast<const float*>(tiles);
             const int nz = (int)gridDim.z, ntok = min(BN, G.RB - b0);
-            const int total = ntok * BM, share = (((total + nz - 1) / nz) + 3) & ~3;
+            // with the residual add folded in, a block's share is whole tokens: a warp then holds all 128 rows of one
+            const int total = ntok * BM, share = G.res_x ? ((ntok + nz - 1) / nz) * BM : (((total + nz - 1) / nz) + 3) & ~3;
             const int lo = split * share, hi = min(total, lo + share);
             // four rows of A a thread and step (shares and BM are multiples of 4): one 16-byte load a peer
             const bool wide = (G.ldo & 3) == 0 && (((uintptr_t)G.out) & 15) == 0;
@@ -343,6 +466,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                 }
                 const int tok = idx / BM, a = a0 + (idx - tok * BM);
+                if (G.res_x) {
+                    // x += the sums rounded to bfloat16 (what the addend would have been stored as); the sum of squares of the
+                    // new values of this token's 128 rows goes to its place, in the fixed order of the warp's butterfly
+                    float sq = 0.f;
+                    if (a + 3 < G.RA) {
+                        float* xp = G.res_x + (size_t)(b0 + tok) * G.res_ld + a;
+                        float4 xv = idx == x_first_idx ? x_first : *reinterpret_cast<float4*>(xp);
+                        xv.x += __bfloat162float(__float2bfloat16_rn(acc.x)); xv.y += __bfloat162float(__float2bfloat16_rn(acc.y));
+                        xv.z += __bfloat162float(__float2bfloat16_rn(acc.z)); xv.w += __bfloat162float(__float2bfloat16_rn(acc.w));
+                        *reinterpret_cast<float4*>(xp) = xv;
+                        sq = fmaf(xv.x, xv.x, fmaf(xv.y, xv.y, fmaf(xv.z, xv.z, xv.w * xv.w)));
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) G.ssq_out[(size_t)(b0 + tok) * gridDim.x + blockIdx.x] = sq;
+                    continue;
+                }
                 const size_t o = (size_t)(b0 + tok) * G.ldo + a;
                 if (wide && a + 3 < G.RA) {
                     if (G.out_f32) {
@@ -410,13 +549,16 @@ int get_encode() {
 }
 
 // A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of [box_rows, 64] and 128-byte swizzle.
+// box_rows < 0: a [rows, K] float matrix with boxes of [-box_rows, 64] and no swizzle (the residual stream as raw material).
 int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    const bool f32 = box_rows < 0;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * (f32 ? 4 : 2)};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)(f32 ? -box_rows : box_rows)};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = g_encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                          dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          f32 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : 101;
 }
@@ -455,12 +597,15 @@ int g_drop_last_load = 0;
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3 grid, cudaStream_t stream) {
-    constexpr int SMEM = STAGES * (BM + BN) * BK * 2 + 1024 + (2 * STAGES + 1) * 8 + 32;
+    constexpr int RAW = BN <= 64 ? STAGES * raw_stage_bytes<BN>() : 0;
+    constexpr int SMEM_PLAIN = STAGES * (BM + BN) * BK * 2 + 1024 + (3 * STAGES + 1) * 8 + 32 + BN * 4;
+    constexpr int SMEM_MAX = SMEM_PLAIN + RAW;
+    const int SMEM = SMEM_PLAIN + (G.nx != nullptr ? RAW : 0);
     static bool attr_set[TL_MAX_DEVICES] = {};
     const int dev = tl_device_index();
     if (dev < 0) return 1;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX);
         if (e != cudaSuccess) return (int)e;
         attr_set[dev] = true;
     }
@@ -489,11 +634,21 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
 // the call) receives a non-zero code if a wait inside the kernel ran out.  `gated` (swap = 1, one split, N % 128 == 0, bfloat16 out):
 // w holds gate and up rows interleaved in blocks of 64 and y [T, N / 2] receives silu(gate) * up.  `cluster_reduce` (swap = 1,
 // 2..8 ranges): the ranges of a tile are a thread-block cluster and sum their tiles through distributed shared memory.
-TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
-                         int bn, int splits, float* partial, int* status, int* counters, int n_counters,
-                         int gated, int cluster_reduce, cudaStream_t stream) {
+namespace {
+// The two fusions with the layer's norms (see GemmArgs).  All null / zero: the plain product.
+struct NormFusion {
+    float* res_x; int res_ld; float* ssq_out;                                      // the residual add, in the epilogue
+    const float* nx; const float* nssq; int nparts; const void* nw; int nw_f32; float neps;   // the norm, in the B operand
+};
+
+int gemm_impl(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
+              int bn, int splits, float* partial, int* status, int* counters, int n_counters,
+              int gated, int cluster_reduce, const NormFusion& F, cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
+    const bool made_b = F.nx != nullptr, adds = F.res_x != nullptr;
+    if (made_b && (!swap || bn > 64 || F.nssq == nullptr || F.nw == nullptr || F.nparts < 1 || ((uintptr_t)F.nx & 15) || ((uintptr_t)F.nw & 15))) return 1;
+    if (adds && (!swap || !cluster_reduce || F.ssq_out == nullptr || (N & 3) || (F.res_ld & 3) || ((uintptr_t)F.res_x & 15))) return 1;
+    if (K <= 0 || (K & 7) || (!made_b && ((uintptr_t)x & 15)) || ((uintptr_t)w & 15)) return 1;      // TMA: 16-byte rows and bases
     if (splits < 1 || (splits > 1 && partial == nullptr && !cluster_reduce)) return 1;
     int e = get_encode();
     if (e) return e;
@@ -502,7 +657,9 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     const int RA = swap ? N : T, RB = swap ? T : N;
     CUtensorMap ma, mb;
     if ((e = cached_map(&ma, a, RA, K, BM))) return e;
-    if ((e = cached_map(&mb, b, RB, K, bn))) return e;
+    if (made_b) {                                                                        // the float stream: boxes of [bn rows, 64 floats]
+        if ((e = cached_map(&mb, F.nx, RB, K, -bn))) return e;
+    } else if ((e = cached_map(&mb, b, RB, K, bn))) return e;
     const int k_tiles = (K + BK - 1) / BK;
     if (splits > k_tiles) splits = k_tiles;
     const int per = (k_tiles + splits - 1) / splits;
@@ -512,7 +669,10 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     GemmArgs G{};
     G.gated = gated;
     G.cluster_reduce = (cluster_reduce && splits >= 2) ? 1 : 0;
-    if (cluster_reduce && (!swap || splits > 8 || y == nullptr)) return 1;
+    if (cluster_reduce && (!swap || splits > 8 || (y == nullptr && !adds))) return 1;
+    if (adds && !G.cluster_reduce) return 1;                                             // the caller's plan must give 2..8 ranges
+    G.res_x = F.res_x; G.res_ld = F.res_ld; G.ssq_out = F.ssq_out;
+    G.nx = F.nx; G.nssq = F.nssq; G.nparts = F.nparts; G.nw = F.nw; G.nw_f32 = F.nw_f32; G.neps = F.neps;
     G.out = y; G.partial = partial; G.ldo = ldo; G.RA = RA; G.RB = RB; G.K = K;
     G.k_tiles_per_split = per; G.swap = swap; G.out_f32 = out_f32; G.status = status;
     G.wait_cycles = g_wait_cycles; G.drop_last_load = g_drop_last_load;
@@ -532,6 +692,30 @@ TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int
     const size_t cap = (size_t)tl_num_sms() * 8;
     const int blocks = (int)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
     return launch_after_wait(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (void*)y, out_f32, splits, T, N, ldo);
+}
+}  // namespace
+
+TL_EXPORT int tl_gemm_tc(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
+                         int bn, int splits, float* partial, int* status, int* counters, int n_counters,
+                         int gated, int cluster_reduce, cudaStream_t stream) {
+    return gemm_impl(x, w, y, out_f32, ldo, T, N, K, swap, bn, splits, partial, status, counters, n_counters, gated, cluster_reduce,
+                     NormFusion{}, stream);
+}
+
+// The product with the layer's norms folded in (few-token order only).
+//   res_x, res_ld, ssq_out: y is not stored; its values, rounded to bfloat16, are added into the float residual stream res_x
+//     [T, res_ld] in place, and ssq_out [T, ceil(N / 128)] receives the sums of squares of the new values per (token, tile of
+//     128 features).  Needs 2..8 K ranges summed inside a cluster (`cluster_reduce`), N % 4 == 0.
+//   nx, nssq, nparts, nw, nw_f32, neps: x is not read; the activations are rms_norm(nx[row]) * nw, made on the fly from the
+//     float residual stream nx [T, K], with the row's sum of squares taken from its nparts partial sums nssq [T, nparts].
+TL_EXPORT int tl_gemm_tc_normed(const void* x, const void* w, void* y, int out_f32, int ldo, int T, int N, int K, int swap,
+                                int bn, int splits, float* partial, int* status, int* counters, int n_counters,
+                                int gated, int cluster_reduce, float* res_x, int res_ld, float* ssq_out,
+                                const float* nx, const float* nssq, int nparts, const void* nw, int nw_f32, float neps,
+                                cudaStream_t stream) {
+    NormFusion F{res_x, res_ld, ssq_out, nx, nssq, nparts, nw, nw_f32, neps};
+    return gemm_impl(x, w, y, out_f32, ldo, T, N, K, swap, bn, splits, partial, status, counters, n_counters, gated, cluster_reduce,
+                     F, stream);
 }
 
 // For tests of the failure path only.  `wait_cycles` > 0: how many clock cycles a wait on a barrier may take from

@@ -121,5 +121,8 @@ class Model:
             pending = self.blocks[e.layer].forward(x, pending, ctx, cache)
         if ctx.want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
-        h = self.final_norm.add_norm(x, pending, rows=ctx.want_rows)
+        if getattr(self.head, "accepts_normed_input", False) and getattr(self.final_norm, "can_defer", False):
+            h = self.final_norm.add_norm(x, pending, rows=ctx.want_rows, defer=True)
+        else:
+            h = self.final_norm.add_norm(x, pending, rows=ctx.want_rows)
         return self.head.forward(h)

@@ -30,6 +30,9 @@ def lib():
         l = load_library("tl_gemm_tc", ["gemm_tc.cu"])
         l.tl_gemm_tc.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _P]
         l.tl_gemm_tc.restype = ctypes.c_int
+        l.tl_gemm_tc_normed.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I,
+                                        _P, _I, _P, _P, _P, _I, _P, _I, ctypes.c_float, _P]
+        l.tl_gemm_tc_normed.restype = ctypes.c_int
         l.tl_splitk_reduce.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
         l.tl_splitk_reduce.restype = ctypes.c_int
         _lib = l
@@ -59,21 +62,51 @@ def plan(T: int, N: int, K: int, sms: int | None = None) -> tuple:
     return 0, 128 if N <= 4096 else 256, 1
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
+def can_add_residual(T: int, N: int, K: int) -> bool:
+    """Whether the plan for these sizes lets the product add its result into the residual stream itself: the few-token
+    order with 2..8 K ranges summed inside a cluster."""
+    swap, _, splits = plan(T, N, K)
+    k_tiles = -(-K // 64)
+    splits = -(-k_tiles // -(-k_tiles // min(splits, k_tiles)))
+    return bool(swap) and CLUSTER_REDUCE and 2 <= splits <= CLUSTER_MAX and N % 4 == 0
+
+
+def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap=None, bn=None,
             splits=None, out: torch.Tensor | None = None, fused_reduce: bool = False, pieces: bool = False,
-            gated: bool = False, cluster: bool | None = None):
+            gated: bool = False, cluster: bool | None = None, residual: torch.Tensor | None = None):
     """x [T, K] times w [N, K]^T.  With 2..8 K ranges (few-token order) the ranges of a tile form a
     thread-block cluster and sum through distributed shared memory (`cluster`; None = wherever it
     applies).  `pieces`: when K is split otherwise, return the float32 pieces [S, T, N] unsummed (for a
     consumer that adds them up itself) instead of the product.
     `gated`: w holds gate and up rows interleaved in blocks of 64 (N % 128 == 0); the result is
     silu(gate) * up, [T, N / 2] bfloat16, formed in the epilogue (few tokens, one split only:
-    check `can_gate` first)."""
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    check `can_gate` first).
+    `x` may be a `parts.linear.NormedInput` (few-token order): the activations are then the RMS norm of rows of the
+    float32 residual stream, made inside the kernel from the stream, the rows' partial sums of squares and the norm weight.
+    `residual` (float32 [T, N], check `can_add_residual` first): the result, rounded to bfloat16, is added into it in
+    place inside the kernel; returned are the partial sums of squares of its new rows, float32 [T, ceil(N / 128)]."""
+    normed = None
+    if not isinstance(x, torch.Tensor):
+        normed, x = x, None
+        T, K = normed.shape
+        if normed.rows is not None:
+            raise KernelError("gemm_tc: a normed input that picks rows has to be materialized first")
+        if normed.x.dtype != torch.float32 or not normed.x.is_contiguous() or normed.x.shape[1] != K or K % 8:
+            raise KernelError("gemm_tc: a normed input needs a contiguous float32 stream of a width that is a multiple of 8")
+        if normed.ssq.dtype != torch.float32 or not normed.ssq.is_contiguous() or normed.ssq.shape[0] != normed.x.shape[0]:
+            raise KernelError("gemm_tc: a normed input needs float32 sums of squares, one row per row of the stream")
+        if normed.weight.numel() != K or normed.weight.dtype not in (torch.float32, torch.bfloat16) or not normed.weight.is_contiguous():
+            raise KernelError("gemm_tc: the norm weight must be float32 or bfloat16 [K]")
+        dev = normed.x.device
+    else:
+        if x.dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: bfloat16 operands only")
+        T, K = x.shape
+        dev = x.device
+    if w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: bfloat16 operands only")
-    T, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or not x.is_contiguous() or not w.is_contiguous():
+    if w.shape[1] != K or (x is not None and not x.is_contiguous()) or not w.is_contiguous():
         raise KernelError("gemm_tc: x [T, K] and w [N, K] must be contiguous with equal K")
     if K % 8:
         raise KernelError(f"gemm_tc: K = {K} must be a multiple of 8 (TMA needs 16-byte rows)")
@@ -87,26 +120,49 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     splits = -(-k_tiles // -(-k_tiles // min(splits, k_tiles)))          # as the kernel rounds it: no empty split
     use_cluster = (CLUSTER_REDUCE if cluster is None else cluster) and swap and 2 <= splits <= CLUSTER_MAX and not fused_reduce
     pieces = pieces and splits > 1 and not fused_reduce and not use_cluster
+    if normed is not None and (not swap or bn > 64):
+        raise KernelError("gemm_tc: a normed input needs the few-token order")
+    ssq = None
+    if residual is not None:
+        if not use_cluster or gated or N % 4:
+            raise KernelError("gemm_tc: the residual add needs 2..8 K ranges summed inside a cluster (see can_add_residual)")
+        if residual.dtype != torch.float32 or residual.shape != (T, N) or residual.stride(1) != 1 or residual.stride(0) % 4:
+            raise KernelError("gemm_tc: residual must be float32 [T, N] with unit inner stride")
+        ssq = torch.empty((T, -(-N // 128)), dtype=torch.float32, device=dev)
     if gated:
         if not swap or splits != 1 or N % 128 or out_dtype != torch.bfloat16:
             raise KernelError("gemm_tc: the gated epilogue needs the few-token order, one split, N % 128 == 0, bfloat16")
         if out is None:
-            out = torch.empty((T, N // 2), dtype=out_dtype, device=x.device)
+            out = torch.empty((T, N // 2), dtype=out_dtype, device=dev)
         elif out.shape != (T, N // 2) or out.dtype != out_dtype or out.stride(1) != 1:
             raise KernelError("gemm_tc: out must be [T, N / 2] bfloat16 for the gated epilogue")
-    elif pieces:
+    elif pieces or residual is not None:
         out = None
     elif out is None:
-        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((T, N), dtype=out_dtype, device=dev)
     elif out.shape != (T, N) or out.dtype != out_dtype or out.stride(1) != 1:
         raise KernelError("gemm_tc: out must be [T, N] of the output type with unit inner stride")
-    partial = torch.empty((splits, T, N), dtype=torch.float32, device=x.device) if splits > 1 and not use_cluster else None
-    st = status_word(x.device)
-    _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), N if pieces else out.stride(0),
-                            T, N, K, swap, bn, splits, _ptr(partial), _ptr(st),
-                            (st.data_ptr() + 4) if fused_reduce else None, N_COUNTERS, int(gated), int(use_cluster), _stream()),
-           f"gemm_tc<{bn}>" + ("+gated" if gated else "") + ("+cluster" if use_cluster else "") + ("+pieces" if pieces else "")
-           + ("" if swap else "+rows"), launches=1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2)
+    partial = torch.empty((splits, T, N), dtype=torch.float32, device=dev) if splits > 1 and not use_cluster else None
+    st = status_word(dev)
+    ldo = N if out is None else out.stride(0)
+    name = (f"gemm_tc<{bn}>" + ("+gated" if gated else "") + ("+cluster" if use_cluster else "") + ("+pieces" if pieces else "")
+            + ("" if swap else "+rows") + ("+normed" if normed is not None else "") + ("+residual" if residual is not None else ""))
+    launches = 1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2
+    counters = (st.data_ptr() + 4) if fused_reduce else None
+    if normed is None and residual is None:
+        _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), ldo, T, N, K, swap, bn, splits,
+                                _ptr(partial), _ptr(st), counters, N_COUNTERS, int(gated), int(use_cluster), _stream()),
+               name, launches=launches)
+    else:
+        n = normed
+        _check(lib().tl_gemm_tc_normed(
+            _ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), ldo, T, N, K, swap, bn, splits,
+            _ptr(partial), _ptr(st), counters, N_COUNTERS, int(gated), int(use_cluster),
+            _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(ssq),
+            _ptr(n.x) if n else None, _ptr(n.ssq) if n else None, n.ssq.shape[1] if n else 0, _ptr(n.weight) if n else None,
+            int(n.weight.dtype == torch.float32) if n else 0, float(n.eps) if n else 0.0, _stream()), name, launches=launches)
+    if residual is not None:
+        return ssq
     return partial if pieces else out
 
 

@@ -26,6 +26,7 @@ from .linear import SplitSum, matmul
 @register_mixer("paged_attention")
 class PagedAttention(Part):
     graph_capturable = True
+    accepts_normed_input = True         # `h` may be a `NormedInput`: the q|k|v product normalises it on the fly
 
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None,
@@ -82,14 +83,14 @@ class PagedAttention(Part):
         pieces = None
         if isinstance(qkv, SplitSum):                    # a split-K product: the rotary kernel sums its pieces
             pieces = qkv.pieces
-            qkv = torch.empty(qkv.shape, dtype=h.dtype, device=h.device)
+            qkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=h.device)
         table = ctx.tables[cache.group]
         ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
                           nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces, pairing=rotary.pairing,
                           q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0)
-        o = torch.empty((T, nq * d), dtype=h.dtype, device=h.device)
+        o = torch.empty((T, nq * d), dtype=qkv.dtype, device=h.device)
         self.attend(qkv, o, ctx, cache, table)
-        return matmul(o, self.w_o, may_defer=True)             # the block's next norm adds it up
+        return matmul(o, self.w_o, may_defer=True, to_residual=True)     # the block's next norm adds it up
 
     def attend(self, qkv, o, ctx, cache, table):
         from . import attention_kernels

@@ -47,7 +47,15 @@ class PreNormBlock(Part):
         return all(part.graph_capturable for part in (self.norm1, self.mixer, self.norm2, self.ff))
 
     def forward(self, x, pending, ctx, cache):
-        h = self.norm1.add_norm(x, pending)
+        # a norm that supports it hands a part that says it can take one (`accepts_normed_input`) the recipe of its
+        # result instead of the result (see parts/linear.py)
+        h = self._norm(self.norm1, x, pending, self.mixer)
         a = self.mixer.forward(h, ctx, cache)
-        h = self.norm2.add_norm(x, a)
+        h = self._norm(self.norm2, x, a, self.ff)
         return self.ff.forward(h, ctx)
+
+    @staticmethod
+    def _norm(norm, x, pending, consumer):
+        if getattr(consumer, "accepts_normed_input", False) and getattr(norm, "can_defer", False):
+            return norm.add_norm(x, pending, defer=True)
+        return norm.add_norm(x, pending)

@@ -35,6 +35,7 @@ class LMHead(Part):
     """logits = h W^T in float32, no bias.  Tied: W is the embedding table; a stored
     `lm_head.weight` is then ignored."""
     graph_capturable = True
+    accepts_normed_input = True         # `h` may be a `NormedInput`: the product normalises it on the fly
 
     def __init__(self, rt: Runtime, vocab: int, dim: int, tied: bool):
         super().__init__(rt)

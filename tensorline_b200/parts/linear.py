@@ -55,14 +55,80 @@ class SplitSum:
         return ops_gemm.sum_pieces(self.pieces, self.dtype)
 
 
+# The layer's norms folded into the products around them (steps of few tokens, bfloat16): the product that makes an
+# addend adds it into the residual stream in its own epilogue, and the product that reads a norm's result normalises its
+# operand on the fly.  The norm kernel between them, which moves almost no bytes but costs a launch and two memory round
+# trips, goes away (two a layer).  TENSORLINE_B200_FUSE_NORMS=0: every norm a kernel of its own (A/B timing).
+FUSE_NORMS = os.environ.get("TENSORLINE_B200_FUSE_NORMS", "1") != "0"
+# Every block of the reading product normalises the activations of its K range itself; with many tokens that is more
+# traffic through L2 than the norm kernel saves, so steps of more tokens keep the norm kernel.
+FUSE_NORMS_MAX_TOKENS = int(os.environ.get("TENSORLINE_B200_FUSE_NORMS_MAX_TOKENS", 16))
+
+
+class PendingProduct:
+    """A product x W^T that has not run yet and whose result is an addend of the residual stream.  Whoever adds it up
+    (a norm) either lets the product do the addition itself (`add_into`) or runs it (`run`) and adds the result."""
+
+    def __init__(self, x: torch.Tensor, w: torch.Tensor):
+        self.x, self.w = x, w
+        self.dtype, self.shape = x.dtype, (x.shape[0], w.shape[0])
+
+    def run(self):
+        """The product as a tensor, or as a `SplitSum`."""
+        return matmul(self.x, self.w, may_defer=True)
+
+    def add_into(self, stream: torch.Tensor):
+        """stream += x W^T (rounded to the activation type first) inside the product's kernel; returns the partial sums
+        of squares of the stream's new rows, float32 [T, parts], or None if these sizes do not take that path."""
+        from .. import ops_gemm
+        T, N, K = self.x.shape[0], self.w.shape[0], self.w.shape[1]
+        if not (stream.dtype == torch.float32 and stream.shape == (T, N) and stream.is_contiguous() and N % 4 == 0
+                and ops_gemm.can_add_residual(T, N, K)):
+            return None
+        return ops_gemm.gemm_tc(self.x, self.w, residual=stream)
+
+
+class NormedInput:
+    """Activations that exist only as their recipe: rows of the float32 residual stream `x`, the partial sums of squares
+    of those rows `ssq` [rows of x, parts], the norm's weight and eps.  A product that takes it (`matmul`) normalises its
+    operand inside its kernel; anyone else calls `materialize()`.  `rows`: int32 indices into x, or None for all rows."""
+
+    def __init__(self, x, ssq, weight, eps, rows, dtype):
+        self.x, self.ssq, self.weight, self.eps, self.rows, self.dtype = x, ssq, weight, eps, rows, dtype
+        self.shape = (x.shape[0] if rows is None else rows.numel(), x.shape[1])
+        self.device = x.device
+
+    def is_contiguous(self) -> bool:
+        return True
+
+    def materialize(self) -> torch.Tensor:
+        h = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+        ops.add_rmsnorm(self.x, None, self.weight, h, self.eps, rows=self.rows)
+        return h
+
+
 def resolve(t):
-    """A tensor from what a projection returned."""
+    """A tensor from what a projection or a norm returned."""
+    if isinstance(t, PendingProduct):
+        t = t.run()
+    if isinstance(t, NormedInput):
+        return t.materialize()
     return t.sum() if isinstance(t, SplitSum) else t
 
 
-def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, may_defer: bool = False):
+def matmul(x, w: torch.Tensor, out_dtype: torch.dtype | None = None, may_defer: bool = False, to_residual: bool = False):
     """x [T, K] (float32 or bfloat16) times w [N, K]^T -> [T, N].  `may_defer`: the caller hands the
-    result to a consumer that takes a `SplitSum`."""
+    result to a consumer that takes a `SplitSum`.  `to_residual`: the result is an addend of the residual stream and
+    goes to a norm's `add_norm`: a `PendingProduct` may come back instead of a result.  `x` may be a `NormedInput`."""
+    if isinstance(x, NormedInput):
+        if x.rows is None and use_tc(x.shape[0], w.shape[0], w.shape[1]) and w.dtype == torch.bfloat16:
+            from .. import ops_gemm
+            y = ops_gemm.gemm_tc(x, w, out_dtype or x.dtype, pieces=may_defer)
+            return SplitSum(y, out_dtype or x.dtype) if y.dim() == 3 else y
+        x = x.materialize()
+    if to_residual and FUSE_NORMS and x.shape[0] <= FUSE_NORMS_MAX_TOKENS and x.dtype == torch.bfloat16 and x.is_cuda and \
+            x.is_contiguous() and use_tc(x.shape[0], w.shape[0], w.shape[1]) and out_dtype in (None, x.dtype):
+        return PendingProduct(x, w)
     if x.dtype == torch.float32:
         out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
         ops.gemm_f32(x, w, out)

@@ -11,7 +11,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_feed_forward
-from .linear import matmul, use_pair_product, use_tc
+from .linear import NormedInput, matmul, use_pair_product, use_tc
 
 GATE_BLOCK = 64
 
@@ -19,6 +19,7 @@ GATE_BLOCK = 64
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
     graph_capturable = True
+    accepts_normed_input = True         # `h` may be a `NormedInput`: the gate|up product normalises it on the fly
 
     def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu"):
         super().__init__(rt)
@@ -47,11 +48,15 @@ class GatedMLP(Part):
 
     def forward(self, h, ctx):
         I = self.intermediate
+        if isinstance(h, NormedInput) and h.rows is not None:
+            h = h.materialize()
         if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
                 m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=True)
-                return matmul(m, self.w_down, may_defer=True)
+                return matmul(m, self.w_down, may_defer=True, to_residual=True)
+        if isinstance(h, NormedInput):                   # only the few-token products above take the recipe
+            h = h.materialize()
         if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=True)          # long steps: pairs of blocks, activation in the epilogue
@@ -59,4 +64,4 @@ class GatedMLP(Part):
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)
         ops.silu_mul(gu, m, block=self.block)
-        return matmul(m, self.w_down, may_defer=True)          # the next norm adds it up
+        return matmul(m, self.w_down, may_defer=True, to_residual=True)          # the next norm adds it up

@@ -602,3 +602,70 @@ def test_two_block_product_with_the_activation_in_its_epilogue(T, I, K):
     assert_close(got, want, "gated two-block product", rtol=2e-2, atol=2e-2 * float(want.abs().max()))
     with pytest.raises(ops.KernelError, match="gated"):
         ops_gemm.gemm_tc2(x, w[:64], gated=True)               # 64 rows: a gate block without its up block
+
+
+@pytest.mark.parametrize("T,N,K,rows", [(8, 3584, 3584, None), (5, 264, 2056, None), (37, 4608, 1024, None), (64, 2560, 520, None),
+                                         (16, 1152, 648, None)])
+@pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
+def test_product_that_normalises_its_operand_on_the_fly(T, N, K, rows, wdt):
+    """The few-token product fed with the recipe of a norm's result (residual stream, partial sums of squares, norm
+    weight) instead of the result: bit for bit what the product of the same normalised activations gives, when those
+    are made with the same rstd (the partial sums added as the kernel adds them: eight lanes, then a butterfly), cast
+    before and after the weight as the norm kernel casts."""
+    from tensorline_b200 import ops_gemm
+    from tensorline_b200.parts.linear import NormedInput
+    eps = 1e-5
+    R = T if rows is None else 8
+    x = rnd(R, K, seed=1, scale=1.5).cuda()
+    w = rnd(N, K, seed=2, scale=0.1, dtype=torch.bfloat16).cuda()
+    nw = (1 + rnd(K, seed=3, scale=0.2)).to(wdt).cuda()
+    parts = 5
+    cut = [0, K // 7, K // 3, K // 2, K - 8, K]
+    ssq = torch.stack([(x[:, cut[i]:cut[i + 1]] ** 2).sum(-1) for i in range(parts)], dim=1).contiguous()
+    sel = None if rows is None else i32(rows)
+    v = [ssq[:, p] if p < parts else torch.zeros(R, device="cuda") for p in range(8)]
+    total = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))
+    rstd = 1.0 / torch.sqrt(total / K + eps)
+    h = ((x * rstd[:, None]).to(torch.bfloat16).float() * nw.float()).to(torch.bfloat16)
+    if rows is not None:
+        h = h[rows]
+    want = ops_gemm.gemm_tc(h.contiguous(), w, torch.float32)
+    got = ops_gemm.gemm_tc(NormedInput(x, ssq, nw, eps, sel, torch.bfloat16), w, torch.float32)
+    ops_gemm.check_status()
+    assert torch.equal(got, want)
+    assert_close(got, h.double() @ w.double().T, "normed product", rtol=1e-4, atol=1e-4 * float(want.abs().max()))
+    if N % 128 == 0 and ops_gemm.can_gate(T, N, K):          # with the activation in the epilogue as well
+        assert torch.equal(ops_gemm.gemm_tc(NormedInput(x, ssq, nw, eps, sel, torch.bfloat16), w, gated=True),
+                           ops_gemm.gemm_tc(h.contiguous(), w, gated=True))
+
+
+@pytest.mark.parametrize("T,N,K", [(8, 3584, 3584), (8, 3584, 18944), (1, 5120, 5120), (37, 1024, 4096), (64, 3584, 2048), (5, 264, 2056)])
+def test_product_that_adds_its_result_into_the_residual_stream(T, N, K):
+    """The few-token product whose K ranges are summed inside a cluster, adding its result into the float32 residual
+    stream itself: the stream becomes bit for bit x + (the product rounded to bfloat16), and the partial sums of squares
+    it leaves add up to the squares of the new rows; the norm fed with them agrees with the norm kernel."""
+    from tensorline_b200 import ops, ops_gemm
+    from tensorline_b200.parts.linear import NormedInput
+    if not ops_gemm.can_add_residual(T, N, K):
+        pytest.skip("the plan for these sizes has no cluster of 2..8 K ranges")
+    a = rnd(T, K, seed=1, dtype=torch.bfloat16).cuda()
+    w = rnd(N, K, seed=2, scale=0.05, dtype=torch.bfloat16).cuda()
+    x = rnd(T, N, seed=3, scale=2.0).cuda()
+    y = ops_gemm.gemm_tc(a, w)                                 # the same ranges, summed in the same order, rounded to bfloat16
+    want = x + y.float()
+    got = x.clone()
+    ssq = ops_gemm.gemm_tc(a, w, residual=got)
+    ops_gemm.check_status()
+    assert torch.equal(got, want)
+    assert ssq.shape == (T, -(-N // 128)) and ssq.dtype == torch.float32
+    assert_close(ssq.sum(-1), (want.double() ** 2).sum(-1), "sums of squares", rtol=1e-5, atol=1e-5)
+    nw = (1 + rnd(N, seed=4, scale=0.2)).to(torch.bfloat16).cuda()
+    h_kernel = torch.empty(T, N, dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(want.clone(), None, nw, h_kernel, 1e-6)
+    h_recipe = NormedInput(got, ssq, nw, 1e-6, None, torch.bfloat16).materialize()
+    assert torch.equal(h_recipe, h_kernel)                    # materialize() is the norm kernel itself
+    if N % 8 == 0:
+        w2 = rnd(256, N, seed=5, scale=0.05, dtype=torch.bfloat16).cuda()
+        fused = ops_gemm.gemm_tc(NormedInput(got, ssq, nw, 1e-6, None, torch.bfloat16), w2, torch.float32)
+        plain = ops_gemm.gemm_tc(h_kernel, w2, torch.float32)
+        assert_close(fused, plain, "norm folded into the next product", rtol=2e-2, atol=2e-2 * float(plain.abs().max()))
