@@ -79,7 +79,53 @@ struct AttnArgs {
     // all requests; null: one request after the other from the end
     const int* order;
     TlLimits lim;                      // for the checking build; zeros: nothing known, nothing checked
+    // TMA decode with the rotary step folded in: `q` points at the step's q|k|v rows as the projection left them (row stride
+    // q_stride, k of KV head h at column (nq + h) * D, v at (nq + nkv + h) * D).  The block applies bias and rotation to its
+    // query heads on the way to shared memory; the block whose key range holds the token's own position does the same for
+    // the new key and value, writes them to their page (rope_write) and puts them into its own tiles.  Null inv_freq: not folded.
+    const float* rope_inv_freq; const void* rope_bias; int rope_bias_f32; int rope_write;
+    bf16* k_pages_w; bf16* v_pages_w;
 };
+
+// Eight values at i0.. and the eight at D/2 + i0.. of one head's row: + bias, rotated (rotate-half pairs, angle of pair i in
+// cs[i] = cos, cs[D/2 + i] = sin) unless `rotate` is false, rounded to bfloat16.  The arithmetic of rope_kv_vec_kernel.
+__device__ __forceinline__ void rope_pairs(const bf16* row, const void* bias, int bias_f32, int bias_off, int i0, const float* cs,
+                                           bool rotate, uint4& lo, uint4& hi) {
+    constexpr int half = HEAD_DIM / 2;
+    const uint4 av = *reinterpret_cast<const uint4*>(row + i0), bv = *reinterpret_cast<const uint4*>(row + half + i0);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+    float a[8], b[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        a[2 * k] = __low2float(a2[k]); a[2 * k + 1] = __high2float(a2[k]);
+        b[2 * k] = __low2float(b2[k]); b[2 * k + 1] = __high2float(b2[k]);
+    }
+    if (bias) {
+        if (bias_f32) {
+            const float* bp = (const float*)bias + bias_off;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { a[k] += bp[i0 + k]; b[k] += bp[half + i0 + k]; }
+        } else {
+            const bf16* bp = (const bf16*)bias + bias_off;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { a[k] += __bfloat162float(bp[i0 + k]); b[k] += __bfloat162float(bp[half + i0 + k]); }
+        }
+    }
+    if (rotate) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float c = cs[i0 + k], sn = cs[half + i0 + k];
+            const float ra = __fmul_rn(a[k], c) - __fmul_rn(b[k], sn);
+            const float rb = __fmul_rn(b[k], c) + __fmul_rn(a[k], sn);
+            a[k] = ra; b[k] = rb;
+        }
+    }
+    __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { lo2[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]); hi2[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]); }
+}
 
 // A [ROWS][DP] tile of keys (or values) of one KV head is filled by 128 threads in chunks of 16
 // bytes.  Which chunk a thread copies never changes, so its place inside a page, its page
@@ -494,7 +540,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 constexpr int TMA_TILE_BYTES = BN * D * 2;                       // K or V of one stage
 constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
 constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
-constexpr int TMA_TAB_OFFSET = TMA_BAR_OFFSET + 128;             // room for 2 * DEC_STAGES barriers and a flag
+constexpr int TMA_CS_OFFSET = TMA_BAR_OFFSET + 128;              // room for 2 * DEC_STAGES barriers and a flag; then cos, sin [D]
+constexpr int TMA_TAB_OFFSET = TMA_CS_OFFSET + D * 4;
 #ifndef TL_TMA_COPY_WARPS
 #define TL_TMA_COPY_WARPS 2
 #endif
@@ -588,7 +635,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     grid_dependency_wait();                                // queries and the newest keys and values: the kernel before
     grid_dependency_trigger();
-    if (warp < 4) {
+    const bool fold = A.rope_inv_freq != nullptr;          // bias and rotation of q, k, v happen here, not in a kernel before
+    float* cs = reinterpret_cast<float*>(tiles + TMA_CS_OFFSET);
+    if (warp < 4 && !fold) {
         for (int idx = tid; idx < 16 * CH; idx += 128) {
             const int r = idx / CH, c = idx - r * CH;
             const int hg = mt * 16 + r;
@@ -599,7 +648,48 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         cp_async_commit();
     }
+    if (warp < 4 && fold) {
+        for (int i = tid; i < D / 2; i += 128) {           // the token's angles, once for all its heads
+            float sn, c;
+            sincosf(__fmul_rn((float)pos, A.rope_inv_freq[i]), &sn, &c);
+            cs[i] = c; cs[D / 2 + i] = sn;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        constexpr int PER = D / 16;                        // items of 8 + 8 values a head
+        for (int item = tid; item < 16 * PER; item += 128) {
+            const int r = item / PER, i0 = (item - r * PER) * 8, hg = mt * 16 + r;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (hg < g) {
+                const int head = kh * g + hg;
+                rope_pairs(A.q + (size_t)qrow * A.q_stride + (size_t)head * D, A.rope_bias, A.rope_bias_f32, head * D, i0, cs, true, lo, hi);
+            }
+            *reinterpret_cast<uint4*>(sQ + r * DP + i0) = lo;
+            *reinterpret_cast<uint4*>(sQ + r * DP + D / 2 + i0) = hi;
+        }
+    }
     __syncthreads();                                       // table copy and barriers are visible
+    // The token's own key and value: made by the block whose range holds its position, written to their page by one of the
+    // blocks of that range (the first row tile), and kept in registers to be put into this block's tiles when that stage
+    // has landed (the page in memory still holds what was there before).
+    const bool has_new = fold && A.rope_write && n_stage > 0 && pos >= k_begin && pos < k_end;
+    const int st_new = has_new ? (pos - k_begin) / BN : -1, r_new = (pos - k_begin) % BN;
+    uint4 new_lo = make_uint4(0, 0, 0, 0), new_hi = new_lo;
+    int new_i0 = -1, new_is_v = 0;
+    if (has_new && warp < 4) {
+        constexpr int PER = D / 16;
+        if (tid >= 64 && tid < 64 + PER) { new_i0 = (tid - 64) * 8; new_is_v = 0; }
+        else if (tid >= 96 && tid < 96 + PER) { new_i0 = (tid - 96) * 8; new_is_v = 1; }
+        if (new_i0 >= 0) {
+            const int col = (A.nq + (new_is_v ? A.nkv : 0) + kh) * D;
+            rope_pairs(A.q + (size_t)qrow * A.q_stride + col, A.rope_bias, A.rope_bias_f32, col, new_i0, cs, !new_is_v, new_lo, new_hi);
+            if (mt == 0) {
+                const int page = stab[pos / A.page_size - first_page];
+                bf16* dst = (new_is_v ? A.v_pages_w : A.k_pages_w) + (((size_t)page * A.nkv + kh) * A.page_size + pos % A.page_size) * D;
+                *reinterpret_cast<uint4*>(dst + new_i0) = new_lo;
+                *reinterpret_cast<uint4*>(dst + D / 2 + new_i0) = new_hi;
+            }
+        }
+    }
 
     // The copy warps: a TMA copy takes about 95 cycles to issue, whether the boxes of a stage come from one thread
     // or from the lanes of one warp instruction, and a stage is 2 * (64 / page) * (D / 64) boxes (16 for pages of
@@ -635,6 +725,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     cp_async_wait<0>();
     asm volatile("bar.sync 1, 128;" ::: "memory");         // the queries are in (the four compute warps only)
+    (void)r_new;
     uint32_t qf[KBLK][4];
 #pragma unroll
     for (int kb = 0; kb < KBLK; ++kb)
@@ -649,6 +740,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int st = 0; st < n_stage; ++st) {
         const int buf = st % DEC_STAGES;
         if (!mbar_wait_tma(full + buf, (st / DEC_STAGES) & 1, abort_flag, status)) break;
+        if (st == st_new) {                                // the stage with the token's own position: its new key and value
+            if (new_i0 >= 0) {
+                unsigned char* tile = tiles + buf * 2 * TMA_TILE_BYTES + (new_is_v ? TMA_TILE_BYTES : 0);
+                const int c_lo = new_i0 >> 3, c_hi = (D / 2 + new_i0) >> 3;
+                *reinterpret_cast<uint4*>(tile + (c_lo >> 3) * (BN * 128) + r_new * 128 + (((c_lo & 7) ^ (r_new & 7)) << 4)) = new_lo;
+                *reinterpret_cast<uint4*>(tile + (c_hi >> 3) * (BN * 128) + r_new * 128 + (((c_hi & 7) ^ (r_new & 7)) << 4)) = new_hi;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // before a later TMA copy into the same buffer
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         const int key0 = k_begin + st * BN + warp * 16;    // this warp's 16 keys of the stage
         if (key0 >= k_end) {                               // none of them exist: hand the buffer back at once
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + buf)) : "memory");
@@ -939,13 +1040,17 @@ int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_
 // tl_attn_decode with K and V loaded by TMA.  Needs a head size that is a multiple of 64, pages of 8 to 64
 // tokens, and `total_pages` (first dimension of the cache tensors).  `status`: device int for a wait that
 // ran out (may be null).  Returns 2 if this build or these sizes do not take the TMA path.
-TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
-                                 long long total_pages, const int* table, int max_pages, int page_size,
-                                 const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
-                                 int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
-                                 int* status, int cluster_merge, int table_rows, int* fault, cudaStream_t stream) {
+namespace {
+struct RopeFold { const float* inv_freq; const void* bias; int bias_f32; int write_kv; };
+
+int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                    long long total_pages, const int* table, int max_pages, int page_size,
+                    const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                    int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
+                    int* status, int cluster_merge, int table_rows, int* fault, const RopeFold& R, cudaStream_t stream) {
 #if HEAD_DIM % 64 == 0
     if (B <= 0) return 0;
+    if (R.inv_freq && ((q_stride & 7) || ((uintptr_t)q & 15) || (R.bias && ((uintptr_t)R.bias & 15)))) return 2;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     // cluster_merge: the key ranges of a (request, KV head) merge inside a thread-block cluster, no partials needed
     if (cluster_merge && (splits < 2 || splits > 8 || nq / (nkv > 0 ? nkv : 1) > 16)) return 1;
@@ -986,6 +1091,8 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
     A.lim = TlLimits{table_rows, (int)total_pages, fault};
+    A.rope_inv_freq = R.inv_freq; A.rope_bias = R.bias; A.rope_bias_f32 = R.bias_f32; A.rope_write = R.write_kv;
+    A.k_pages_w = (bf16*)const_cast<void*>(k_pages); A.v_pages_w = (bf16*)const_cast<void*>(v_pages);
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
     if (grid.z > 65535) return 1;
@@ -1009,6 +1116,33 @@ TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const v
 #else
     return 2;
 #endif
+}
+}  // namespace
+
+TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                 long long total_pages, const int* table, int max_pages, int page_size,
+                                 const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                 int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
+                                 int* status, int cluster_merge, int table_rows, int* fault, cudaStream_t stream) {
+    return decode_tma_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
+                           B, nq, nkv, window, scale, chunk, splits, part_o, part_ml, status, cluster_merge, table_rows, fault,
+                           RopeFold{nullptr, nullptr, 0, 0}, stream);
+}
+
+// The same with the rotary step folded in (full rotation over rotate-half pairs, no q/k norm): `q` points at the step's q|k|v
+// rows as the projection left them, [T, (nq + 2 nkv) * D] with row stride q_stride; bias (float or bfloat16, may be null)
+// and inv_freq [D / 2] as tl_rope_kv_write takes them; write_kv: the token's key and value are written to their page.
+// Returns 2 (nothing launched) for what it does not take; the caller then runs the rotary kernel and the decode kernel apart.
+TL_EXPORT int tl_attn_decode_tma_rope(const void* qkv, int q_stride, void* out, void* k_pages, void* v_pages,
+                                      long long total_pages, const int* table, int max_pages, int page_size,
+                                      const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                      int window, float scale, int chunk, int splits, float* part_o, float* part_ml,
+                                      int* status, int cluster_merge, int table_rows, int* fault,
+                                      const float* inv_freq, const void* bias, int bias_f32, int write_kv, cudaStream_t stream) {
+    if (inv_freq == nullptr) return 1;
+    return decode_tma_impl(qkv, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
+                           B, nq, nkv, window, scale, chunk, splits, part_o, part_ml, status, cluster_merge, table_rows, fault,
+                           RopeFold{inv_freq, bias, bias_f32, write_kv}, stream);
 }
 
 // ------------------------------------------------------------------------------------ no allocation

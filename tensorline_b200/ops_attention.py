@@ -41,6 +41,8 @@ def attn_lib(head_dim: int):
         lib.tl_attn_decode_tma.argtypes = [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _P, _P, _P, _I, _I, _P, _P]
         lib.tl_attn_decode_tma.restype = ctypes.c_int
+        lib.tl_attn_decode_tma_rope.argtypes = lib.tl_attn_decode_tma.argtypes[:-1] + [_P, _P, _I, _I, _P]
+        lib.tl_attn_decode_tma_rope.restype = ctypes.c_int
         if lib.tl_attn_decode_max_table() != DECODE_MAX_TABLE_ENTRIES:
             raise KernelError(f"the attention library copies {lib.tl_attn_decode_max_table()} block-table entries a block, "
                               f"the split planner assumes {DECODE_MAX_TABLE_ENTRIES}")
@@ -212,16 +214,30 @@ TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.
 CLUSTER_MERGE = os.environ.get("TENSORLINE_B200_CLUSTER_MERGE", "1") != "0"   # 0: partials + combine kernel (A/B timing)
 
 
+FOLD_ROPE = os.environ.get("TENSORLINE_B200_FOLD_ROPE", "1") != "0"   # 0: the rotary step always a kernel of its own (A/B timing)
+
+
+def decode_takes_rope(B: int, d: int, page_size: int) -> bool:
+    """Whether a decode step of these sizes goes to the kernel that can do bias, rotation and the page write of the
+    step's own tokens itself (the TMA decode kernel, as `decode` picks it)."""
+    return FOLD_ROPE and TMA_DECODE and B >= 4 and d % 64 == 0 and 8 <= page_size <= 64 and page_size & (page_size - 1) == 0
+
+
 def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
            nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None, tma: bool | None = None,
-           cluster: bool | None = None) -> None:
+           cluster: bool | None = None, rope: dict | None = None) -> None:
     """Split-KV decode attention.  `tma`: load K and V by TMA (head sizes that are multiples of 64, pages of
     8..64 tokens); None = wherever that applies.  `cluster` (TMA path, 2..8 key ranges, groups of at most 16
     heads): the ranges of a request merge inside a thread-block cluster, no partials, no second kernel;
-    None = wherever that applies."""
+    None = wherever that applies.
+    `rope` (TMA path only; see `decode_takes_rope`): `q` is the step's q|k|v as the projection left it and the kernel
+    does bias, rotation and the page write itself: {"inv_freq", "bias" (or None), "write_kv", "unfold"}; `unfold()`
+    runs the rotary kernel instead, for the case that the library turns the launch down."""
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
     use_tma = (TMA_DECODE and B >= 4 if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
+    if rope is not None and not use_tma:
+        raise KernelError("attn_decode: the rotary step folds into the TMA kernel only")
     can_cluster = use_tma and 2 <= splits <= 8 and nq // nkv <= 16
     use_cluster = can_cluster and (CLUSTER_MERGE if cluster is None else cluster)
     if splits > 1 and not use_cluster:
@@ -233,17 +249,25 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
     # below that the launch is too short for the difference to show and the tensor-map set-up costs a little
     if use_tma:
         from .ops_gemm import status_word
-        rc = attn_lib(d).tl_attn_decode_tma(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
-                                            _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
-                                            _ptr(slots), B, nq, nkv, int(window or 0), float(scale), chunk, splits,
-                                            _ptr(part_o) if splits > 1 and not use_cluster else None,
-                                            _ptr(part_ml) if splits > 1 and not use_cluster else None,
-                                            _ptr(status_word(q.device)), int(use_cluster), table.shape[0],
-                                            ops.fault_words(q.device), _stream())
+        args = (_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
+                _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
+                _ptr(slots), B, nq, nkv, int(window or 0), float(scale), chunk, splits,
+                _ptr(part_o) if splits > 1 and not use_cluster else None,
+                _ptr(part_ml) if splits > 1 and not use_cluster else None,
+                _ptr(status_word(q.device)), int(use_cluster), table.shape[0], ops.fault_words(q.device))
+        if rope is not None:
+            bias = rope["bias"]
+            rc = attn_lib(d).tl_attn_decode_tma_rope(*args, _ptr(rope["inv_freq"]), _ptr(bias),
+                                                     int(bias is not None and bias.dtype == torch.float32),
+                                                     int(rope["write_kv"]), _stream())
+        else:
+            rc = attn_lib(d).tl_attn_decode_tma(*args, _stream())
         if rc != 2:                                    # 2: this build or these sizes do not take the TMA path
-            _check(rc, "attn_decode_tma" + ("+cluster" if use_cluster else "+combine" if splits > 1 else ""),
+            _check(rc, "attn_decode_tma" + ("+rope" if rope is not None else "") + ("+cluster" if use_cluster else "+combine" if splits > 1 else ""),
                    launches=2 if splits > 1 and not use_cluster else 1)
             return
+        if rope is not None:                           # turned down: the rotary step as a kernel of its own after all
+            rope["unfold"]()
     _check(attn_lib(d).tl_attn_decode(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                       table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                       nq, nkv, int(window or 0), float(scale), chunk, splits,
@@ -252,10 +276,13 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
-def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale) -> None:
+def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None) -> None:
+    """`rope`: only for decode-only steps that `decode_takes_rope` accepted (see `decode`)."""
     if qkv.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attend_bf16: bfloat16 tensors only")
     q_stride = qkv.shape[1]
+    if rope is not None and not ctx.decode_only:
+        raise KernelError("attend_bf16: the rotary step folds into decode-only steps")
     if ctx.decode_only:
         span = ctx.graph_max_ctx or ctx.max_ctx
         if window:
@@ -266,7 +293,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale)
             part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((ctx.B, nq, splits, 2), dtype=torch.float32, device=qkv.device)
         decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
-               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope)
     else:
         g = nq // nkv
         singles = _single_token_requests(ctx, qkv.device, g)

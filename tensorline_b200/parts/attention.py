@@ -85,13 +85,28 @@ class PagedAttention(Part):
             pieces = qkv.pieces
             qkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=h.device)
         table = ctx.tables[cache.group]
-        ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
-                          nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces, pairing=rotary.pairing,
-                          q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0)
+
+        def rotary_kernel():
+            ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
+                              nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces, pairing=rotary.pairing,
+                              q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0)
+
+        # A step of single tokens whose attention kernel can do bias, rotation and the page write of its own tokens
+        # (the TMA decode kernel) needs no rotary kernel in front of it.
+        fold = None
+        if (ctx.decode_only and not ctx.force_exact_attention and qkv.dtype == torch.bfloat16 and pieces is None and plain
+                and rot == d and self._folds_rope(ctx)):
+            fold = {"inv_freq": inv_freq, "bias": self.b_qkv, "write_kv": cache.owner, "unfold": rotary_kernel}
+        else:
+            rotary_kernel()
         o = torch.empty((T, nq * d), dtype=qkv.dtype, device=h.device)
-        self.attend(qkv, o, ctx, cache, table)
+        self.attend(qkv, o, ctx, cache, table, rope=fold)
         return matmul(o, self.w_o, may_defer=True, to_residual=True)     # the block's next norm adds it up
 
-    def attend(self, qkv, o, ctx, cache, table):
+    def _folds_rope(self, ctx) -> bool:
+        from .. import ops_attention
+        return ops_attention.decode_takes_rope(ctx.B, self.d, ctx.page_size)
+
+    def attend(self, qkv, o, ctx, cache, table, rope=None):
         from . import attention_kernels
-        attention_kernels.attend(self, qkv, o, ctx, cache, table)
+        attention_kernels.attend(self, qkv, o, ctx, cache, table, rope=rope)

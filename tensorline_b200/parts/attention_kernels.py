@@ -12,11 +12,11 @@ import torch
 from .. import ops
 
 
-def attend(mixer, qkv, o, ctx, cache, table) -> None:
+def attend(mixer, qkv, o, ctx, cache, table, rope=None) -> None:
     nq, nkv, d = mixer.nq, mixer.nkv, mixer.d
     if qkv.dtype == torch.float32 or ctx.force_exact_attention:
         ops.attn_tokenwise(qkv, qkv.shape[1], o, cache.k, cache.v, table, ctx.page_size, ctx.pos, ctx.req_slot,
                            nq, nkv, d, mixer.window, mixer.scale)
         return
     from .. import ops_attention
-    ops_attention.attend_bf16(qkv, o, ctx, cache.k, cache.v, table, nq, nkv, d, mixer.window, mixer.scale)
+    ops_attention.attend_bf16(qkv, o, ctx, cache.k, cache.v, table, nq, nkv, d, mixer.window, mixer.scale, rope=rope)

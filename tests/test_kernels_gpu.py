@@ -669,3 +669,61 @@ def test_product_that_adds_its_result_into_the_residual_stream(T, N, K):
         fused = ops_gemm.gemm_tc(NormedInput(got, ssq, nw, 1e-6, None, torch.bfloat16), w2, torch.float32)
         plain = ops_gemm.gemm_tc(h_kernel, w2, torch.float32)
         assert_close(fused, plain, "norm folded into the next product", rtol=2e-2, atol=2e-2 * float(plain.abs().max()))
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps,ctx_lens,window,bias_dt", [
+    (28, 4, 128, 16, [300, 0, 63, 64, 1000], None, torch.bfloat16),
+    (20, 1, 64, 8, [77, 200, 5, 128], None, torch.float32),          # 20 heads a group: two row tiles a range
+    (14, 2, 64, 32, [500, 129, 31, 32], 100, None),                  # a window, no bias
+    (7, 1, 128, 64, [15, 16, 2000, 640], None, torch.bfloat16),
+])
+def test_decode_attention_with_the_rotary_step_folded_in(nq, nkv, d, ps, ctx_lens, window, bias_dt):
+    """The TMA decode kernel doing bias, rotation and the page write of the step's own tokens itself gives bit for bit
+    what the rotary kernel followed by the decode kernel gives: the same outputs and the same pages, with one key
+    range, with ranges merged by the combine kernel and with ranges merged inside clusters."""
+    from tensorline_b200 import ops, ops_attention
+    B = len(ctx_lens)
+    g = torch.Generator().manual_seed(11)
+    num_pages, max_pages = 400, 160
+    kp = torch.randn(num_pages + 1, nkv, ps, d, generator=g).to(torch.bfloat16).cuda()
+    vp = torch.randn(num_pages + 1, nkv, ps, d, generator=g).to(torch.bfloat16).cuda()
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    rows, used = [], 0
+    for n in ctx_lens:
+        need = -(-(n + 1) // ps)
+        rows.append(perm[used:used + need]); used += need
+    table = table_tensor(rows, max_pages, num_pages)
+    qkv = (torch.randn(B, (nq + 2 * nkv) * d, generator=g) * 1.5).to(torch.bfloat16).cuda()
+    bias = None if bias_dt is None else (torch.randn((nq + 2 * nkv) * d, generator=g) * 0.5).to(bias_dt).cuda()
+    inv_freq = (1e4 ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).float().cuda()
+    pos, slots, q_start = i32(ctx_lens), i32(list(range(B))), i32(list(range(B + 1)))
+    span = max(ctx_lens) + 1
+    if window:
+        span = min(span, window + 63)
+    tiles = -(-span // 64)
+    for splits_wanted, cluster in ((1, False), (3, False), (3, True), (8, True)):
+        splits = min(splits_wanted, tiles)
+        chunk = -(-tiles // splits) * 64
+        splits = -(-tiles * 64 // chunk)
+        if cluster and not 2 <= splits <= 8:
+            continue
+        po = torch.empty(B, nq, splits, d, device="cuda")
+        pml = torch.empty(B, nq, splits, 2, device="cuda")
+        # apart: the rotary kernel, then the decode kernel
+        q1, k1, v1 = qkv.clone(), kp.clone(), vp.clone()
+        ops.rope_kv_write(q1, bias, pos, slots, table, ps, inv_freq, d, nq, nkv, d, k1, v1)
+        want = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
+        ops_attention.decode(q1, q1.shape[1], want, k1, v1, table, ps, q_start, pos, slots, B, nq, nkv, d, window, d ** -0.5,
+                             chunk, splits, po, pml, tma=True, cluster=cluster)
+        # folded
+        k2, v2 = kp.clone(), vp.clone()
+        got = torch.zeros_like(want)
+        before = ops.kernel_counts.copy()
+        ops_attention.decode(qkv, qkv.shape[1], got, k2, v2, table, ps, q_start, pos, slots, B, nq, nkv, d, window, d ** -0.5,
+                             chunk, splits, po, pml, tma=True, cluster=cluster,
+                             rope={"inv_freq": inv_freq, "bias": bias, "write_kv": True, "unfold": lambda: pytest.fail("turned down")})
+        ops.check_device_status()
+        assert any(k.startswith("attn_decode_tma+rope") for k in (ops.kernel_counts - before))
+        assert torch.equal(k2, k1) and torch.equal(v2, v1), f"pages differ ({splits} ranges, cluster {cluster})"
+        assert torch.equal(got, want), f"outputs differ ({splits} ranges, cluster {cluster})"
+        assert float(want.float().abs().max()) > 0.05

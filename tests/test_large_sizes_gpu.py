@@ -131,8 +131,9 @@ def test_long_prompt_takes_the_two_tile_attention_and_agrees_with_the_other_kern
 def test_decode_graph_at_these_sizes_agrees_with_the_32_bit_engine_and_the_plain_model(big, batch):
     """The step the benchmark times, asserted: `batch` requests at contexts of 1,000 to 1,500 keys decode through
     the CUDA graph of their bucket (a padding row or more at 33).  Inside it: the tcgen05 product with 16- or
-    64-token tiles, its gated epilogue, split-K sums inside clusters or left to their consumers, TMA decode attention
-    with the merge inside clusters (observed from the captured graph, not inferred).  The logits are compared with
+    64-token tiles, its gated epilogue, split-K sums inside clusters or left to their consumers, at batch 8 the norms
+    folded into the products around them and the rotary step folded into the TMA decode attention, whose key ranges
+    merge inside clusters (observed from the captured graph, not inferred).  The logits are compared with
     the 32-bit engine on the same weights and schedule (every row) and with the plain model (two rows)."""
     from tensorline_b200 import Engine, ops
     from tensorline_b200.engine.runner import StepEntry
@@ -164,8 +165,10 @@ def test_decode_graph_at_these_sizes_agrees_with_the_32_bit_engine_and_the_plain
             assert any(k.startswith(f"gemm_tc<{bn}>") for k in kernels), kernels
             assert any("+gated" in k for k in kernels) and any("+cluster" in k or "+pieces" in k for k in kernels), kernels
             assert any(k.startswith("attn_decode_tma") for k in kernels), kernels
-            if batch == 8:
-                assert "attn_decode_tma+cluster" in kernels, kernels
+            if batch == 8:                                # key ranges merged inside clusters, the rotary step folded in,
+                assert "attn_decode_tma+rope+cluster" in kernels and "rope_kv_write" not in kernels, kernels
+                assert any(k.endswith("+normed") for k in kernels) and any(k.endswith("+residual") for k in kernels), kernels
+                assert kernels["add_rmsnorm"] == 2, kernels     # the first layer's first norm and the last norm: the rest are folded
             assert runner._bucket(batch) > batch or batch == 8
         ops.check_device_status()
         del eng, runner, cache
