@@ -244,7 +244,10 @@ def e2e_decode(eng, batch, ctx0, steps, warmup, vocab):
     return produced / dt, h2d, d2h
 
 
-def timed_prefill(eng, tokens, vocab, iters=5, warm=3):
+def timed_prefill(eng, tokens, vocab, iters=24, warm=4):
+    """Median time of one `tokens`-token prompt step.  Under the power limit the clock of a run of such steps swings
+    with a period of about ten steps (single steps of the 7B sizes read 21 to 27 ms, the first ones after a pause the
+    fastest), so the median is taken over two dozen."""
     import torch
     from tensorline_b200.engine.runner import StepEntry
     runner, cache = eng.runner, eng.cache
