@@ -633,9 +633,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
-    grid_dependency_wait();                                // queries and the newest keys and values: the kernel before
-    grid_dependency_trigger();
     const bool fold = A.rope_inv_freq != nullptr;          // bias and rotation of q, k, v happen here, not in a kernel before
+    // When this kernel itself makes and writes the token's own key and value, the pages hold nothing that the kernel in
+    // front writes (what is in them is from earlier steps, whose kernels have all finished before this one may start): the
+    // copy warps then request the first stages at once, while the kernel in front is still at its last tiles.
+    const bool early = fold && A.rope_write;
+    __syncthreads();                                       // table copy and barriers are visible
+    if (warp < 4 || !early) {
+        grid_dependency_wait();                            // queries and the newest keys and values: the kernel before
+        grid_dependency_trigger();
+    }
     float* cs = reinterpret_cast<float*>(tiles + TMA_CS_OFFSET);
     if (warp < 4 && !fold) {
         for (int idx = tid; idx < 16 * CH; idx += 128) {
@@ -667,7 +674,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             *reinterpret_cast<uint4*>(sQ + r * DP + D / 2 + i0) = hi;
         }
     }
-    __syncthreads();                                       // table copy and barriers are visible
     // The token's own key and value: made by the block whose range holds its position, written to their page by one of the
     // blocks of that range (the first row tile), and kept in registers to be put into this block's tiles when that stage
     // has landed (the page in memory still holds what was there before).

@@ -211,6 +211,7 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
 
 
 TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.async loads only (A/B timing)
+TMA_DECODE_MIN_BATCH = int(os.environ.get("TENSORLINE_B200_TMA_DECODE_MIN_BATCH", "1"))   # fewer requests: cp.async loads
 CLUSTER_MERGE = os.environ.get("TENSORLINE_B200_CLUSTER_MERGE", "1") != "0"   # 0: partials + combine kernel (A/B timing)
 
 
@@ -220,7 +221,7 @@ FOLD_ROPE = os.environ.get("TENSORLINE_B200_FOLD_ROPE", "1") != "0"   # 0: the r
 def decode_takes_rope(B: int, d: int, page_size: int) -> bool:
     """Whether a decode step of these sizes goes to the kernel that can do bias, rotation and the page write of the
     step's own tokens itself (the TMA decode kernel, as `decode` picks it)."""
-    return FOLD_ROPE and TMA_DECODE and B >= 4 and d % 64 == 0 and 8 <= page_size <= 64 and page_size & (page_size - 1) == 0
+    return FOLD_ROPE and TMA_DECODE and B >= TMA_DECODE_MIN_BATCH and d % 64 == 0 and 8 <= page_size <= 64 and page_size & (page_size - 1) == 0
 
 
 def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
@@ -235,7 +236,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
     runs the rotary kernel instead, for the case that the library turns the launch down."""
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
-    use_tma = (TMA_DECODE and B >= 4 if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
+    use_tma = (TMA_DECODE and B >= TMA_DECODE_MIN_BATCH if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
     if rope is not None and not use_tma:
         raise KernelError("attn_decode: the rotary step folds into the TMA kernel only")
     can_cluster = use_tma and 2 <= splits <= 8 and nq // nkv <= 16
