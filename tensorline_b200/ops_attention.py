@@ -246,8 +246,9 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
             raise KernelError("attn_decode: part_o must be float32 [B, nq, splits, d]")
         if part_ml is None or part_ml.numel() < B * nq * splits * 2 or part_ml.dtype != torch.float32:
             raise KernelError("attn_decode: part_ml must be float32 [B, nq, splits, 2]")
-    # measured at 7B sizes: TMA loads win from about four requests on (5.8 against 5.4 TB/s at batch 64);
-    # below that the launch is too short for the difference to show and the tensor-map set-up costs a little
+    # measured at 7B sizes: TMA loads win at batch 64 (5.8 against 5.4 TB/s); with fewer requests the loads themselves
+    # make no difference, but the TMA kernel can take the rotary step in and start its loads before the kernel in
+    # front has finished (batch 1: 2.85 -> 2.80 ms a step)
     if use_tma:
         from .ops_gemm import status_word
         args = (_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
