@@ -121,10 +121,11 @@ __device__ __forceinline__ void rope_pairs(const bf16* row, const void* bias, in
             a[k] = ra; b[k] = rb;
         }
     }
-    __nv_bfloat162* lo2 = reinterpret_cast<__nv_bfloat162*>(&lo);
-    __nv_bfloat162* hi2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+    uint32_t pa[4], pb[4];                                // by value: the results stay in registers at the caller
 #pragma unroll
-    for (int k = 0; k < 4; ++k) { lo2[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]); hi2[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]); }
+    for (int k = 0; k < 4; ++k) { pa[k] = pack_bf16(a[2 * k], a[2 * k + 1]); pb[k] = pack_bf16(b[2 * k], b[2 * k + 1]); }
+    lo = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+    hi = make_uint4(pb[0], pb[1], pb[2], pb[3]);
 }
 
 // A [ROWS][DP] tile of keys (or values) of one KV head is filled by 128 threads in chunks of 16

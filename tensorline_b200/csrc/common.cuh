@@ -122,6 +122,12 @@ __device__ __forceinline__ int tl_checked(int v, int limit, const TlLimits& L, i
 }
 TL_EXPORT int tl_check_build();
 
+// silu(g) * u in the bfloat16 engine (g and u hold bfloat16 values): float32 arithmetic with the division that has no
+// special-case branch, so the chains of neighbouring elements overlap (an epilogue of 16 tokens took 2,600 cycles with
+// the exact division, 1,500 with this one).  Every bfloat16 path of the activation calls this function and so gives the
+// same bits; the 32-bit engine divides exactly.
+__device__ __forceinline__ float tl_silu_mul(float g, float u) { return __fdividef(g, 1.0f + expf(-g)) * u; }
+
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while
 // the kernel before it in the stream is still running; its blocks run their set-up and then stop in
 // grid_dependency_wait() until that kernel has finished and its writes are visible.  Every kernel launched

@@ -221,7 +221,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
         const int gc = (c / blk) * 2 * blk + c % blk;
         const float g = to_f<TA>(gu[t * 2 * I + gc]);
         const float u = to_f<TA>(gu[t * 2 * I + gc + blk]);
-        out[idx] = from_f<TA>((g / (1.0f + expf(-g))) * u);
+        if constexpr (sizeof(TA) == 4) out[idx] = (g / (1.0f + expf(-g))) * u;     // the 32-bit engine: exact division
+        else                           out[idx] = from_f<TA>(tl_silu_mul(g, u));
     }
 }
 
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restri
         for (int e = 0; e < 4; ++e) {
             const float g0 = __low2float(g2[e]), g1 = __high2float(g2[e]);
             const float u0 = __low2float(u2[e]), u1 = __high2float(u2[e]);
-            o2[e] = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+            o2[e] = __floats2bfloat162_rn(tl_silu_mul(g0, u0), tl_silu_mul(g1, u1));
         }
         *reinterpret_cast<uint4*>(out + t * I + cs[k]) = ov;
     }

@@ -107,6 +107,11 @@ __device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
     return reinterpret_cast<const float*>(out);
 }
 
+// silu(gate) * up of two accumulator values, each rounded to bfloat16 first (as a stored gate|up product would have been).
+__device__ __forceinline__ float silu_mul_rounded(float gate, float up) {
+    return tl_silu_mul(__bfloat162float(__float2bfloat16_rn(gate)), __bfloat162float(__float2bfloat16_rn(up)));
+}
+
 struct GemmArgs {
     void* out;            // bf16 or float [rows, ldo]
     float* partial;       // [splits, RB or RA rows..] float, when splits > 1
@@ -342,32 +347,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld16(taddr + c0, r);
                 if (a >= G.RA && !G.gated && !G.cluster_reduce) continue;
                 if (G.gated) {
-                    // The up half (TMEM lanes 64..127) hands its values over through shared memory (the tile ring is
-                    // idle by now); the gate half rounds both to bfloat16 as a stored gate|up product would have
-                    // been, and writes silu(gate) * up.
-                    float* hand = reinterpret_cast<float*>(tiles);                   // [16 tokens][64 features]
+                    // A feature's gate value sits in TMEM lane f, its up value in lane 64 + f: two threads.  They share the
+                    // step's tokens: the up thread hands its values of the first half over through shared memory (the tile
+                    // ring is idle by now), the gate thread its values of the second half; each rounds both to bfloat16 as
+                    // a stored gate|up product would have been and writes silu(gate) * up for its half of the tokens.
+                    float* hand = reinterpret_cast<float*>(tiles) + ((c0 >> 4) & 1) * (16 * 64);   // [16 tokens][64 features], two in turn
                     const int f = (quarter & 1) * 32 + lane;
-                    if (quarter >= 2) {
+                    const bool up_side = quarter >= 2;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) hand[j * 64 + f] = __uint_as_float(r[j]);
-                    }
+                    for (int j = 0; j < 8; ++j) hand[(up_side ? j : 8 + j) * 64 + f] = __uint_as_float(up_side ? r[j] : r[8 + j]);
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (quarter < 2) {
-                        const int col = blockIdx.x * 64 + f;                       // feature of the output
-                        if (col < (G.RA >> 1)) {
+                    const int col = blockIdx.x * 64 + f;                           // feature of the output
+                    float res[8];                        // no branch in here: the eight tokens' chains overlap
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const int b = b0 + c0 + j;
-                                if (b < G.RB) {
-                                    const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j])));
-                                    const float u = __bfloat162float(__float2bfloat16_rn(hand[j * 64 + f]));
-                                    ((bf16*)G.out)[(size_t)b * G.ldo + col] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
-                                }
-                            }
-                        }
+                    for (int j = 0; j < 8; ++j) {
+                        const int t = up_side ? 8 + j : j;
+                        const float mine = __uint_as_float(up_side ? r[8 + j] : r[j]), other = hand[t * 64 + f];
+                        res[j] = silu_mul_rounded(up_side ? other : mine, up_side ? mine : other);
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");                   // `hand` is free for the next 16 tokens
-                    continue;
+                    if (col < (G.RA >> 1)) {
+                        bf16* dst = (bf16*)G.out + (size_t)(b0 + c0 + (up_side ? 8 : 0)) * G.ldo + col;
+                        const int left = G.RB - (b0 + c0 + (up_side ? 8 : 0));
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (j < left) dst[(size_t)j * G.ldo] = __float2bfloat16_rn(res[j]);
+                    }
+                    continue;                            // the next 16 tokens use the other buffer: no second barrier
                 }
                 if (G.cluster_reduce) {                  // [token][128 rows of A] floats in the idle tile ring
                     float* red = reinterpret_cast<float*>(tiles);
@@ -459,12 +464,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int lo = split * share, hi = min(total, lo + share);
             // four rows of A a thread and step (shares and BM are multiples of 4): one 16-byte load a peer
             const bool wide = (G.ldo & 3) == 0 && (((uintptr_t)G.out) & 15) == 0;
+            const float* peer[8];                        // the tile of every block of the cluster
+#pragma unroll
+            for (int z = 0; z < 8; ++z) peer[z] = cluster_peer(red, z < nz ? z : 0);
             for (int idx = lo + 4 * ((int)threadIdx.x - 64); idx < hi; idx += 4 * 128) {
+                float4 v[8];                             // all loads are on their way before the first addition
+#pragma unroll
+                for (int z = 0; z < 8; ++z)
+                    if (z < nz) v[z] = *reinterpret_cast<const float4*>(peer[z] + idx);
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int z = 0; z < nz; ++z) {
-                    const float4 v = *reinterpret_cast<const float4*>(cluster_peer(red + idx, z));
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
+#pragma unroll
+                for (int z = 0; z < 8; ++z)
+                    if (z < nz) { acc.x += v[z].x; acc.y += v[z].y; acc.z += v[z].z; acc.w += v[z].w; }
                 const int tok = idx / BM, a = a0 + (idx - tok * BM);
                 if (G.res_x) {
                     // x += the sums rounded to bfloat16 (what the addend would have been stored as); the sum of squares of the

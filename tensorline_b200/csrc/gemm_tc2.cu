@@ -249,7 +249,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             for (int j = 0; j < 16; ++j) {
                                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[j])));
                                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[j])));
-                                v[j] = (g / (1.0f + expf(-g))) * u;
+                                v[j] = tl_silu_mul(g, u);
                             }
                             store16_bf16((bf16*)G.out + (size_t)t * G.ldo + col, v, (G.N >> 1) - col);
                         }
