@@ -89,10 +89,10 @@ struct AttnArgs {
 
 // Eight values at i0.. and the eight at D/2 + i0.. of one head's row: + bias, rotated (rotate-half pairs, angle of pair i in
 // cs[i] = cos, cs[D/2 + i] = sin) unless `rotate` is false, rounded to bfloat16.  The arithmetic of rope_kv_vec_kernel.
-__device__ __forceinline__ void rope_pairs(const bf16* row, const void* bias, int bias_f32, int bias_off, int i0, const float* cs,
+// av, bv: the sixteen values as loaded (the caller issues the loads of all its items before it works on the first).
+__device__ __forceinline__ void rope_pairs(const uint4 av, const uint4 bv, const void* bias, int bias_f32, int bias_off, int i0, const float* cs,
                                            bool rotate, uint4& lo, uint4& hi) {
     constexpr int half = HEAD_DIM / 2;
-    const uint4 av = *reinterpret_cast<const uint4*>(row + i0), bv = *reinterpret_cast<const uint4*>(row + half + i0);
     const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
     const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
     float a[8], b[8];
@@ -396,7 +396,7 @@ constexpr int DEC_STAGES = TL_DEC_STAGES;
 constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
 constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
 constexpr int DECODE_TAB_OFFSET = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
-constexpr int DECODE_MAX_TAB = 2048;                    // table entries a block may copy (8 KB)
+constexpr int DECODE_MAX_TAB = 1536;                    // table entries a block may copy (6 KB: head size 256 leaves no more)
 
 // grid (splits * m_tiles, nkv, B); 4 warps; each stage is 64 keys, 16 per warp.
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
@@ -542,14 +542,20 @@ constexpr int TMA_TILE_BYTES = BN * D * 2;                       // K or V of on
 constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
 constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
 constexpr int TMA_CS_OFFSET = TMA_BAR_OFFSET + 128;              // room for 2 * DEC_STAGES barriers and a flag; then cos, sin [D]
-constexpr int TMA_TAB_OFFSET = TMA_CS_OFFSET + D * 4;
+// Where the other blocks of a cluster put their shares of this block's columns (CLUSTER): [key range][16 rows][columns of this
+// block] floats, at most 16 (D + 8) in all, then (m, l) [key range][16 rows].  Not in the stage buffers: a block that has
+// finished writes here while this one may still be loading keys.
+constexpr int TMA_RECV_OFFSET = TMA_CS_OFFSET + D * 4;
+constexpr int TMA_RECV_ML = 16 * (D + 8) * 4;
+constexpr int TMA_TAB_OFFSET = TMA_RECV_OFFSET + TMA_RECV_ML + 8 * 16 * 2 * 4;
 #ifndef TL_TMA_COPY_WARPS
 #define TL_TMA_COPY_WARPS 2
 #endif
 constexpr int TMA_COPY_WARPS = TL_TMA_COPY_WARPS;
 constexpr int TMA_DEC_THREADS = 128 + 32 * TMA_COPY_WARPS;       // four compute warps and the copy warps
 static_assert(2 * DEC_STAGES * 8 + 8 <= 128, "the barrier area holds at most 7 stages");
-constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM) ? 1 : 0;
+constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM + 6 * 16 * 4) ? 1 : 0;
+static_assert(TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024 <= 227 * 1024, "the decode block does not fit an SM's shared memory");
 static_assert(TMA_MERGE_OK == 1, "the stage buffers must hold the merge area");
 constexpr long long TMA_WAIT_CYCLES = 4000000000LL;
 
@@ -583,10 +589,10 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");   // not .aligned: lanes of a warp may arrive apart
 }
 // The same shared-memory location in block `rank` of this cluster.
-__device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
+__device__ __forceinline__ float* cluster_peer_rw(float* p, int rank) {
     uint64_t out;
     asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"(reinterpret_cast<uint64_t>(p)), "r"(rank));
-    return reinterpret_cast<const float*>(out);
+    return reinterpret_cast<float*>(out);
 }
 
 // CLUSTER: the blocks of one (request, KV head) - one per key range - form a thread-block cluster and merge their
@@ -639,12 +645,31 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // front writes (what is in them is from earlier steps, whose kernels have all finished before this one may start): the
     // copy warps then request the first stages at once, while the kernel in front is still at its last tiles.
     const bool early = fold && A.rope_write;
-    __syncthreads();                                       // table copy and barriers are visible
+    float* cs = reinterpret_cast<float*>(tiles + TMA_CS_OFFSET);
+    if (warp < 4 && fold) {                                // the token's angles, once for all its heads: positions and
+        for (int i = tid; i < D / 2; i += 128) {           // frequencies are not the kernel in front's, so before the wait
+            float sn, c;
+            sincosf(__fmul_rn((float)pos, A.rope_inv_freq[i]), &sn, &c);
+            cs[i] = c; cs[D / 2 + i] = sn;
+        }
+    }
+    __syncthreads();                                       // table copy, barriers and angles are visible
+    // The token's own key and value: made by the block whose range holds its position, written to their page by one of the
+    // blocks of that range (the first row tile), and kept in registers to be put into this block's tiles when that stage
+    // has landed (the page in memory still holds what was there before).
+    const bool has_new = fold && A.rope_write && n_stage > 0 && pos >= k_begin && pos < k_end;
+    const int st_new = has_new ? (pos - k_begin) / BN : -1, r_new = (pos - k_begin) % BN;
+    uint4 new_lo = make_uint4(0, 0, 0, 0), new_hi = new_lo;
+    int new_i0 = -1, new_is_v = 0;
+    if (has_new && warp < 4) {
+        constexpr int PER = D / 16;
+        if (tid >= 64 && tid < 64 + PER) { new_i0 = (tid - 64) * 8; new_is_v = 0; }
+        else if (tid >= 96 && tid < 96 + PER) { new_i0 = (tid - 96) * 8; new_is_v = 1; }
+    }
     if (warp < 4 || !early) {
         grid_dependency_wait();                            // queries and the newest keys and values: the kernel before
         grid_dependency_trigger();
     }
-    float* cs = reinterpret_cast<float*>(tiles + TMA_CS_OFFSET);
     if (warp < 4 && !fold) {
         for (int idx = tid; idx < 16 * CH; idx += 128) {
             const int r = idx / CH, c = idx - r * CH;
@@ -657,38 +682,28 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         cp_async_commit();
     }
     if (warp < 4 && fold) {
-        for (int i = tid; i < D / 2; i += 128) {           // the token's angles, once for all its heads
-            float sn, c;
-            sincosf(__fmul_rn((float)pos, A.rope_inv_freq[i]), &sn, &c);
-            cs[i] = c; cs[D / 2 + i] = sn;
+        // the loads of the new key's or value's item go out before the query items are worked on: one round trip, not two
+        const int new_col = (A.nq + (new_is_v ? A.nkv : 0) + kh) * D;
+        uint4 nav = make_uint4(0, 0, 0, 0), nbv = nav;
+        if (new_i0 >= 0) {
+            const bf16* nrow = A.q + (size_t)qrow * A.q_stride + new_col;
+            nav = *reinterpret_cast<const uint4*>(nrow + new_i0); nbv = *reinterpret_cast<const uint4*>(nrow + D / 2 + new_i0);
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
         constexpr int PER = D / 16;                        // items of 8 + 8 values a head
         for (int item = tid; item < 16 * PER; item += 128) {
             const int r = item / PER, i0 = (item - r * PER) * 8, hg = mt * 16 + r;
             uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
             if (hg < g) {
                 const int head = kh * g + hg;
-                rope_pairs(A.q + (size_t)qrow * A.q_stride + (size_t)head * D, A.rope_bias, A.rope_bias_f32, head * D, i0, cs, true, lo, hi);
+                const bf16* row = A.q + (size_t)qrow * A.q_stride + (size_t)head * D;
+                rope_pairs(*reinterpret_cast<const uint4*>(row + i0), *reinterpret_cast<const uint4*>(row + D / 2 + i0),
+                           A.rope_bias, A.rope_bias_f32, head * D, i0, cs, true, lo, hi);
             }
             *reinterpret_cast<uint4*>(sQ + r * DP + i0) = lo;
             *reinterpret_cast<uint4*>(sQ + r * DP + D / 2 + i0) = hi;
         }
-    }
-    // The token's own key and value: made by the block whose range holds its position, written to their page by one of the
-    // blocks of that range (the first row tile), and kept in registers to be put into this block's tiles when that stage
-    // has landed (the page in memory still holds what was there before).
-    const bool has_new = fold && A.rope_write && n_stage > 0 && pos >= k_begin && pos < k_end;
-    const int st_new = has_new ? (pos - k_begin) / BN : -1, r_new = (pos - k_begin) % BN;
-    uint4 new_lo = make_uint4(0, 0, 0, 0), new_hi = new_lo;
-    int new_i0 = -1, new_is_v = 0;
-    if (has_new && warp < 4) {
-        constexpr int PER = D / 16;
-        if (tid >= 64 && tid < 64 + PER) { new_i0 = (tid - 64) * 8; new_is_v = 0; }
-        else if (tid >= 96 && tid < 96 + PER) { new_i0 = (tid - 96) * 8; new_is_v = 1; }
         if (new_i0 >= 0) {
-            const int col = (A.nq + (new_is_v ? A.nkv : 0) + kh) * D;
-            rope_pairs(A.q + (size_t)qrow * A.q_stride + col, A.rope_bias, A.rope_bias_f32, col, new_i0, cs, !new_is_v, new_lo, new_hi);
+            rope_pairs(nav, nbv, A.rope_bias, A.rope_bias_f32, new_col, new_i0, cs, !new_is_v, new_lo, new_hi);
             if (mt == 0) {
                 const int page = stab[pos / A.page_size - first_page];
                 bf16* dst = (new_is_v ? A.v_pages_w : A.k_pages_w) + (((size_t)page * A.nkv + kh) * A.page_size + pos % A.page_size) * D;
@@ -727,7 +742,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         __syncthreads();                                   // meets the compute warps after their last stage
         __syncthreads();                                   // and after they have laid out their partial results
-        if (CLUSTER) { cluster_barrier(); cluster_barrier(); }
+        if (CLUSTER) cluster_barrier();                    // every thread of the cluster takes part in its barrier
         return;
     }
     cp_async_wait<0>();
@@ -792,70 +807,91 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     __syncthreads();                                       // the stage buffers become the merge area
     if (*abort_flag) {
         __syncthreads();
-        if (CLUSTER) { cluster_barrier(); cluster_barrier(); }     // the others must not wait for this block for ever
+        if (CLUSTER) cluster_barrier();                    // the others must not wait for this block for ever
         return;
     }
 
-    float* mO = reinterpret_cast<float*>(tiles);           // [4][16][D]
+    float* mO = reinterpret_cast<float*>(tiles);           // [4][16][D]   every warp's part (its 16 keys of every stage)
     float* mML = mO + 4 * 16 * D;                          // [4][16][2]
-    float* bO = mML + 4 * 16 * 2;                          // [16][D]   the block's own result, read by its cluster
-    float* bML = bO + 16 * D;                              // [16][2]
+    float* sF = mML + 4 * 16 * 2;                          // [4][16]      a warp's weight in the block's result
+    float* sMM = sF + 4 * 16;                              // [16]         the block's running maximum and sum
+    float* sLT = sMM + 16;                                 // [16]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float lr = l[r];
         lr += __shfl_xor_sync(0xffffffffu, lr, 1);
         lr += __shfl_xor_sync(0xffffffffu, lr, 2);
         const int row = (lane >> 2) + r * 8;
+        if (mt * 16 + row >= g) continue;                  // a row beyond the group: nothing reads it
         if ((lane & 3) == 0) { mML[(warp * 16 + row) * 2] = m[r]; mML[(warp * 16 + row) * 2 + 1] = lr; }
 #pragma unroll
         for (int nb = 0; nb < D / 8; ++nb) {
             float* dst = mO + (warp * 16 + row) * D + nb * 8 + (lane & 3) * 2;
-            dst[0] = o[nb][2 * r]; dst[1] = o[nb][2 * r + 1];
+            *reinterpret_cast<float2*>(dst) = make_float2(o[nb][2 * r], o[nb][2 * r + 1]);
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < 16 * D; idx += 128) {
-        const int row = idx / D, col = idx - row * D;
-        const int hg = mt * 16 + row;
-        if (hg >= g) continue;
+    if (tid < 16 && mt * 16 + tid < g) {                   // the four warps' weights, once a row
+        const int row = tid;
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) mm = fmaxf(mm, mML[(w * 16 + row) * 2]);
-        float acc = 0.f, lt = 0.f;
+        float lt = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = mML[(w * 16 + row) * 2];
             const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
-            acc += f * mO[(w * 16 + row) * D + col];
+            sF[w * 16 + row] = f;
             lt += f * mML[(w * 16 + row) * 2 + 1];
         }
-        const int head = kh * g + hg;
+        sMM[row] = mm; sLT[row] = lt;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int ns = A.splits, cpc = (D + ns - 1) / ns;      // CLUSTER: block s finishes columns [s * cpc, + cpc)
+    float* recvO = reinterpret_cast<float*>(tiles + TMA_RECV_OFFSET);
+    float* recvML = reinterpret_cast<float*>(tiles + TMA_RECV_OFFSET + TMA_RECV_ML);
+    const int rows = min(16, g - mt * 16);
+    for (int col = tid; col < D; col += 128) {             // a column a thread: the block's result, sent where it is finished
+        float* dst_o = nullptr;
         if (CLUSTER) {
-            bO[row * D + col] = acc;
-            if (col == 0) { bML[row * 2] = mm; bML[row * 2 + 1] = lt; }
-        } else if (A.splits == 1) {
-            A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
-        } else {
-            const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
-            A.part_o[pi * D + col] = acc;
-            if (col == 0) { A.part_ml[pi * 2] = mm; A.part_ml[pi * 2 + 1] = lt; }
+            const int owner = col / cpc;
+            dst_o = cluster_peer_rw(recvO + (split * 16) * cpc + (col - owner * cpc), owner);
+        }
+        for (int row = 0; row < rows; ++row) {
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) acc += sF[w * 16 + row] * mO[(w * 16 + row) * D + col];
+            const int head = kh * g + mt * 16 + row;
+            if (CLUSTER) {
+                dst_o[row * cpc] = acc;
+            } else if (A.splits == 1) {
+                const float lt = sLT[row];
+                A.out[((size_t)qrow * A.nq + head) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
+            } else {
+                const size_t pi = ((size_t)b * A.nq + head) * A.splits + split;
+                A.part_o[pi * D + col] = acc;
+                if (col == 0) { A.part_ml[pi * 2] = sMM[row]; A.part_ml[pi * 2 + 1] = sLT[row]; }
+            }
         }
     }
     if (CLUSTER) {
-        cluster_barrier();                                 // every block's result is in its shared memory
-        const int ns = A.splits, cpc = (D + ns - 1) / ns;  // this block finishes columns [split * cpc, + cpc)
-        for (int idx = tid; idx < g * cpc; idx += 128) {
-            const int row = idx / cpc, col = split * cpc + (idx - row * cpc);
+        if (tid < ns * 16 && (tid & 15) < rows) {          // (m, l) of every row to every block
+            const int owner = tid >> 4, row = tid & 15;
+            float* dst = cluster_peer_rw(recvML + (split * 16 + row) * 2, owner);
+            dst[0] = sMM[row]; dst[1] = sLT[row];
+        }
+        cluster_barrier();                                 // all shares have arrived; nobody touches another block's memory after this
+        for (int idx = tid; idx < rows * cpc; idx += 128) {
+            const int row = idx / cpc, c = idx - row * cpc, col = split * cpc + c;
             if (col >= D) continue;
             float ms[8], ls[8], os[8];
             float mm = -INFINITY;
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp) {
                 if (sp < ns) {
-                    const float2 ml = *reinterpret_cast<const float2*>(cluster_peer(bML + row * 2, sp));
-                    ms[sp] = ml.x; ls[sp] = ml.y;
-                    os[sp] = *cluster_peer(bO + row * D + col, sp);
-                    mm = fmaxf(mm, ml.x);
+                    ms[sp] = recvML[(sp * 16 + row) * 2]; ls[sp] = recvML[(sp * 16 + row) * 2 + 1];
+                    os[sp] = recvO[(sp * 16 + row) * cpc + c];
+                    mm = fmaxf(mm, ms[sp]);
                 }
             }
             float acc = 0.f, lt = 0.f;
@@ -868,7 +904,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             A.out[((size_t)qrow * A.nq + kh * g + row) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
         }
-        cluster_barrier();                                 // nobody leaves while its shared memory is still read
     }
 }
 #endif  // HEAD_DIM % 64 == 0

@@ -268,6 +268,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------------------------------------------------------- TMA producer
         // The weights are nobody's output: the first ring of weight tiles is requested before the wait for the
         // kernel that writes the activations, so the stream from memory is already running when that kernel ends.
+        // the activations' descriptor is first used after the wait: fetched now, that round trip is off the critical path
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         const int ahead = (n_kt < STAGES ? n_kt : STAGES) - ((G.drop_last_load && n_kt <= STAGES) ? 1 : 0);
         const uint32_t tx_bytes = made_b ? A_BYTES : STAGE_BYTES;      // made: the epilogue warps write the B tiles
         const int w_elem = G.nw_f32 ? 4 : 2;

@@ -19,7 +19,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _libs: dict = {}
 
 KEY_TILE = 64
-DECODE_MAX_TABLE_ENTRIES = 2048     # block-table entries a decode block copies to shared memory (`tl_attn_decode_max_table`)
+DECODE_MAX_TABLE_ENTRIES = 1536     # block-table entries a decode block copies to shared memory (`tl_attn_decode_max_table`)
 TC_PREFILL = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: mma.sync attention only (A/B timing)
 
 
