@@ -148,12 +148,28 @@ struct GemmArgs {
 constexpr int RAW_W_BYTES = 256;                                         // 64 norm weights of a stage, float at most
 template <int BN> __host__ __device__ constexpr int raw_stage_bytes() { return BN * BK * 4 + RAW_W_BYTES; }
 
+// Whether the partial sums of squares of this block's tokens go to shared memory by one bulk copy (16-byte rules, and room
+// in one operand tile of BN x 64 bfloat16).
+template <int BN>
+__device__ __forceinline__ bool ssq_in_smem(const GemmArgs& G, int b0) {
+    const int n = min(BN, G.RB - b0) * G.nparts;
+    return (n & 3) == 0 && n * 4 <= BN * BK * 2 && ((reinterpret_cast<uintptr_t>(G.nssq + (size_t)b0 * G.nparts)) & 15) == 0;
+}
+
 template <int BN, int STAGES>
 __device__ __forceinline__ void make_b_tiles(const GemmArgs& G, unsigned char* tiles, unsigned char* raw, uint64_t* full_bar,
-                                             uint64_t* raw_bar, float* rstd_s, volatile int* abort_flag, int b0, int kt_begin, int n_kt) {
+                                             uint64_t* raw_bar, uint64_t* ssq_bar, float* rstd_s, volatile int* abort_flag, int b0, int kt_begin, int n_kt) {
     constexpr int A_BYTES = BM * BK * 2, STAGE_BYTES = A_BYTES + BN * BK * 2, RAW_BYTES = raw_stage_bytes<BN>();
     constexpr int CHUNKS = BN * 8 / 128 > 0 ? BN * 8 / 128 : 1;          // 16-byte chunks of the tile a thread writes
     const int e = (int)threadIdx.x - 64;                                 // 0..127
+    // The partial sums of squares: every block of the launch wants the same few hundred bytes at the same moment, and
+    // ordinary loads of such lines take two microseconds where a bulk copy takes one (measured with time stamps).  Where
+    // they fit, the copy thread has brought them into the operand tile of the last stage, which nothing writes before here.
+    const float* ssq_s = nullptr;
+    if (ssq_in_smem<BN>(G, b0)) {
+        if (!mbar_wait(ssq_bar, 0, abort_flag, G.status, 4, G.wait_cycles)) return;
+        ssq_s = reinterpret_cast<const float*>(tiles + (STAGES - 1) * STAGE_BYTES + A_BYTES);
+    }
     // rstd of every token: eight lanes a token, each sums the partial sums p = lane, lane + 8, ... (loads independent of one
     // another), then the eight are added in a fixed order
     for (int t0 = 0; t0 < BN; t0 += 16) {
@@ -161,7 +177,7 @@ __device__ __forceinline__ void make_b_tiles(const GemmArgs& G, unsigned char* t
         float ss = 0.f;
         const bool live = tl < BN && b < G.RB;
         if (live) {
-            const float* src = G.nssq + (size_t)b * G.nparts;
+            const float* src = ssq_s ? ssq_s + (size_t)tl * G.nparts : G.nssq + (size_t)b * G.nparts;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             int p = l8;
             for (; p + 24 < G.nparts; p += 32) { s0 += src[p]; s1 += src[p + 8]; s2 += src[p + 16]; s3 += src[p + 24]; }
@@ -232,7 +248,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* done_bar = empty_bar + STAGES;
     uint64_t* raw_bar = done_bar + 1;                    // [STAGES] the stage's raw material has landed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_bar + STAGES);
+    uint64_t* ssq_bar = raw_bar + STAGES;                // the partial sums of squares have landed (made B operand)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ssq_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* last_flag = abort_flag + 1;
     float* rstd_s = reinterpret_cast<float*>(const_cast<int*>(last_flag) + 1);      // [BN] with a made B operand
@@ -248,6 +265,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, made_b ? 2 : 1); mbar_init(empty_bar + s, 1); mbar_init(raw_bar + s, 1); }
         mbar_init(done_bar, 1);
+        mbar_init(ssq_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -290,6 +308,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         grid_dependency_wait();
         grid_dependency_trigger();
+        if constexpr (BN <= 64) {
+            if (made_b && ssq_in_smem<BN>(G, b0)) {
+                const uint32_t bytes = (uint32_t)(min(BN, G.RB - b0) * G.nparts * 4);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(ssq_bar)), "r"(bytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_addr(tiles + (STAGES - 1) * STAGE_BYTES + A_BYTES)), "l"(G.nssq + (size_t)b0 * G.nparts), "r"(bytes),
+                               "r"(smem_addr(ssq_bar)) : "memory");
+            }
+        }
         for (int i = 0; i < ahead; ++i) {
             unsigned char* st = tiles + i * STAGE_BYTES;
             if (made_b)      load_raw(i, kt_begin + i);
@@ -336,7 +363,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
         if constexpr (BN <= 64) {                        // the few-token order only
-            if (made_b) make_b_tiles<BN, STAGES>(G, tiles, raw, full_bar, raw_bar, rstd_s, abort_flag, b0, kt_begin, n_kt);
+            if (made_b) make_b_tiles<BN, STAGES>(G, tiles, raw, full_bar, raw_bar, ssq_bar, rstd_s, abort_flag, b0, kt_begin, n_kt);
         }
         if (mbar_wait(done_bar, 0, abort_flag, G.status, 3, G.wait_cycles)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -611,7 +638,7 @@ int g_drop_last_load = 0;
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3 grid, cudaStream_t stream) {
     constexpr int RAW = BN <= 64 ? STAGES * raw_stage_bytes<BN>() : 0;
-    constexpr int SMEM_PLAIN = STAGES * (BM + BN) * BK * 2 + 1024 + (3 * STAGES + 1) * 8 + 32 + BN * 4;
+    constexpr int SMEM_PLAIN = STAGES * (BM + BN) * BK * 2 + 1024 + (3 * STAGES + 2) * 8 + 32 + BN * 4;
     constexpr int SMEM_MAX = SMEM_PLAIN + RAW;
     const int SMEM = SMEM_PLAIN + (G.nx != nullptr ? RAW : 0);
     static bool attr_set[TL_MAX_DEVICES] = {};
