@@ -298,7 +298,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope)
     else:
         g = nq // nkv
-        singles = _single_token_requests(ctx, qkv.device, g)
+        singles = _single_token_requests(ctx, qkv.device, g, nkv)
         skip = singles["set"] if singles else frozenset()
         if singles:
             # the single decoded tokens of a mixed step: the decode kernel cuts their keys into ranges, where a
@@ -314,16 +314,20 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                    singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
         rest = [i for i in range(ctx.B) if i not in skip]
         rest_rows = sum(ctx.h_q_start[i + 1] - ctx.h_q_start[i] for i in rest) * g
-        # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05; steps of mostly
-        # single tokens (a few decoded tokens beside a short portion) keep the 64-row mma.sync tiles.
-        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and rest_rows >= 96 * len(rest)
+        # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05, and so do steps with a
+        # portion of a thousand rows or more whatever else is beside it (a 464-token portion beside 48 single tokens,
+        # 14B head counts: 129 against 169 us); steps of mostly single tokens beside a short portion keep the 64-row
+        # mma.sync tiles.
+        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and \
+            (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE)
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
-        # Two query tiles a block pay once its blocks (one per SM) fill most of the GPU; below that the one-tile
-        # kernel has twice as many blocks to spread (measured at 7B sizes: 2,048 new tokens 45 against 71 us,
-        # 4,096 140 against 219 us, 1,024 on 3,072 cached (112 blocks of pairs) 78 against 116 us, 1,024 alone 27
-        # against 27 us; 512 tokens on 3,584 cached, 56 blocks of pairs, 76 against 69 us)
-        pairs = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in rest)
+        # Two query tiles a block pay as soon as the one-tile kernel's blocks (one an SM) would need a second round:
+        # measured at 7B head counts 2,048 new tokens 45 against 71 us, 1,024 on 1,024 cached (224 one-tile blocks) 46
+        # against 58 us, but 512 on 3,584 cached (112 blocks) 76 against 70 us; at 14B head counts 512 on 1,024 cached
+        # (160 blocks) 36 against 47 us, 512 on 3,584 cached 78 against 121 us, 256 on 1,024 cached (80 blocks) 31
+        # against 29 us.
+        one_tile_blocks = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * g // TC_QUERY_TILE) for i in rest) * nkv
 
         def order(rows_per_tile):
             if not TILE_ORDER and not skip:
@@ -332,7 +336,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
             if key not in ctx.scratch:
                 ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, g, rows_per_tile, qkv.device, skip)
             return ctx.scratch[key]
-        if use_tc and TC_PAIR and pairs * nkv >= 0.7 * ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
+        if use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
             return
         if use_tc:
             prefill_tc(*args, order(TC_QUERY_TILE))
@@ -342,17 +346,21 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
 
 SINGLES_MIN_KEYS = int(os.environ.get("TENSORLINE_B200_SINGLES_MIN_KEYS", 768))
 SINGLES_RATIO = float(os.environ.get("TENSORLINE_B200_SINGLES_RATIO", 1.5))
+SINGLES_FILL = float(os.environ.get("TENSORLINE_B200_SINGLES_FILL", 1.6))
 
 
-def _single_token_requests(ctx, device, group: int):
+def _single_token_requests(ctx, device, group: int, nkv: int = 1, sms: int | None = None):
     """The requests of a mixed step that bring one token, if they are worth a launch of the decode kernel: the longest
-    of them reads SINGLES_MIN_KEYS keys or more and SINGLES_RATIO times as many as any other request of the step (a
-    query tile walks its keys alone, so the longest one sets the pace of the portion kernel; measured at 7B sizes,
+    of them reads SINGLES_MIN_KEYS keys or more and either SINGLES_RATIO times as many as any other request of the step
+    (a query tile walks its keys alone, so the longest one sets the pace of the portion kernel; measured at 7B sizes,
     a layer: 7 x 4,000 cached beside 2,041 new tokens 66 against 83 us, 3 x 8,000 beside 509 33 against 156 us, 31
     x 1,000 beside 481 30 against 35 us, but 3,000 / 2,000 / 500 beside 2,045 66 against 62 us and 7 x 4,000 beside
-    2,041 on 2,048 cached 122 against 115 us).  {"set", "rows", "start_pos", "slots", "span"} with device tensors,
+    2,041 on 2,048 cached 122 against 115 us), or there are so many of them that their (request, KV head) pairs fill
+    the GPU SINGLES_FILL times over: the decode kernel streams keys faster than a query tile with one token in it
+    (a 464-token portion beside 48 single tokens at 1,500 keys, 8 KV heads: 105 against 129 us; beside 16: 80 against
+    72; 4 KV heads, 48 single tokens: 82 against 72).  {"set", "rows", "start_pos", "slots", "span"} with device tensors,
     or None.  Computed once a step."""
-    key = ("single_token_requests", group)
+    key = ("single_token_requests", group, nkv)
     if key not in ctx.scratch:
         B = ctx.B
         ones = [b for b in range(B) if ctx.h_q_start[b + 1] - ctx.h_q_start[b] == 1]
@@ -360,7 +368,8 @@ def _single_token_requests(ctx, device, group: int):
         span = max((ctx.h_start_pos[b] + 1 for b in ones), default=0)
         rest_span = max((ctx.h_start_pos[b] + ctx.h_q_start[b + 1] - ctx.h_q_start[b] for b in range(B)
                          if ctx.h_q_start[b + 1] - ctx.h_q_start[b] != 1), default=0)
-        if ones and len(ones) < B and B < 1 << 15 and span >= SINGLES_MIN_KEYS and span >= SINGLES_RATIO * rest_span and \
+        many = len(ones) * nkv >= SINGLES_FILL * (sms or ops.num_sms()) if len(ones) * nkv >= 64 else False
+        if ones and len(ones) < B and B < 1 << 15 and span >= SINGLES_MIN_KEYS and (span >= SINGLES_RATIO * rest_span or many) and \
                 all((ctx.h_q_start[b + 1] - ctx.h_q_start[b]) * group < KEY_TILE << 16 for b in range(B)):
             n = len(ones)
             packed = torch.tensor([ctx.h_q_start[b] for b in ones] + [ctx.h_start_pos[b] for b in ones] +

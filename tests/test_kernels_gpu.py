@@ -462,12 +462,12 @@ def test_single_tokens_of_a_mixed_step_take_the_decode_kernel(case, monkeypatch)
         return out, ctx
 
     out, ctx = run()
-    found = ctx.scratch[("single_token_requests", nq // nkv)]
+    found = ctx.scratch[("single_token_requests", nq // nkv, nkv)]
     assert found is not None and found["set"] == frozenset(b for b, (c, n) in enumerate(reqs) if n == 1)
     assert_close(out.view(T, nq, d), torch.cat(want), "mixed step, single tokens by the decode kernel", **BF16)
     monkeypatch.setattr(ops_attention, "SINGLES_MIN_KEYS", 1 << 30)
     whole, ctx = run()
-    assert ctx.scratch[("single_token_requests", nq // nkv)] is None
+    assert ctx.scratch[("single_token_requests", nq // nkv, nkv)] is None
     assert_close(whole.view(T, nq, d), torch.cat(want), "mixed step, all in the prompt kernel", **BF16)
     single_rows = [q_start[b] for b, (c, n) in enumerate(reqs) if n == 1]
     other = [r for r in range(T) if r not in single_rows]

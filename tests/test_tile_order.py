@@ -51,6 +51,11 @@ def test_which_single_tokens_of_a_mixed_step_leave_the_portion_kernel():
     assert _single_token_requests(_ctx([(300, 1), (0, 100)]), "cpu", 7) is None
     assert _single_token_requests(_ctx([(4000, 1), (3000, 1)]), "cpu", 7) is None
     assert _single_token_requests(_ctx([(4000, 2), (0, 100)]), "cpu", 7) is None
+    # many single tokens beside a portion that reads as many keys: their (request, KV head) pairs fill the GPU 1.6 times over
+    many = [(1500, 1)] * 30 + [(1500, 482)]
+    assert _single_token_requests(_ctx(many), "cpu", 5, nkv=8, sms=148)["set"] == frozenset(range(30))
+    assert _single_token_requests(_ctx(many), "cpu", 7, nkv=4, sms=148) is None
+    assert _single_token_requests(_ctx([(1500, 1)] * 16 + [(1500, 496)]), "cpu", 5, nkv=8, sms=148) is None
 
 
 def test_skipped_requests_get_no_tile():
