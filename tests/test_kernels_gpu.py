@@ -409,6 +409,58 @@ def test_attention_over_a_long_context(window):
             assert_close(out.view(1, nq, d), want1, f"decode over a long cache, {splits} ranges, tma {tma}, cluster {cluster}", **BF16)
 
 
+@pytest.mark.parametrize("nq,nkv,d", [(7, 1, 128), (16, 1, 128), (6, 2, 64), (5, 5, 128), (12, 3, 192)])
+def test_decode_cluster_merge_for_every_number_of_ranges(nq, nkv, d):
+    """The key ranges of a (request, KV head) merged inside a thread-block cluster: every block sends its share of each
+    column range to the block that finishes it.  2 to 8 ranges (column ranges that do not divide the head size among
+    them), groups of 1 to 16 heads, and beside the long request a short one whose later ranges hold no key at all
+    (those blocks send weight zero).  Against the plain formula in float64, and within a last bit of the combine kernel."""
+    from tensorline_b200 import ops_attention, ops_gemm
+    ps, lens = 16, [1030, 70, 517]                                   # keys each request reads (its own token included)
+    B = len(lens)
+    ks = [rnd(n, nkv, d, seed=80 + b, dtype=torch.bfloat16) for b, n in enumerate(lens)]
+    vs = [rnd(n, nkv, d, seed=90 + b, dtype=torch.bfloat16) for b, n in enumerate(lens)]
+    q = rnd(B, nq, d, seed=79, scale=2.0, dtype=torch.bfloat16)
+    k_all, v_all = torch.cat(ks), torch.cat(vs)
+    num_pages = sum(-(-n // ps) for n in lens) + 9
+    # requests laid out one after the other in token order, their pages scattered over the pool
+    gen = torch.Generator().manual_seed(11)
+    perm = torch.randperm(num_pages, generator=gen).tolist()
+    kd = torch.zeros(num_pages + 1, nkv, ps, d, dtype=torch.bfloat16)
+    vd = torch.zeros_like(kd)
+    rows, used = [], 0
+    for b, n in enumerate(lens):
+        mine = perm[used:used + -(-n // ps)]
+        used += len(mine)
+        for t in range(n):
+            kd[mine[t // ps], :, t % ps] = ks[b][t]
+            vd[mine[t // ps], :, t % ps] = vs[b][t]
+        rows.append(mine)
+    kd, vd = kd.cuda(), vd.cuda()
+    table = table_tensor(rows, 80, num_pages)
+    want = torch.cat([_plain_attention_rows(q[b:b + 1].double(), ks[b].double(), vs[b].double(), [lens[b] - 1], None) for b in range(B)])
+    qd = q.reshape(B, nq * d).cuda()
+    args = (qd, nq * d, None, kd, vd, table, ps, i32(list(range(B))), i32([n - 1 for n in lens]), i32(list(range(B))))
+    tiles = -(-max(lens) // 64)
+    for ranges in range(2, 9):
+        chunk = -(-tiles // ranges) * 64
+        splits = -(-tiles * 64 // chunk)
+        if not 2 <= splits <= 8:
+            continue
+        po = torch.full((B, nq, splits, d), float("nan"), device="cuda")
+        pml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")
+        outs = []
+        for cluster in (True, False):
+            out = torch.zeros(B, nq * d, dtype=torch.bfloat16, device="cuda")
+            ops_attention.decode(args[0], args[1], out, *args[3:], B, nq, nkv, d, None, d ** -0.5, chunk, splits, po, pml,
+                                 tma=True, cluster=cluster)
+            ops_gemm.check_status()
+            assert_close(out.view(B, nq, d), want, f"{splits} ranges, cluster {cluster}", **BF16)
+            outs.append(out)
+        # the combine kernel multiplies by a reciprocal where the cluster merge divides: a last bit of bfloat16 at most
+        assert_close(outs[0].float(), outs[1].float(), f"{splits} ranges: cluster merge against combine kernel", rtol=2 ** -7, atol=1e-6)
+
+
 @pytest.mark.parametrize("case", [
     # nq, nkv, d, page, (cached, new tokens) a request, window
     (28, 4, 128, 16, [(1500, 1), (0, 300), (1100, 1), (40, 1)], None),      # singles between and around a portion
