@@ -310,8 +310,23 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
             if splits > 1:
                 part_o = torch.empty((n, nq, splits, d), dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty((n, nq, splits, 2), dtype=torch.float32, device=qkv.device)
-            decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
-                   singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+            # The two kernels read the same inputs and write different rows, and neither fills the GPU alone (the
+            # portion's blocks are few and bound by arithmetic, the decode kernel is bound by memory): the decode
+            # kernel goes to a second stream and the step's stream joins it after the portion kernel.
+            joined = None
+            if SINGLES_STREAM and qkv.is_cuda:
+                main, side = torch.cuda.current_stream(qkv.device), _side_stream(qkv.device)
+                ready = torch.cuda.Event()
+                ready.record(main)                         # the step's q, k, v and pages are complete
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
+                           singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
+                    joined = torch.cuda.Event()
+                    joined.record(side)
+            else:
+                decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
+                       singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml)
         rest = [i for i in range(ctx.B) if i not in skip]
         rest_rows = sum(ctx.h_q_start[i + 1] - ctx.h_q_start[i] for i in rest) * g
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05, and so do steps with a
@@ -337,11 +352,25 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                 ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, g, rows_per_tile, qkv.device, skip)
             return ctx.scratch[key]
         if use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
-            return
-        if use_tc:
+            pass
+        elif use_tc:
             prefill_tc(*args, order(TC_QUERY_TILE))
         else:
             prefill(*args, order(KEY_TILE))
+        if singles and joined is not None:
+            torch.cuda.current_stream(qkv.device).wait_event(joined)
+
+
+SINGLES_STREAM = os.environ.get("TENSORLINE_B200_SINGLES_STREAM", "1") != "0"   # 0: both kernels on the step's stream (A/B timing)
+_side_streams: dict = {}
+
+
+def _side_stream(device):
+    """The second stream of `device` for the single tokens of mixed steps (one for the life of the process)."""
+    key = torch.device(device).index
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 SINGLES_MIN_KEYS = int(os.environ.get("TENSORLINE_B200_SINGLES_MIN_KEYS", 768))
