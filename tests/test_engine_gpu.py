@@ -262,3 +262,15 @@ def test_overlapped_decoding_with_sampled_requests_equals_synchronous(tiny_a):
     first = results[True][0][0].index(stop)
     assert outs[True].token_ids == outs[False].token_ids == results[True][0][0][:first]
     assert outs[True].finish_reason == outs[False].finish_reason == "stop"
+
+
+def test_the_smoke_entry_point_passes():
+    """`__graft_entry__.smoke()` is what a deployment check runs first: the tiny model in both precisions against the
+    plain model, then one call of each Blackwell kernel family."""
+    import importlib.util
+    import pathlib
+    path = pathlib.Path(__file__).resolve().parent.parent / "__graft_entry__.py"
+    spec = importlib.util.spec_from_file_location("graft_entry_under_test", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.smoke()
