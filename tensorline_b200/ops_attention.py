@@ -173,7 +173,7 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     whatever else runs, so a request's keys are cut into ranges until the blocks fill the GPU's resident
     slots once (a second, partly filled round would double the time) - but not finer than four tiles a
     range (two when that leaves 64 blocks or fewer), below which the merge of the partials costs more
-    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 4 -> 16, 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1.
+    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 2 to 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1.
     A block copies its range's block-table entries to shared memory, DECODE_MAX_TABLE_ENTRIES at most: a range is
     never longer than that many pages, whatever the rules above say (long contexts on small pages get more ranges)."""
     NUM_SMS = sms or ops.num_sms()
@@ -185,8 +185,11 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     splits = min(fill, max(1, tiles // 4), max_splits)
     if base * splits <= 64:
         splits = min(fill, max(1, tiles // 2), max_splits)
-    if 8 < splits <= 12:
-        splits = 8          # eight ranges merge inside a cluster; measured at batch 8, 8 k to 32 k keys: 27 / 46 / 86 against 30 / 49 / 88 us with nine
+    if 8 < splits <= 16:
+        # eight ranges merge inside a cluster; measured at batch 8, 8 k to 32 k keys: 27 / 46 / 86 against 30 / 49 / 88 us
+        # with nine; at batch 2 and 4, context 4,090, against sixteen ranges and the combine kernel: 2.768 / 2.793 against
+        # 2.782 / 2.861 ms a step
+        splits = 8
     chunk = -(-tiles // splits) * KEY_TILE
     most = max(KEY_TILE, DECODE_MAX_TABLE_ENTRIES * page_size // KEY_TILE * KEY_TILE)
     chunk = min(chunk, most)
