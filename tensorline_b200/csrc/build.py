@@ -87,9 +87,21 @@ def library_path(name: str, sources, defines: dict | None = None, extra_flags=()
     if check:
         name = name + "_chk"
     fname = f"lib{name}_{tag}.so"
-    for d in (CSRC / "_build", Path(tempfile.gettempdir()) / f"tensorline_b200_build_{os.getuid()}"):
-        if (d / fname).is_file():
-            return d / fname, flags, True
+    home = CSRC / "_build"
+    if (home / fname).is_file():
+        return home / fname, flags, True
+    spare = Path(tempfile.gettempdir()) / f"tensorline_b200_build_{os.getuid()}" / fname
+    if spare.is_file():
+        # built while the package's own folder could not be written: move in beside the sources if that is possible
+        # now (a copy of the package then carries its libraries along), else use it where it is
+        try:
+            home.mkdir(parents=True, exist_ok=True)
+            tmp = home / f".{fname}.{os.getpid()}"
+            shutil.copyfile(spare, tmp)
+            os.replace(tmp, home / fname)
+            return home / fname, flags, True
+        except OSError:
+            return spare, flags, True
     return build_dir() / fname, flags, False
 
 
