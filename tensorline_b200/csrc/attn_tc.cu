@@ -504,6 +504,28 @@ __device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap* map, ui
                  ::"r"(dst), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P: one row a lane, two bfloat16 a column) comes from tensor memory.
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t (&u)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
+                   "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
+                   "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
+                   "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+                 : "memory");
+}
+
+// P_TMEM: the softmax does not write P to shared memory but back into the S slot it has just read, as packed bfloat16
+// (32 of the slot's 64 columns), and O += P V takes P as its tensor-memory operand.  A key-tile step then moves 160 KB
+// through shared memory instead of 224 KB (the bound of this kernel: see the notes above).  The S slot of product i is
+// free again when P(i) V is complete, not when the softmax has read S(i): that is what the S issuer then waits for.
+template <bool P_TMEM>
 __global__ void __launch_bounds__(THREADS2, 1)
 attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs A) {
     extern __shared__ unsigned char smem_raw[];
@@ -642,7 +664,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
             m_ref = m_new;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            if (i >= 2) {                                   // the P slot is free once P(i-2) V(i-2) is complete
+            if (!P_TMEM && i >= 2) {                        // the P slot is free once P(i-2) V(i-2) is complete
                 ok = mbar_wait(bar_o + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 3);
                 if (!ok) break;
             }
@@ -652,6 +674,7 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (!ok) break;
             }
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[P_TMEM ? BN / 2 : 1];                // P_TMEM: the row's P, two bfloat16 a column
 #pragma unroll
             for (int j8 = 0; j8 < BN / 8; ++j8) {
                 float p[8];
@@ -660,16 +683,27 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     p[e] = fast_exp2(fmaf(s[j8 * 8 + e], A.scale_log2, -m_use));
                     l4[e & 3] += p[e];
                 }
-                const uint32_t dst = sP + bi * P_BYTES + swz(BM, r, j8);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
-                             "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
+                if constexpr (P_TMEM) {
+                    pk[j8 * 4] = pack_bf16(p[0], p[1]); pk[j8 * 4 + 1] = pack_bf16(p[2], p[3]);
+                    pk[j8 * 4 + 2] = pack_bf16(p[4], p[5]); pk[j8 * 4 + 3] = pack_bf16(p[6], p[7]);
+                } else {
+                    const uint32_t dst = sP + bi * P_BYTES + swz(BM, r, j8);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(p[0], p[1])),
+                                 "r"(pack_bf16(p[2], p[3])), "r"(pack_bf16(p[4], p[5])), "r"(pack_bf16(p[6], p[7])) : "memory");
+                }
                 if (j8 == TURN_AT && in_turns) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(x_mine);
                 }
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            fence_async_proxy();                            // generic-proxy writes of P before the MMA reads them
+            if constexpr (P_TMEM) {
+                static_assert(BN == 64, "one 32-column store holds the row's P");
+                tmem_st32_nowait(s_addr, reinterpret_cast<const uint32_t(&)[32]>(pk));
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            } else {
+                fence_async_proxy();                        // generic-proxy writes of P before the MMA reads them
+            }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar_p + bi);
         }
@@ -717,7 +751,8 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     if (!reads(t, j)) { mbar_arrive(bar_kfree + sl); continue; }
                     const int bi = t * 2 + (i & 1);
                     if (i >= 2) {                           // that S slot is free once the softmax of product i-2 has written its P
-                        ok = mbar_wait(bar_p + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 6, true);
+                        ok = P_TMEM ? mbar_wait(bar_o + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 6, true)   // ... and P(i-2) V has read it there
+                                    : mbar_wait(bar_p + bi, ((i - 2) >> 1) & 1, abort_flag, A.status, 6, true);
                         if (!ok) break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -744,9 +779,14 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t v_addr = sV + sl * V_BYTES, p_addr = sP + bi * P_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k)       // O_t += P V(j)
-                        umma(tmem + O2_COL + t * D, desc_kmajor(p_addr + (k >> 2) * BM * 128 + (k & 3) * 32),
-                             desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BN / 16; ++k) {     // O_t += P V(j)
+                        if constexpr (P_TMEM)
+                            umma_a_tmem(tmem + O2_COL + t * D, tmem + S2_COL + bi * BN + k * 8,
+                                        desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                        else
+                            umma(tmem + O2_COL + t * D, desc_kmajor(p_addr + (k >> 2) * BM * 128 + (k & 3) * 32),
+                                 desc_mnmajor(v_addr + k * 16 * 128, BN * 128), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(bar_o + bi);
                     umma_commit(bar_vfree + sl);
                     ++i;
@@ -823,23 +863,6 @@ constexpr uint32_t TMEM3_COLS = 512;
 constexpr uint32_t S3_COL = 0, O3_COL = QT * BN3;
 static_assert(O3_COL + QT * D <= 512, "S and O of both tiles must fit the tensor memory");
 static_assert(SMEM3_BYTES <= 227 * 1024, "shared memory");
-
-// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P: one row a lane, two bfloat16 a column) comes from tensor memory.
-__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t (&u)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-                 ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]),
-                   "r"(u[8]), "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]),
-                   "r"(u[16]), "r"(u[17]), "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]),
-                   "r"(u[24]), "r"(u[25]), "r"(u[26]), "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
-                 : "memory");
-}
 
 __global__ void __launch_bounds__(THREADS2, 1)
 attn_tc3_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnArgs A) {
@@ -1177,11 +1200,11 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
 // The same attention with two query tiles (256 rows) per block and K, V loaded by TMA.  total_tiles = sum over
 // requests of ceil(q_len * g / 256); `total_pages`: first dimension of the cache tensors.  Returns 2 if this build
 // or these sizes do not take this kernel (head size above 128, pages of fewer than 8 tokens, unaligned pages).
-TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
-                                  long long total_pages, const int* table, int max_pages, int page_size,
-                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
-                                  int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
-                                  int* fault, cudaStream_t stream) {
+static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                            long long total_pages, const int* table, int max_pages, int page_size,
+                            const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                            int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                            int* fault, bool p_tmem, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
@@ -1197,7 +1220,8 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     const int dev = tl_device_index();
     if (dev < 0) return 1;
     if (!g_attr2_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc2_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attn_tc2_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tc2_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
         if (e != cudaSuccess) return (int)e;
         g_attr2_done[dev] = true;
     }
@@ -1214,11 +1238,31 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
     A.lim = TlLimits{table_rows, (int)total_pages, fault};
     dim3 grid((unsigned)total_tiles * (unsigned)nkv);
-    attn_tc2_prefill_kernel<<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    if (p_tmem) attn_tc2_prefill_kernel<true><<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    else          attn_tc2_prefill_kernel<false><<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
     return tl_launch_status();
 #else
     return 2;
 #endif
+}
+
+TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                  long long total_pages, const int* table, int max_pages, int page_size,
+                                  const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                  int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                                  int* fault, cudaStream_t stream) {
+    return tc2_prefill_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
+                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, false, stream);
+}
+
+// The same kernel with P kept in tensor memory (key tiles of 64 still, two S slots a query tile).
+TL_EXPORT int tl_attn_tc2p_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                   long long total_pages, const int* table, int max_pages, int page_size,
+                                   const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                   int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                                   int* fault, cudaStream_t stream) {
+    return tc2_prefill_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
+                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, true, stream);
 }
 
 // Two query tiles (256 rows) per block, key tiles of 128, P kept in tensor memory; K, V loaded by TMA.  total_tiles = sum over

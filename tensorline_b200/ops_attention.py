@@ -75,6 +75,8 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_tc2_prefill.restype = ctypes.c_int
         lib.tl_attn_tc3_prefill.argtypes = lib.tl_attn_tc2_prefill.argtypes
         lib.tl_attn_tc3_prefill.restype = ctypes.c_int
+        lib.tl_attn_tc2p_prefill.argtypes = lib.tl_attn_tc2_prefill.argtypes
+        lib.tl_attn_tc2p_prefill.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
 
@@ -132,19 +134,21 @@ TILE_ORDER = os.environ.get("TENSORLINE_B200_TILE_ORDER", "1") != "0"   # 0: req
 TC_PAIR = os.environ.get("TENSORLINE_B200_TC_PAIR", "1") != "0"   # 0: one query tile per block only (A/B timing)
 
 
-# 1: the pair kernel with 128-key tiles and P kept in tensor memory.  It is correct (same tests) but slower than the
-# 64-key kernel as it stands (8,192 tokens: 916 against 512 us): with one S slot a query tile, a tile's products and
-# softmax alternate, both tiles run in step, and the softmax of 128 keys a row (4,300 cycles for the two warps of a
-# scheduler) is the whole step.  Kept for further work, off by default.
-TC_P_IN_TMEM = os.environ.get("TENSORLINE_B200_TC_P_TMEM", "0") == "1"
+# Where the pair kernel keeps P.  "64" (default): the softmax writes P back into the S slot it has read (tensor memory)
+# and O += P V takes it from there; key tiles of 64, two S slots a query tile.  Bit for bit the results of "0" (P through
+# shared memory) and 1 to 4 % faster at 2,048 and 4,096 tokens (46.5 -> 45.5, 142 -> 139 us at 7B head counts, 69.5 ->
+# 66.7 at 14B), equal at 8,192: the step is bound by the softmax warps' instructions, not by shared memory.  "1": key
+# tiles of 128 and one S slot a query tile; correct (same tests) but slower (8,192 tokens: 916 against 512 us): a tile's
+# products and softmax alternate and the softmax of 128 keys a row is the whole step.  Kept for further work.
+TC_P_IN_TMEM = {"0": False, "1": True}.get(os.environ.get("TENSORLINE_B200_TC_P_TMEM", "64"), "64")
 
 
 def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-                    nq, nkv, d, window, scale, order=None, p_in_tmem: bool | None = None) -> bool:
+                    nq, nkv, d, window, scale, order=None, p_in_tmem=None) -> bool:
     """Prompt-portion attention on tcgen05 with two query tiles (256 rows) per block and K, V by TMA.
-    `p_in_tmem` (None: as the switch says): key tiles of 128 and P kept in tensor memory, else key tiles of 64 and
-    P through shared memory.  Head sizes 64 and 128, pages of 8 to 64 tokens; returns False (nothing launched)
-    for other sizes."""
+    `p_in_tmem` (None: as the switch says): "64": P kept in tensor memory, key tiles of 64; False: P through shared
+    memory; True: key tiles of 128 and P in tensor memory.  Head sizes 64 and 128, pages of 8 to 64 tokens; returns
+    False (nothing launched) for other sizes."""
     from .ops_gemm import status_word
     p_in_tmem = TC_P_IN_TMEM if p_in_tmem is None else p_in_tmem
     if d > 128 or page_size < 8 or page_size > KEY_TILE or page_size & (page_size - 1):
@@ -154,7 +158,8 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in range(B))
     if order is not None:
         tiles = order.numel()
-    entry = attn_tc_lib(d).tl_attn_tc3_prefill if p_in_tmem else attn_tc_lib(d).tl_attn_tc2_prefill
+    lib = attn_tc_lib(d)
+    entry = lib.tl_attn_tc2p_prefill if p_in_tmem == "64" else lib.tl_attn_tc3_prefill if p_in_tmem is True else lib.tl_attn_tc2_prefill
     rc = entry(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
                                             _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
@@ -162,7 +167,7 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
                                             table.shape[0], ops.fault_words(q.device), _stream())
     if rc == 2:
         return False
-    _check(rc, "attn_tc3_prefill" if p_in_tmem else "attn_tc2_prefill")
+    _check(rc, "attn_tc3_prefill" if p_in_tmem is True else "attn_tc2_prefill")     # "64" is the same kernel, another place for P
     return True
 
 

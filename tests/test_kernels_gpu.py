@@ -261,12 +261,12 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
 
 
 @pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
-@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16"])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16"])
 def test_paged_attention(case, kernel):
     """Decode and prefill attention over scattered pages against the plain formula."""
     from tensorline_b200 import ops, ops_attention
     nq, nkv, d, ps, ctx_lens, step_lens, window = case
-    if kernel in ("tcgen05_pair_bf16", "tcgen05_p_tmem_bf16") and d % 64:
+    if kernel in ("tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16") and d % 64:
         pytest.skip("no tcgen05 build for this head size")
     if kernel == "tcgen05_bf16" and (d % 64 or ps < 2):
         with pytest.raises(ops.KernelError):
@@ -307,13 +307,13 @@ def test_paged_attention(case, kernel):
     table = table_tensor(rows, max_pages, num_pages)
     kd, vd = kps.cuda(), vps.cuda()
     scale = d ** -0.5
-    if kernel in ("tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16"):
+    if kernel in ("tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16"):
         import functools
         q_start = [0]
         for n in step_lens:
             q_start.append(q_start[-1] + n)
         fn = ops_attention.prefill_tc if kernel == "tcgen05_bf16" else functools.partial(
-            ops_attention.prefill_tc_pair, p_in_tmem=kernel == "tcgen05_p_tmem_bf16")
+            ops_attention.prefill_tc_pair, p_in_tmem={"tcgen05_p_tmem_bf16": True, "tcgen05_p_tmem64_bf16": "64"}.get(kernel, False))
         took = fn(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
                   q_start, nq, nkv, d, window, scale)
         from tensorline_b200 import ops_gemm
