@@ -175,6 +175,12 @@ struct TcAttnArgs {
     // null: one request after the other from the end
     const int* order;
     TlLimits lim;                      // for the checking build; zeros: nothing known, nothing checked
+    // The pair kernel only.  ksplit > 1: the key tiles of every block are dealt out to ksplit blocks in equal runs; each
+    // leaves its unnormalised O rows in part_o [ksplit][tokens][nq][D] and (m, l) in part_ml [ksplit][tokens][nq][2]
+    // (m = -inf: that run held no key for the row) and a second kernel merges them.  For portions on long contexts whose
+    // query tiles alone would leave most of the GPU idle.
+    int ksplit, tokens;
+    float* part_o; float* part_ml;
 };
 
 // One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
@@ -545,11 +551,13 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kh = blockIdx.x % A.nkv, g = A.nq / A.nkv;   // blocks in order of falling length over all KV heads
+    const int ksplit = A.ksplit > 1 ? A.ksplit : 1, run = (int)(blockIdx.x % (unsigned)ksplit);
+    const int bx = (int)(blockIdx.x / (unsigned)ksplit), nbx = (int)(gridDim.x / (unsigned)ksplit);
+    const int kh = bx % A.nkv, g = A.nq / A.nkv;           // blocks in order of falling length over all KV heads
 
-    int tile = (int)(gridDim.x / A.nkv) - 1 - (int)(blockIdx.x / A.nkv), b = 0;          // longest tiles (late rows of a request) first
+    int tile = nbx / A.nkv - 1 - bx / A.nkv, b = 0;        // longest tiles (late rows of a request) first
     if (A.order != nullptr) {
-        const int packed = A.order[blockIdx.x / A.nkv];
+        const int packed = A.order[bx / A.nkv];
         b = packed >> 16; tile = packed & 0xFFFF;
     } else {
         for (; b < A.B; ++b) {
@@ -577,7 +585,15 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
     }
     // tile 1 holds the later rows: its range starts and ends no earlier than tile 0's
-    const int kt_lo = kt_first[0], kt_hi = max(kt_last[0], kt_last[1]), n_kt = kt_hi - kt_lo + 1;
+    int kt_lo = kt_first[0], kt_hi = max(kt_last[0], kt_last[1]), n_kt = kt_hi - kt_lo + 1;
+    if (ksplit > 1) {                                      // this block's run of the key tiles; a query tile may have none in it
+        const int per = (n_kt + ksplit - 1) / ksplit;
+        kt_lo += run * per;
+        kt_hi = min(kt_hi, kt_lo + per - 1);
+        n_kt = kt_hi - kt_lo + 1;                          // <= 0: nothing to read, the rows' parts say so
+#pragma unroll
+        for (int t = 0; t < QT; ++t) { kt_first[t] = max(kt_first[t], kt_lo); kt_last[t] = min(kt_last[t], kt_hi); }
+    }
     auto reads = [&](int t, int j) { return kt_lo + j >= kt_first[t] && kt_lo + j <= kt_last[t]; };
 
     if (tid == 0) {
@@ -708,7 +724,28 @@ attn_tc2_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mbar_arrive(bar_p + bi);
         }
         // ------------------------------------------------------------ epilogue: the tile's last P V has finished
-        if (ok && n_mine > 0 &&
+        if (ksplit > 1) {                                   // this run's part of the row: (m, l) and the unnormalised O
+            const bool any = n_mine > 0;                   // the same for all rows of the tile
+            if (any && ok) ok = mbar_wait(bar_o + t * 2 + ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag, A.status, 4);
+            const bool row = R < rows_total, live = any && ok && m_ref != -INFINITY;
+            const size_t slot = row ? ((size_t)run * A.tokens + (qs + R / g)) * A.nq + (kh * g + R % g) : 0;
+            if (row) *reinterpret_cast<float2*>(A.part_ml + slot * 2) = make_float2(live ? m_ref : -INFINITY, live ? l : 0.f);
+            if (any && ok) {                                // every lane of the warp takes part in the loads
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float* dst = A.part_o + slot * D;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float o[32];
+                    tmem_ld32(lane_addr + O2_COL + t * D + c0, o);
+                    tmem_ld_wait();
+                    if (row && live) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                    }
+                }
+            }
+        } else if (ok && n_mine > 0 &&
             mbar_wait(bar_o + t * 2 + ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag, A.status, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -1200,11 +1237,39 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
 // The same attention with two query tiles (256 rows) per block and K, V loaded by TMA.  total_tiles = sum over
 // requests of ceil(q_len * g / 256); `total_pages`: first dimension of the cache tensors.  Returns 2 if this build
 // or these sizes do not take this kernel (head size above 128, pages of fewer than 8 tokens, unaligned pages).
+// The parts that the runs of a split launch have left, merged: one (token, head) a group of D / 4 threads.  rows: the
+// tokens to merge (the step may hold tokens that another kernel serves).
+__global__ void attn_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                     const int* __restrict__ rows, int n_rows, int tokens, int nq, int ksplit) {
+    constexpr int PER = D / 4;                             // threads a (token, head)
+    const size_t item = (size_t)blockIdx.x * (blockDim.x / PER) + threadIdx.x / PER;
+    if (item >= (size_t)n_rows * nq) return;
+    const int token = rows[item / nq], head = (int)(item % nq), c = (threadIdx.x % PER) * 4;
+    float m = -INFINITY;
+    for (int r = 0; r < ksplit; ++r) m = fmaxf(m, part_ml[(((size_t)r * tokens + token) * nq + head) * 2]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    for (int r = 0; r < ksplit; ++r) {                     // in run order: the sum does not depend on who finished first
+        const size_t slot = ((size_t)r * tokens + token) * nq + head;
+        const float mr = part_ml[slot * 2];
+        if (mr == -INFINITY) continue;                     // that run held no key for this row: its O was never written
+        const float f = exp2f(mr - m);
+        const float4 o = *reinterpret_cast<const float4*>(part_o + slot * D + c);
+        acc.x += f * o.x; acc.y += f * o.y; acc.z += f * o.z; acc.w += f * o.w;
+        l += f * part_ml[slot * 2 + 1];
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    uint2 v;
+    v.x = pack_bf16(acc.x * inv, acc.y * inv); v.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)token * nq + head) * D + c) = v;
+}
+
 static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                             long long total_pages, const int* table, int max_pages, int page_size,
                             const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
                             int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
-                            int* fault, bool p_tmem, cudaStream_t stream) {
+                            int* fault, bool p_tmem, int ksplit, int tokens, float* part_o, float* part_ml,
+                            const int* merge_rows, int n_merge_rows, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
@@ -1237,9 +1302,17 @@ static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* 
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E; A.status = status; A.order = order;
     A.lim = TlLimits{table_rows, (int)total_pages, fault};
-    dim3 grid((unsigned)total_tiles * (unsigned)nkv);
+    if (ksplit > 1 && (ksplit > 8 || !part_o || !part_ml || !merge_rows || tokens <= 0 || ((uintptr_t)part_o & 15) || ((uintptr_t)part_ml & 7))) return 1;
+    A.ksplit = ksplit > 1 ? ksplit : 1; A.tokens = tokens; A.part_o = part_o; A.part_ml = part_ml;
+    dim3 grid((unsigned)total_tiles * (unsigned)nkv * (unsigned)A.ksplit);
     if (p_tmem) attn_tc2_prefill_kernel<true><<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
-    else          attn_tc2_prefill_kernel<false><<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    else        attn_tc2_prefill_kernel<false><<<grid, THREADS2, SMEM2_BYTES, stream>>>(mk, mv, A);
+    int rc = tl_launch_status();
+    if (rc || A.ksplit == 1 || n_merge_rows <= 0) return rc;
+    constexpr int GROUPS = 256 / (D / 4);                  // (token, head) pairs a block of 256 threads
+    const long long items = (long long)n_merge_rows * nq;
+    attn_tc_merge_kernel<<<(unsigned)((items + GROUPS - 1) / GROUPS), 256, 0, stream>>>(part_o, part_ml, (bf16*)out, merge_rows, n_merge_rows,
+                                                                                       tokens, nq, A.ksplit);
     return tl_launch_status();
 #else
     return 2;
@@ -1252,7 +1325,7 @@ TL_EXPORT int tl_attn_tc2_prefill(const void* q, int q_stride, void* out, const 
                                   int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
                                   int* fault, cudaStream_t stream) {
     return tc2_prefill_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
-                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, false, stream);
+                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, false, 1, 0, nullptr, nullptr, nullptr, 0, stream);
 }
 
 // The same kernel with P kept in tensor memory (key tiles of 64 still, two S slots a query tile).
@@ -1262,7 +1335,21 @@ TL_EXPORT int tl_attn_tc2p_prefill(const void* q, int q_stride, void* out, const
                                    int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
                                    int* fault, cudaStream_t stream) {
     return tc2_prefill_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
-                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, true, stream);
+                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, true, 1, 0, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The pair kernel with every block's key tiles dealt out to `ksplit` blocks (2..8) and a merge kernel behind them: for
+// portions on long contexts whose query tiles alone leave most of the GPU idle.  part_o: float [ksplit, tokens, nq, D],
+// part_ml: float [ksplit, tokens, nq, 2] (scratch); merge_rows: the n_merge_rows tokens this launch serves; tokens: rows of out.
+TL_EXPORT int tl_attn_tc2_prefill_split(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
+                                        long long total_pages, const int* table, int max_pages, int page_size,
+                                        const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
+                                        int window, float scale, int total_tiles, int* status, const int* order, int table_rows,
+                                        int* fault, int p_tmem, int ksplit, int tokens, float* part_o, float* part_ml,
+                                        const int* merge_rows, int n_merge_rows, cudaStream_t stream) {
+    return tc2_prefill_impl(q, q_stride, out, k_pages, v_pages, total_pages, table, max_pages, page_size, q_start, start_pos, slots,
+                            B, nq, nkv, window, scale, total_tiles, status, order, table_rows, fault, p_tmem != 0, ksplit, tokens,
+                            part_o, part_ml, merge_rows, n_merge_rows, stream);
 }
 
 // Two query tiles (256 rows) per block, key tiles of 128, P kept in tensor memory; K, V loaded by TMA.  total_tiles = sum over

@@ -77,6 +77,8 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_tc3_prefill.restype = ctypes.c_int
         lib.tl_attn_tc2p_prefill.argtypes = lib.tl_attn_tc2_prefill.argtypes
         lib.tl_attn_tc2p_prefill.restype = ctypes.c_int
+        lib.tl_attn_tc2_prefill_split.argtypes = lib.tl_attn_tc2_prefill.argtypes[:-1] + [_I, _I, _I, _P, _P, _P, _I, _P]
+        lib.tl_attn_tc2_prefill_split.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
 
@@ -132,6 +134,7 @@ def tile_order(h_q_start, h_start_pos, group: int, rows_per_tile: int, device, s
 
 TILE_ORDER = os.environ.get("TENSORLINE_B200_TILE_ORDER", "1") != "0"   # 0: request after request (A/B timing)
 TC_PAIR = os.environ.get("TENSORLINE_B200_TC_PAIR", "1") != "0"   # 0: one query tile per block only (A/B timing)
+KEY_SPLIT = os.environ.get("TENSORLINE_B200_KEY_SPLIT", "1") != "0"   # 0: a query tile's keys never dealt out to several blocks
 
 
 # Where the pair kernel keeps P.  "64" (default): the softmax writes P back into the S slot it has read (tensor memory)
@@ -144,11 +147,14 @@ TC_P_IN_TMEM = {"0": False, "1": True}.get(os.environ.get("TENSORLINE_B200_TC_P_
 
 
 def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-                    nq, nkv, d, window, scale, order=None, p_in_tmem=None) -> bool:
+                    nq, nkv, d, window, scale, order=None, p_in_tmem=None, ksplit: int = 1, merge_rows=None) -> bool:
     """Prompt-portion attention on tcgen05 with two query tiles (256 rows) per block and K, V by TMA.
     `p_in_tmem` (None: as the switch says): "64": P kept in tensor memory, key tiles of 64; False: P through shared
     memory; True: key tiles of 128 and P in tensor memory.  Head sizes 64 and 128, pages of 8 to 64 tokens; returns
-    False (nothing launched) for other sizes."""
+    False (nothing launched) for other sizes.
+    `ksplit` (2..8, not with the 128-key kernel): every block's key tiles are dealt out to that many blocks and a second
+    kernel merges their parts; `merge_rows`: int32 device tensor of the tokens this launch serves (None: all rows of
+    `out`).  For portions on long contexts whose query tiles alone leave most of the GPU idle."""
     from .ops_gemm import status_word
     p_in_tmem = TC_P_IN_TMEM if p_in_tmem is None else p_in_tmem
     if d > 128 or page_size < 8 or page_size > KEY_TILE or page_size & (page_size - 1):
@@ -159,6 +165,21 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
     if order is not None:
         tiles = order.numel()
     lib = attn_tc_lib(d)
+    if ksplit > 1 and p_in_tmem is not True:
+        T = out.shape[0]
+        if merge_rows is None:
+            merge_rows = torch.arange(T, dtype=torch.int32, device=q.device)
+        part_o = torch.empty((ksplit, T, nq, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((ksplit, T, nq, 2), dtype=torch.float32, device=q.device)
+        rc = lib.tl_attn_tc2_prefill_split(
+            _ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(table), table.shape[1], page_size,
+            _ptr(q_start), _ptr(start_pos), _ptr(slots), B, nq, nkv, int(window or 0), float(scale), tiles,
+            _ptr(status_word(q.device)), _ptr(order) if order is not None else None, table.shape[0], ops.fault_words(q.device),
+            int(p_in_tmem == "64"), ksplit, T, _ptr(part_o), _ptr(part_ml), _ptr(merge_rows), merge_rows.numel(), _stream())
+        if rc == 2:
+            return False
+        _check(rc, "attn_tc2_prefill+split", launches=2)
+        return True
     entry = lib.tl_attn_tc2p_prefill if p_in_tmem == "64" else lib.tl_attn_tc3_prefill if p_in_tmem is True else lib.tl_attn_tc2_prefill
     rc = entry(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0],
                                             _ptr(table), table.shape[1], page_size, _ptr(q_start), _ptr(start_pos),
@@ -359,7 +380,25 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
             if key not in ctx.scratch:
                 ctx.scratch[key] = tile_order(ctx.h_q_start, ctx.h_start_pos, g, rows_per_tile, qkv.device, skip)
             return ctx.scratch[key]
-        if use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
+        # A portion on a long context whose pairs of query tiles fill less than half the GPU: every block's key tiles
+        # are dealt out to several blocks and their parts merged by a second kernel (7B head counts, 512 tokens on
+        # 3,584 cached: 54 against 71 us for the one-tile kernel and 77 for the pair kernel alone; 256 tokens: 35
+        # against 66; 128 tokens on 8,000 cached: 42 against 127), as long as a run keeps twelve key tiles or more.
+        ksplit = 1
+        if use_tc and TC_PAIR and KEY_SPLIT and d <= 128 and not window:
+            pair_blocks = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in rest) * nkv
+            key_tiles = max(-(-(ctx.h_start_pos[i] + ctx.h_q_start[i + 1] - ctx.h_q_start[i]) // KEY_TILE) for i in rest) if rest else 0
+            ksplit = min(8, ops.num_sms() // max(1, pair_blocks), key_tiles // 12)
+        if ksplit >= 2:
+            rows_key = ("merge_rows", len(skip))
+            if rows_key not in ctx.scratch:
+                rows = [t for i in rest for t in range(ctx.h_q_start[i], ctx.h_q_start[i + 1])]
+                ctx.scratch[rows_key] = torch.tensor(rows, dtype=torch.int32).to(qkv.device, non_blocking=True)
+            if not prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), ksplit=ksplit, merge_rows=ctx.scratch[rows_key]):
+                ksplit = 1
+        if ksplit >= 2:
+            pass
+        elif use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE)):
             pass
         elif use_tc:
             prefill_tc(*args, order(TC_QUERY_TILE))

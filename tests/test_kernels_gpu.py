@@ -261,12 +261,12 @@ ATT_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in th
 
 
 @pytest.mark.parametrize("case", ATT_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}" for c in ATT_CASES])
-@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16"])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "mma_bf16", "tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16", "tcgen05_pair_split_bf16"])
 def test_paged_attention(case, kernel):
     """Decode and prefill attention over scattered pages against the plain formula."""
     from tensorline_b200 import ops, ops_attention
     nq, nkv, d, ps, ctx_lens, step_lens, window = case
-    if kernel in ("tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16") and d % 64:
+    if kernel in ("tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16", "tcgen05_pair_split_bf16") and d % 64:
         pytest.skip("no tcgen05 build for this head size")
     if kernel == "tcgen05_bf16" and (d % 64 or ps < 2):
         with pytest.raises(ops.KernelError):
@@ -307,13 +307,15 @@ def test_paged_attention(case, kernel):
     table = table_tensor(rows, max_pages, num_pages)
     kd, vd = kps.cuda(), vps.cuda()
     scale = d ** -0.5
-    if kernel in ("tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16"):
+    if kernel in ("tcgen05_bf16", "tcgen05_pair_bf16", "tcgen05_p_tmem_bf16", "tcgen05_p_tmem64_bf16", "tcgen05_pair_split_bf16"):
         import functools
         q_start = [0]
         for n in step_lens:
             q_start.append(q_start[-1] + n)
         fn = ops_attention.prefill_tc if kernel == "tcgen05_bf16" else functools.partial(
             ops_attention.prefill_tc_pair, p_in_tmem={"tcgen05_p_tmem_bf16": True, "tcgen05_p_tmem64_bf16": "64"}.get(kernel, False))
+        if kernel == "tcgen05_pair_split_bf16":             # every block's key tiles dealt out to three blocks (some get none)
+            fn = functools.partial(ops_attention.prefill_tc_pair, p_in_tmem="64", ksplit=3)
         took = fn(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))),
                   q_start, nq, nkv, d, window, scale)
         from tensorline_b200 import ops_gemm
@@ -466,6 +468,8 @@ def test_decode_cluster_merge_for_every_number_of_ranges(nq, nkv, d):
     (28, 4, 128, 16, [(1500, 1), (0, 300), (1100, 1), (40, 1)], None),      # singles between and around a portion
     (8, 2, 64, 8, [(70, 2), (1300, 1), (0, 150), (900, 1)], 700),           # a window; the two-token portion stays
     (6, 2, 48, 16, [(1200, 1), (5, 40)], None),                             # a head size without tcgen05 build
+    # a portion on a long context that fills little of the GPU: its key tiles are dealt out to two blocks a query-tile pair
+    (8, 2, 64, 16, [(3000, 1), (1500, 200), (2900, 1)], None),
     # no single token reads 1.5 times the portion's keys, but their (request, KV head) pairs fill the GPU 1.6 times over
     (40, 8, 128, 16, [(800 + 7 * i, 1) for i in range(30)] + [(900, 260)], None),
 ])
@@ -526,10 +530,9 @@ def test_single_tokens_of_a_mixed_step_take_the_decode_kernel(case, monkeypatch)
     assert_close(whole.view(T, nq, d), torch.cat(want), "mixed step, all in the prompt kernel", **BF16)
     single_rows = [q_start[b] for b, (c, n) in enumerate(reqs) if n == 1]
     other = [r for r in range(T) if r not in single_rows]
-    if B <= 8:
-        assert torch.equal(out[other], whole[other])        # the portions' rows do not notice
-    else:                                                   # with the single tokens' tiles the other prompt kernel is chosen
-        assert_close(out[other].float(), whole[other].float(), "the portion's rows by the two prompt kernels", rtol=2 ** -6, atol=2e-3)
+    # the portions' rows do not notice, beyond rounding (with the single tokens' tiles another prompt kernel may be chosen,
+    # or the key tiles dealt out to several blocks)
+    assert_close(out[other].float(), whole[other].float(), "the portion's rows with and without the single tokens beside them", **BF16)
 
 
 def test_attention_refuses_unsupported_head_size():
