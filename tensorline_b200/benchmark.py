@@ -418,6 +418,15 @@ def run_ours(a):
         line["gpu_launches"] = ops.launch_count()
         print(json.dumps(line))
         return 0
+    if a.timeline:
+        # the tracing build's stamps of one captured decode step (TENSORLINE_B200_TRACE=1), as a table
+        from tensorline_b200 import ops_attention, ops_gemm, timeline
+        tl = timeline.Timeline({"product": ops_gemm.lib(), "attn": ops_attention.attn_lib(cfg.head_dim)}, device)
+        ms, _, _ = timed_decode(eng, batch, ctx0, max(K, 8), W, V)
+        tl.stop()
+        print(f"decode step, batch {batch}, context {ctx0}, {L} layers: {ms:.4f} ms with the stamps")
+        print(timeline.table(tl.last_step(ms)))
+        return 0
     if a.only == "prefill":
         pre_ms = timed_prefill(eng, PREFILL_TOKENS, V, iters=max(1, K), warm=W)
         print(json.dumps({"impl": "ours", "only": "prefill", "layers": L, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3)}))
@@ -499,6 +508,8 @@ def main(argv=None):
                     help="decode / prefill: a short run of that phase alone (for profilers); prints its own line")
     ap.add_argument("--batch", type=int, default=8, help="decode batch of the main measurement")
     ap.add_argument("--profile", action="store_true", help="add milliseconds per kernel class of one eager decode and one prompt step")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
     a = ap.parse_args(argv)
     if a.warmup < 3:

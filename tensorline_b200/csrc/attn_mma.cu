@@ -84,6 +84,9 @@ struct AttnArgs {
     // query heads on the way to shared memory; the block whose key range holds the token's own position does the same for
     // the new key and value, writes them to their page (rope_write) and puts them into its own tiles.  Null inv_freq: not folded.
     const float* rope_inv_freq; const void* rope_bias; int rope_bias_f32; int rope_write;
+    // tracing build (the TMA decode kernel): stamps 0 block start, 1 dependency wait returned, 2 first stage landed, 3 last
+    // stage landed, 4 block end, 5 last stage worked through, 6 at the cluster barrier, 7 past it
+    TlTrace trace;
     bf16* k_pages_w; bf16* v_pages_w;
 };
 
@@ -611,6 +614,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DEC_STAGES);
     int* stab = reinterpret_cast<int*>(tiles + TMA_TAB_OFFSET);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) tl_stamp(A.trace, 0);
     const int g = A.nq / A.nkv, m_tiles = (g + 15) / 16;
     const int split = blockIdx.x / m_tiles, mt = blockIdx.x % m_tiles;
     const int kh = blockIdx.y, b = blockIdx.z;
@@ -668,6 +672,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
     if (warp < 4 || !early) {
         grid_dependency_wait();                            // queries and the newest keys and values: the kernel before
+        if (tid == 0) tl_stamp(A.trace, 1);
         grid_dependency_trigger();
     }
     if (warp < 4 && !fold) {
@@ -762,6 +767,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int st = 0; st < n_stage; ++st) {
         const int buf = st % DEC_STAGES;
         if (!mbar_wait_tma(full + buf, (st / DEC_STAGES) & 1, abort_flag, status)) break;
+        if (tid == 0 && st == 0) tl_stamp(A.trace, 2);
+        if (tid == 0 && st == n_stage - 1) tl_stamp(A.trace, 3);
         if (st == st_new) {                                // the stage with the token's own position: its new key and value
             if (new_i0 >= 0) {
                 unsigned char* tile = tiles + buf * 2 * TMA_TILE_BYTES + (new_is_v ? TMA_TILE_BYTES : 0);
@@ -804,6 +811,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         __syncwarp();                                      // every lane has read the stage
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + buf)) : "memory");
     }
+    if (tid == 0) tl_stamp(A.trace, 5);
     __syncthreads();                                       // the stage buffers become the merge area
     if (*abort_flag) {
         __syncthreads();
@@ -880,7 +888,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             float* dst = cluster_peer_rw(recvML + (split * 16 + row) * 2, owner);
             dst[0] = sMM[row]; dst[1] = sLT[row];
         }
+        if (tid == 0) tl_stamp(A.trace, 6);
         cluster_barrier();                                 // all shares have arrived; nobody touches another block's memory after this
+        if (tid == 0) tl_stamp(A.trace, 7);
         for (int idx = tid; idx < rows * cpc; idx += 128) {
             const int row = idx / cpc, c = idx - row * cpc, col = split * cpc + c;
             if (col >= D) continue;
@@ -905,6 +915,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             A.out[((size_t)qrow * A.nq + kh * g + row) * D + col] = __float2bfloat16_rn(lt > 0.f ? acc / lt : 0.f);
         }
     }
+    if (tid == 0) tl_stamp(A.trace, 4);
 }
 #endif  // HEAD_DIM % 64 == 0
 
@@ -1002,6 +1013,7 @@ TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
 TL_EXPORT int tl_attn_decode_max_table() { return DECODE_MAX_TAB; }
 
+
 // total_tiles = sum over requests of ceil(q_len * g / 64), computed by the caller.
 TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                               const int* table, int max_pages, int page_size, const int* q_start,
@@ -1085,6 +1097,7 @@ int make_pages_map(CUtensorMap* map, const void* base, long long rows, int page_
 namespace {
 struct RopeFold { const float* inv_freq; const void* bias; int bias_f32; int write_kv; };
 
+TlTraceHost g_trace;
 int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                     long long total_pages, const int* table, int max_pages, int page_size,
                     const int* q_start, const int* start_pos, const int* slots, int B, int nq, int nkv,
@@ -1134,6 +1147,7 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
     A.lim = TlLimits{table_rows, (int)total_pages, fault};
     A.rope_inv_freq = R.inv_freq; A.rope_bias = R.bias; A.rope_bias_f32 = R.bias_f32; A.rope_write = R.write_kv;
+    A.trace = g_trace.take((unsigned)(splits * ((nq / nkv + 15) / 16) * nkv * B));
     A.k_pages_w = (bf16*)const_cast<void*>(k_pages); A.v_pages_w = (bf16*)const_cast<void*>(v_pages);
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
@@ -1160,6 +1174,15 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
 #endif
 }
 }  // namespace
+
+// Tracing build: the TMA decode launches from now on leave their stamps in buf [slots][512][8] (device, zeroed by the
+// caller), one slot a launch from `first` on; null: no more stamps.  Accepted and without effect in the ordinary build.
+TL_EXPORT int tl_trace_set(long long* buf, int slots, int first) {
+    g_trace.buf = buf; g_trace.slots = slots; g_trace.next = first;
+    return g_trace.next;
+}
+TL_EXPORT int tl_trace_next() { return g_trace.next; }
+TL_EXPORT int tl_trace_build() { return TL_TRACING; }
 
 TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                  long long total_pages, const int* table, int max_pages, int page_size,

@@ -32,6 +32,9 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 # The checking build: TENSORLINE_B200_CHECK=1 compiles every library with -DTL_CHECK=1 (bounds checks on every
 # block-table and page index inside the kernels, see common.cuh); it is a library of its own beside the ordinary one.
 CHECK_BUILD = os.environ.get("TENSORLINE_B200_CHECK", "0") == "1"
+# The tracing build: TENSORLINE_B200_TRACE=1 compiles every library with -DTL_TRACE=1 (global-timer stamps in the kernels
+# that wait on the kernel in front of them, see common.cuh and tensorline_b200/timeline.py) under a name of its own.
+TRACE_BUILD = os.environ.get("TENSORLINE_B200_TRACE", "0") == "1"
 
 _loaded: dict = {}
 _lock = threading.Lock()
@@ -76,16 +79,23 @@ def _digest(sources, flags) -> str:
     return h.hexdigest()[:16]
 
 
-def library_path(name: str, sources, defines: dict | None = None, extra_flags=(), check: bool | None = None) -> tuple:
-    """(path, flags, already built).  `check`: the checking build of the library (None: as the environment says)."""
+def library_path(name: str, sources, defines: dict | None = None, extra_flags=(), check: bool | None = None,
+                 trace: bool | None = None) -> tuple:
+    """(path, flags, already built).  `check` / `trace`: the checking / tracing build of the library (None: as the
+    environment says)."""
     check = CHECK_BUILD if check is None else check
+    trace = TRACE_BUILD if trace is None else trace
     defines = dict(defines or {})
     if check:
         defines["TL_CHECK"] = 1
+    if trace:
+        defines["TL_TRACE"] = 1
     flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in sorted(defines.items())] + list(extra_flags)
     tag = _digest(sources, flags)
     if check:
         name = name + "_chk"
+    if trace:
+        name = name + "_trc"
     fname = f"lib{name}_{tag}.so"
     home = CSRC / "_build"
     if (home / fname).is_file():
@@ -106,13 +116,15 @@ def library_path(name: str, sources, defines: dict | None = None, extra_flags=()
 
 
 def build_library(name: str, sources, defines: dict | None = None, extra_flags=(), verbose: bool = True,
-                  check: bool | None = None) -> Path:
+                  check: bool | None = None, trace: bool | None = None) -> Path:
     """Compile (if not yet built) and return the path of the shared library."""
-    path, flags, exists = library_path(name, sources, defines, extra_flags, check)
+    path, flags, exists = library_path(name, sources, defines, extra_flags, check, trace)
     if exists:
         return path
     if CHECK_BUILD if check is None else check:
         name = name + "_chk"
+    if TRACE_BUILD if trace is None else trace:
+        name = name + "_trc"
     nvcc = _nvcc()
     tmp = path.with_suffix(f".tmp{os.getpid()}.so")
     cmd = [nvcc] + flags + ["-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in sources]

@@ -122,6 +122,42 @@ __device__ __forceinline__ int tl_checked(int v, int limit, const TlLimits& L, i
 }
 TL_EXPORT int tl_check_build();
 
+// The tracing build (-DTL_TRACE=1): the kernels that wait on the kernel in front of them (the few-token product, the TMA
+// decode attention) leave global-timer stamps, eight a block, in a buffer the host names: when the block started, when
+// its dependency wait returned, when its first and its last operand tile had landed, when it ended, and three places of
+// its own.  From them the host draws the time line of a captured step: how long each kernel's stream of operands lasts
+// and how long nothing streams between two kernels.  Without the define a stamp compiles to nothing; the record travels
+// in the kernels' arguments either way, so both builds have the same interface.
+struct TlTrace {
+    long long* buf;      // [slots][TL_TRACE_BLOCKS][8] nanoseconds; null: not recorded
+    int slot;            // this launch's slot
+};
+constexpr int TL_TRACE_BLOCKS = 512;                       // launches of more blocks are not recorded
+#ifdef TL_TRACE
+#define TL_TRACING 1
+#else
+#define TL_TRACING 0
+#endif
+__device__ __forceinline__ void tl_stamp(const TlTrace& T, int i) {
+#if TL_TRACING
+    if (T.buf) {
+        const unsigned block = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        T.buf[((size_t)T.slot * TL_TRACE_BLOCKS + block) * 8 + i] = (long long)t;
+    }
+#endif
+}
+// Host side of a library that traces: where the stamps go and which slot the next launch takes.
+struct TlTraceHost {
+    long long* buf = nullptr; int next = 0, slots = 0;
+    TlTrace take(unsigned blocks) {
+        TlTrace t{nullptr, 0};
+        if (TL_TRACING && buf && next < slots && blocks <= (unsigned)TL_TRACE_BLOCKS) { t.buf = buf; t.slot = next++; }
+        return t;
+    }
+};
+
 // silu(g) * u in the bfloat16 engine (g and u hold bfloat16 values): float32 arithmetic with the division that has no
 // special-case branch, so the chains of neighbouring elements overlap (an epilogue of 16 tokens took 2,600 cycles with
 // the exact division, 1,500 with this one).  Every bfloat16 path of the activation calls this function and so gives the

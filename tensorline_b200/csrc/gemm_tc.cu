@@ -136,6 +136,9 @@ struct GemmArgs {
     // epilogue warps from the float residual stream nx [rows, K]: h = cast(cast(x * rstd) * w), rstd of a row from the
     // nparts partial sums of squares nssq [rows, nparts] (summed in a fixed order), K and eps.
     const float* nx; const float* nssq; int nparts; const void* nw; int nw_f32; float neps;
+    // tracing build: stamps 0 block start, 1 dependency wait returned, 2 first stage ready for the MMA, 3 last stage
+    // ready, 4 block end; with a made B operand 5 rstd known, 6 first raw tile landed, 7 first operand tile made
+    TlTrace trace;
 };
 
 // The B operand (activations, BN tokens x 64 k a stage) made from the residual stream instead of loaded.  The copy thread
@@ -190,9 +193,11 @@ __device__ __forceinline__ void make_b_tiles(const GemmArgs& G, unsigned char* t
         if (l8 == 0 && tl < BN) rstd_s[tl] = live ? 1.0f / sqrtf(ss / (float)G.K + G.neps) : 0.f;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (e == 0) tl_stamp(G.trace, 5);
     for (int i = 0; i < n_kt; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(raw_bar + s, (i / STAGES) & 1, abort_flag, G.status, 4, G.wait_cycles)) return;   // the stage's raw material is in
+        if (i == 0 && e == 0) tl_stamp(G.trace, 6);
         const unsigned char* rx = raw + s * RAW_BYTES;
         const unsigned char* rw = rx + BN * BK * 4;
         unsigned char* bt = tiles + s * STAGE_BYTES + A_BYTES;
@@ -230,6 +235,7 @@ __device__ __forceinline__ void make_b_tiles(const GemmArgs& G, unsigned char* t
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes before the MMA reads them
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (e == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(full_bar + s)) : "memory");
+        if (i == 0 && e == 0) tl_stamp(G.trace, 7);
     }
 }
 
@@ -263,6 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 
     if (threadIdx.x == 0) {
+        tl_stamp(G.trace, 0);
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + s, made_b ? 2 : 1); mbar_init(empty_bar + s, 1); mbar_init(raw_bar + s, 1); }
         mbar_init(done_bar, 1);
         mbar_init(ssq_bar, 1);
@@ -307,6 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             else        tma_load_2d(st + A_BYTES, &map_b, full_bar + i, (kt_begin + i) * BK, b0);
         }
         grid_dependency_wait();
+        tl_stamp(G.trace, 1);
         grid_dependency_trigger();
         if constexpr (BN <= 64) {
             if (made_b && ssq_in_smem<BN>(G, b0)) {
@@ -341,6 +349,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int s = i % STAGES;
             ok = mbar_wait(full_bar + s, (i / STAGES) & 1, abort_flag, G.status, 2, G.wait_cycles);
             if (!ok) break;
+            if (i == 0) tl_stamp(G.trace, 2);
+            if (i == n_kt - 1) tl_stamp(G.trace, 3);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_addr = smem_addr(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -548,6 +558,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------------------------------------------------------- teardown
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) tl_stamp(G.trace, 4);
     if (*abort_flag) {                                   // give copies in flight time to land before the block's
         const long long t0 = clock64();                  // shared memory is handed to another block
         while (clock64() - t0 < 2000000LL) { }
@@ -633,6 +644,7 @@ int cached_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows
 }
 
 long long g_wait_cycles = WAIT_CYCLES;
+TlTraceHost g_trace;
 int g_drop_last_load = 0;
 
 template <int BN, int STAGES>
@@ -718,6 +730,7 @@ int gemm_impl(const void* x, const void* w, void* y, int out_f32, int ldo, int T
     G.wait_cycles = g_wait_cycles; G.drop_last_load = g_drop_last_load;
     dim3 grid((RA + BM - 1) / BM, (RB + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return 1;
+    G.trace = g_trace.take(grid.x * grid.y * grid.z);
     G.counters = (splits > 1 && counters != nullptr && (long long)grid.x * grid.y <= n_counters) ? counters : nullptr;
     switch (bn) {
         case 16:  e = launch<16, 5>(ma, mb, G, grid, stream); break;
@@ -757,6 +770,16 @@ TL_EXPORT int tl_gemm_tc_normed(const void* x, const void* w, void* y, int out_f
     return gemm_impl(x, w, y, out_f32, ldo, T, N, K, swap, bn, splits, partial, status, counters, n_counters, gated, cluster_reduce,
                      F, stream);
 }
+
+// Tracing build: the products launched from now on leave their stamps in buf [slots][512][8] (device, zeroed by the caller),
+// one slot a launch, starting at slot `first`; null: no more stamps.  Returns the next free slot.  In the ordinary build
+// the call is accepted and nothing is recorded.
+TL_EXPORT int tl_trace_set(long long* buf, int slots, int first) {
+    g_trace.buf = buf; g_trace.slots = slots; g_trace.next = first;
+    return g_trace.next;
+}
+TL_EXPORT int tl_trace_next() { return g_trace.next; }
+TL_EXPORT int tl_trace_build() { return TL_TRACING; }
 
 // For tests of the failure path only.  `wait_cycles` > 0: how many clock cycles a wait on a barrier may take from
 // now on (0: back to the default of about two seconds).  `drop_last_load` = 1: the copy thread of every block leaves
