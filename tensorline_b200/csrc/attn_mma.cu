@@ -399,7 +399,7 @@ constexpr int DEC_STAGES = TL_DEC_STAGES;
 constexpr int DECODE_KV_SMEM = 2 * DEC_STAGES * BN * DP * 2;
 constexpr int DECODE_MERGE_SMEM = (4 * 16 * D + 4 * 16 * 2) * 4;
 constexpr int DECODE_TAB_OFFSET = 16 * DP * 2 + (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
-constexpr int DECODE_MAX_TAB = 1536;                    // table entries a block may copy (6 KB: head size 256 leaves no more)
+constexpr int DECODE_MAX_TAB = 1024;                    // table entries a block may copy (4 KB: head size 256 leaves no more)
 
 // grid (splits * m_tiles, nkv, B); 4 warps; each stage is 64 keys, 16 per warp.
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
@@ -546,11 +546,12 @@ constexpr int TMA_Q_OFFSET = 2 * DEC_STAGES * TMA_TILE_BYTES;
 constexpr int TMA_BAR_OFFSET = TMA_Q_OFFSET + ((16 * DP * 2 + 15) / 16) * 16;
 constexpr int TMA_CS_OFFSET = TMA_BAR_OFFSET + 128;              // room for 2 * DEC_STAGES barriers and a flag; then cos, sin [D]
 // Where the other blocks of a cluster put their shares of this block's columns (CLUSTER): [key range][16 rows][columns of this
-// block] floats, at most 16 (D + 8) in all, then (m, l) [key range][16 rows].  Not in the stage buffers: a block that has
+// block] floats, at most 16 (D + 16) in all, then (m, l) [key range][16 rows], for up to 16 key ranges.  Not in the stage buffers: a block that has
 // finished writes here while this one may still be loading keys.
 constexpr int TMA_RECV_OFFSET = TMA_CS_OFFSET + D * 4;
-constexpr int TMA_RECV_ML = 16 * (D + 8) * 4;
-constexpr int TMA_TAB_OFFSET = TMA_RECV_OFFSET + TMA_RECV_ML + 8 * 16 * 2 * 4;
+constexpr int TMA_MAX_RANGES = 16;                               // key ranges of a cluster: 8 is the portable size, 16 this GPU's
+constexpr int TMA_RECV_ML = 16 * (D + TMA_MAX_RANGES) * 4;
+constexpr int TMA_TAB_OFFSET = TMA_RECV_OFFSET + TMA_RECV_ML + TMA_MAX_RANGES * 16 * 2 * 4;
 #ifndef TL_TMA_COPY_WARPS
 #define TL_TMA_COPY_WARPS 2
 #endif
@@ -883,10 +884,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     }
     if (CLUSTER) {
-        if (tid < ns * 16 && (tid & 15) < rows) {          // (m, l) of every row to every block
-            const int owner = tid >> 4, row = tid & 15;
-            float* dst = cluster_peer_rw(recvML + (split * 16 + row) * 2, owner);
-            dst[0] = sMM[row]; dst[1] = sLT[row];
+        for (int i = tid; i < ns * 16; i += 128) {         // (m, l) of every row to every block
+            const int owner = i >> 4, row = i & 15;
+            if (row < rows) {
+                float* dst = cluster_peer_rw(recvML + (split * 16 + row) * 2, owner);
+                dst[0] = sMM[row]; dst[1] = sLT[row];
+            }
         }
         if (tid == 0) tl_stamp(A.trace, 6);
         cluster_barrier();                                 // all shares have arrived; nobody touches another block's memory after this
@@ -894,10 +897,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int idx = tid; idx < rows * cpc; idx += 128) {
             const int row = idx / cpc, c = idx - row * cpc, col = split * cpc + c;
             if (col >= D) continue;
-            float ms[8], ls[8], os[8];
+            float ms[TMA_MAX_RANGES], ls[TMA_MAX_RANGES], os[TMA_MAX_RANGES];
             float mm = -INFINITY;
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
+            for (int sp = 0; sp < TMA_MAX_RANGES; ++sp) {
                 if (sp < ns) {
                     ms[sp] = recvML[(sp * 16 + row) * 2]; ls[sp] = recvML[(sp * 16 + row) * 2 + 1];
                     os[sp] = recvO[(sp * 16 + row) * cpc + c];
@@ -906,7 +909,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             float acc = 0.f, lt = 0.f;
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
+            for (int sp = 0; sp < TMA_MAX_RANGES; ++sp) {
                 if (sp < ns) {
                     const float f = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - mm);
                     acc += f * os[sp]; lt += f * ls[sp];
@@ -1108,7 +1111,7 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
     if (R.inv_freq && ((q_stride & 7) || ((uintptr_t)q & 15) || (R.bias && ((uintptr_t)R.bias & 15)))) return 2;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     // cluster_merge: the key ranges of a (request, KV head) merge inside a thread-block cluster, no partials needed
-    if (cluster_merge && (splits < 2 || splits > 8 || nq / (nkv > 0 ? nkv : 1) > 16)) return 1;
+    if (cluster_merge && (splits < 2 || splits > TMA_MAX_RANGES || nq / (nkv > 0 ? nkv : 1) > 16)) return 1;
     if (nq % nkv || chunk % BN || splits < 1 || (splits > 1 && !cluster_merge && (!part_o || !part_ml))) return 1;
     if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
     if (!g_encode) {
@@ -1129,6 +1132,8 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
         if (ce == cudaSuccess)
             ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
+        if (ce == cudaSuccess)                             // clusters of 9 to 16 blocks
+            ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (ce != cudaSuccess) return (int)ce;
         g_tma_attr_done[dev_index] = true;
     }

@@ -19,7 +19,7 @@ _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _libs: dict = {}
 
 KEY_TILE = 64
-DECODE_MAX_TABLE_ENTRIES = 1536     # block-table entries a decode block copies to shared memory (`tl_attn_decode_max_table`)
+DECODE_MAX_TABLE_ENTRIES = 1024     # block-table entries a decode block copies to shared memory (`tl_attn_decode_max_table`)
 TC_PREFILL = os.environ.get("TENSORLINE_B200_TC", "1") != "0"   # 0: mma.sync attention only (A/B timing)
 
 
@@ -199,7 +199,8 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     whatever else runs, so a request's keys are cut into ranges until the blocks fill the GPU's resident
     slots once (a second, partly filled round would double the time) - but not finer than four tiles a
     range (two when that leaves 64 blocks or fewer), below which the merge of the partials costs more
-    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 -> 32 ranges, 2 to 8 -> 8, 16 -> 4, 32 -> 2, 64 -> 1.
+    than the shorter ranges save.  Measured at 7B sizes, context 4,090: batch 1 to 3 -> 16 ranges (one cluster of sixteen blocks a (request, KV head)), 4 to 8 -> 8,
+    16 -> 4, 32 -> 2, 64 -> 1.
     A block copies its range's block-table entries to shared memory, DECODE_MAX_TABLE_ENTRIES at most: a range is
     never longer than that many pages, whatever the rules above say (long contexts on small pages get more ranges)."""
     NUM_SMS = sms or ops.num_sms()
@@ -211,7 +212,11 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
     splits = min(fill, max(1, tiles // 4), max_splits)
     if base * splits <= 64:
         splits = min(fill, max(1, tiles // 2), max_splits)
-    if 8 < splits <= 16:
+    if splits > 8 and base <= CLUSTER16_MAX and m_tiles == 1:
+        # few requests: sixteen ranges in a cluster of sixteen blocks (no parts in memory, no combine kernel, which alone
+        # cost 5 us a layer at batch 1)
+        splits = min(splits, 16)
+    elif 8 < splits <= 16:
         # eight ranges merge inside a cluster; measured at batch 8, 8 k to 32 k keys: 27 / 46 / 86 against 30 / 49 / 88 us
         # with nine; at batch 2 and 4, context 4,090, against sixteen ranges and the combine kernel: 2.768 / 2.793 against
         # 2.782 / 2.861 ms a step
@@ -239,6 +244,7 @@ def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start
                                        ops.fault_words(q.device), _stream()), "attn_prefill")
 
 
+CLUSTER16_MAX = int(os.environ.get("TENSORLINE_B200_CLUSTER16_MAX", "12"))   # (request, KV head) pairs up to which 16 ranges merge in a cluster; 0: never
 TMA_DECODE = os.environ.get("TENSORLINE_B200_TMA_DECODE", "1") != "0"   # 0: cp.async loads only (A/B timing)
 TMA_DECODE_MIN_BATCH = int(os.environ.get("TENSORLINE_B200_TMA_DECODE_MIN_BATCH", "1"))   # fewer requests: cp.async loads
 CLUSTER_MERGE = os.environ.get("TENSORLINE_B200_CLUSTER_MERGE", "1") != "0"   # 0: partials + combine kernel (A/B timing)
@@ -268,7 +274,9 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
     use_tma = (TMA_DECODE and B >= TMA_DECODE_MIN_BATCH if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64
     if rope is not None and not use_tma:
         raise KernelError("attn_decode: the rotary step folds into the TMA kernel only")
-    can_cluster = use_tma and 2 <= splits <= 8 and nq // nkv <= 16
+    # up to 8 ranges in a cluster of the portable size; 9 to 16 (this GPU's limit) while the clusters are few enough to be
+    # placed at once (14 of them fit)
+    can_cluster = use_tma and nq // nkv <= 16 and (2 <= splits <= 8 or (9 <= splits <= 16 and B * nkv <= CLUSTER16_MAX))
     use_cluster = can_cluster and (CLUSTER_MERGE if cluster is None else cluster)
     if splits > 1 and not use_cluster:
         if part_o is None or part_o.numel() < B * nq * splits * d or part_o.dtype != torch.float32:

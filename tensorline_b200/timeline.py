@@ -83,12 +83,14 @@ def table(kernels: list) -> str:
                      f"{us(b[:, 4].min()):7.2f}..{us(b[:, 4].max()):7.2f}   {gap}")
         prev_last = l_max
         d = b.double()
-        if label.startswith("attn") and bool((b[:, 7] > 0).any()):
+        if label.startswith("attn"):
+            if not bool((b[:, 7] > 0).any()):               # no cluster: the ranges' parts go to a combine kernel
+                continue
             m = lambda x: f"{float(x.median()) / 1e3:.2f}"
             lines.append(f"          a block (medians): wait -> first product {m(d[:, 2] - d[:, 1])}, last stage -> worked through "
                          f"{m(d[:, 5] - d[:, 3])}, -> parts combined {m(d[:, 6] - d[:, 5])}, cluster barrier {m(d[:, 7] - d[:, 6])}, "
                          f"merge and store {m(d[:, 4] - d[:, 7])}")
-        elif bool((b[:, 5] > 0).any()):
+        if not label.startswith("attn") and bool((b[:, 5] > 0).any()):
             m = lambda x: f"{float(x.median()) / 1e3:.2f}"
             lines.append(f"          a block (medians, normed operand): wait -> rstd known {m(d[:, 5] - d[:, 1])}, -> raw tile landed "
                          f"{m(d[:, 6] - d[:, 1])}, -> operand tile made {m(d[:, 7] - d[:, 1])}, -> first product {m(d[:, 2] - d[:, 1])}")

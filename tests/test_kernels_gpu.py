@@ -414,7 +414,7 @@ def test_attention_over_a_long_context(window):
 @pytest.mark.parametrize("nq,nkv,d", [(7, 1, 128), (16, 1, 128), (6, 2, 64), (5, 5, 128), (12, 3, 192)])
 def test_decode_cluster_merge_for_every_number_of_ranges(nq, nkv, d):
     """The key ranges of a (request, KV head) merged inside a thread-block cluster: every block sends its share of each
-    column range to the block that finishes it.  2 to 8 ranges (column ranges that do not divide the head size among
+    column range to the block that finishes it.  2 to 16 ranges (column ranges that do not divide the head size among
     them), groups of 1 to 16 heads, and beside the long request a short one whose later ranges hold no key at all
     (those blocks send weight zero).  Against the plain formula in float64, and within a last bit of the combine kernel."""
     from tensorline_b200 import ops_attention, ops_gemm
@@ -444,10 +444,10 @@ def test_decode_cluster_merge_for_every_number_of_ranges(nq, nkv, d):
     qd = q.reshape(B, nq * d).cuda()
     args = (qd, nq * d, None, kd, vd, table, ps, i32(list(range(B))), i32([n - 1 for n in lens]), i32(list(range(B))))
     tiles = -(-max(lens) // 64)
-    for ranges in range(2, 9):
+    for ranges in range(2, 17):                              # 9 to 16: clusters beyond the portable size, few requests only
         chunk = -(-tiles // ranges) * 64
         splits = -(-tiles * 64 // chunk)
-        if not 2 <= splits <= 8:
+        if not 2 <= splits <= 16:
             continue
         po = torch.full((B, nq, splits, d), float("nan"), device="cuda")
         pml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")

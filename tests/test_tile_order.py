@@ -81,5 +81,5 @@ def test_key_ranges_of_a_decode_step_never_exceed_the_block_table_copy():
                     assert chunk * splits >= span, (page, span, batch, chunk, splits)
                     assert chunk * (splits - 1) < -(-span // KEY_TILE) * KEY_TILE          # no empty range
     # the cases that used to fail: the GPU is full, so one range took the whole span
-    assert plan_splits(64, 4, 7, 32768, 128, page_size=8, sms=148) == (12288, 3)
-    assert plan_splits(64, 4, 7, 65536, 128, page_size=16, sms=148) == (24576, 3)
+    assert plan_splits(64, 4, 7, 32768, 128, page_size=8, sms=148) == (8192, 4)
+    assert plan_splits(64, 4, 7, 65536, 128, page_size=16, sms=148) == (16384, 4)
