@@ -550,8 +550,12 @@ constexpr int TMA_CS_OFFSET = TMA_BAR_OFFSET + 128;              // room for 2 *
 // finished writes here while this one may still be loading keys.
 constexpr int TMA_RECV_OFFSET = TMA_CS_OFFSET + D * 4;
 constexpr int TMA_MAX_RANGES = 16;                               // key ranges of a cluster: 8 is the portable size, 16 this GPU's
-constexpr int TMA_RECV_ML = 16 * (D + TMA_MAX_RANGES) * 4;
-constexpr int TMA_TAB_OFFSET = TMA_RECV_OFFSET + TMA_RECV_ML + TMA_MAX_RANGES * 16 * 2 * 4;
+// The receive area is as large as the launch's number of ranges asks (none without a cluster), the table copy follows it:
+// with 8 ranges and a table of up to 400 pages two blocks still share an SM.
+__host__ __device__ constexpr int tma_recv_ml_offset(int ranges) { return TMA_RECV_OFFSET + 16 * (D + ranges) * 4; }
+__host__ __device__ constexpr int tma_tab_offset(int ranges) {
+    return ranges > 0 ? tma_recv_ml_offset(ranges) + ranges * 16 * 2 * 4 : TMA_RECV_OFFSET;
+}
 #ifndef TL_TMA_COPY_WARPS
 #define TL_TMA_COPY_WARPS 2
 #endif
@@ -559,7 +563,7 @@ constexpr int TMA_COPY_WARPS = TL_TMA_COPY_WARPS;
 constexpr int TMA_DEC_THREADS = 128 + 32 * TMA_COPY_WARPS;       // four compute warps and the copy warps
 static_assert(2 * DEC_STAGES * 8 + 8 <= 128, "the barrier area holds at most 7 stages");
 constexpr int TMA_MERGE_OK = (TMA_Q_OFFSET >= DECODE_MERGE_SMEM + 6 * 16 * 4) ? 1 : 0;
-static_assert(TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024 <= 227 * 1024, "the decode block does not fit an SM's shared memory");
+static_assert(tma_tab_offset(TMA_MAX_RANGES) + DECODE_MAX_TAB * 4 + 1024 <= 227 * 1024, "the decode block does not fit an SM's shared memory");
 static_assert(TMA_MERGE_OK == 1, "the stage buffers must hold the merge area");
 constexpr long long TMA_WAIT_CYCLES = 4000000000LL;
 
@@ -613,7 +617,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + TMA_BAR_OFFSET);  // [DEC_STAGES]: the stage's copies have landed
     uint64_t* empty = full + DEC_STAGES;                                   // [DEC_STAGES]: the four compute warps are done with it
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + DEC_STAGES);
-    int* stab = reinterpret_cast<int*>(tiles + TMA_TAB_OFFSET);
+    int* stab = reinterpret_cast<int*>(tiles + tma_tab_offset(CLUSTER ? A.splits : 0));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) tl_stamp(A.trace, 0);
     const int g = A.nq / A.nkv, m_tiles = (g + 15) / 16;
@@ -858,7 +862,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int ns = A.splits, cpc = (D + ns - 1) / ns;      // CLUSTER: block s finishes columns [s * cpc, + cpc)
     float* recvO = reinterpret_cast<float*>(tiles + TMA_RECV_OFFSET);
-    float* recvML = reinterpret_cast<float*>(tiles + TMA_RECV_OFFSET + TMA_RECV_ML);
+    float* recvML = reinterpret_cast<float*>(tiles + tma_recv_ml_offset(A.splits));
     const int rows = min(16, g - mt * 16);
     for (int col = tid; col < D; col += 128) {             // a column a thread: the block's result, sent where it is finished
         float* dst_o = nullptr;
@@ -1123,15 +1127,15 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
     }
     const int tab_entries = chunk / page_size;
     if (tab_entries > DECODE_MAX_TAB) return 1;
-    const int smem = TMA_TAB_OFFSET + tab_entries * 4 + 1024;
+    const int smem = tma_tab_offset(cluster_merge ? splits : 0) + tab_entries * 4 + 1024;
     const int dev_index = tl_device_index();
     if (dev_index < 0) return 1;
     if (!g_tma_attr_done[dev_index]) {
         cudaError_t ce = cudaFuncSetAttribute(attn_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
+                                              tma_tab_offset(TMA_MAX_RANGES) + DECODE_MAX_TAB * 4 + 1024);
         if (ce == cudaSuccess)
             ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      TMA_TAB_OFFSET + DECODE_MAX_TAB * 4 + 1024);
+                                      tma_tab_offset(TMA_MAX_RANGES) + DECODE_MAX_TAB * 4 + 1024);
         if (ce == cudaSuccess)                             // clusters of 9 to 16 blocks
             ce = cudaFuncSetAttribute(attn_decode_tma_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (ce != cudaSuccess) return (int)ce;
@@ -1188,6 +1192,17 @@ TL_EXPORT int tl_trace_set(long long* buf, int slots, int first) {
 }
 TL_EXPORT int tl_trace_next() { return g_trace.next; }
 TL_EXPORT int tl_trace_build() { return TL_TRACING; }
+
+// Dynamic shared memory of a TMA decode block that merges `cluster_ranges` key ranges inside a cluster (0: no cluster) and
+// copies `table_entries` block-table entries; -1 where this head size has no TMA kernel.  Two blocks share an SM (the plan
+// of the key ranges counts on it) while twice this plus 2 KB stays within the SM's 228 KB.
+TL_EXPORT int tl_attn_decode_tma_smem(int cluster_ranges, int table_entries) {
+#if HEAD_DIM % 64 == 0
+    return tma_tab_offset(cluster_ranges) + table_entries * 4 + 1024;
+#else
+    return -1;
+#endif
+}
 
 TL_EXPORT int tl_attn_decode_tma(const void* q, int q_stride, void* out, const void* k_pages, const void* v_pages,
                                  long long total_pages, const int* table, int max_pages, int page_size,

@@ -183,3 +183,21 @@ def test_decode_graph_at_these_sizes_agrees_with_the_32_bit_engine_and_the_plain
         got16 = torch.stack([out["bfloat16"][0][i], out["bfloat16"][2][i]])
         assert float((got32 - want).abs().max()) <= 2e-4 * max(1.0, scale)
         assert float((got16 - want).abs().max()) <= BF16_MODEL_REL * scale
+
+
+def test_two_decode_attention_blocks_share_an_sm_at_the_measured_sizes():
+    """The plan of the key ranges counts on two blocks an SM.  A block's shared memory grows with the cluster's number of
+    ranges (the receive area) and with its block-table copy, and 64 bytes too many halve the occupancy (it happened:
+    32B sizes, attention 26 instead of 16 us).  The launches of the measured configurations stay within the limit."""
+    import ctypes
+    from tensorline_b200 import ops_attention
+    lib = ops_attention.attn_lib(128)
+    lib.tl_attn_decode_tma_smem.argtypes = [ctypes.c_int, ctypes.c_int]
+    lib.tl_attn_decode_tma_smem.restype = ctypes.c_int
+    per_sm = 228 * 1024
+    for name, batch, nkv, group, context in (("7B", 8, 4, 7, 4096), ("7B", 1, 4, 7, 4096), ("7B", 4, 4, 7, 4096), ("7B", 16, 4, 7, 4096),
+                                             ("14B", 8, 8, 5, 4096), ("32B", 8, 8, 5, 3072), ("32B", 1, 8, 5, 3072), ("7B", 8, 4, 7, 32768)):
+        chunk, splits = ops_attention.plan_splits(batch, nkv, group, context, 128, page_size=16)
+        ranges = splits if 2 <= splits <= 16 else 0
+        smem = lib.tl_attn_decode_tma_smem(ranges, chunk // 16)
+        assert 2 * (smem + 1024) <= per_sm, (name, batch, context, chunk, splits, smem)
