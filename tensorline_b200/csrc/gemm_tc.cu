@@ -653,6 +653,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
     constexpr int SMEM_PLAIN = STAGES * (BM + BN) * BK * 2 + 1024 + (3 * STAGES + 2) * 8 + 32 + BN * 4;
     constexpr int SMEM_MAX = SMEM_PLAIN + RAW;
     const int SMEM = SMEM_PLAIN + (G.nx != nullptr ? RAW : 0);
+    // two blocks of the few-token tiles share an SM (the plan of the K ranges and the ring depth count on it)
+    static_assert(BN > 64 || 2 * ((BN == 16 ? SMEM_MAX : SMEM_PLAIN) + 1024) <= 228 * 1024,
+                  "two blocks of this tile no longer fit an SM's shared memory");     // 16 tokens: with the norm fold too
     static bool attr_set[TL_MAX_DEVICES] = {};
     const int dev = tl_device_index();
     if (dev < 0) return 1;
