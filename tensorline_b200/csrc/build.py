@@ -59,7 +59,7 @@ def build_dir() -> Path:
     for d in cands:
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".w{os.getpid()}"
+            probe = d / f".w{os.getpid()}_{threading.get_ident()}"      # several threads may build at once
             probe.write_bytes(b"")
             probe.unlink()
             return d
