@@ -666,7 +666,7 @@ def test_two_block_product_with_the_activation_in_its_epilogue(T, I, K):
 
 
 @pytest.mark.parametrize("T,N,K,rows", [(8, 3584, 3584, None), (5, 264, 2056, None), (37, 4608, 1024, None), (64, 2560, 520, None),
-                                         (16, 1152, 648, None)])
+                                         (16, 1152, 648, None), (32, 4608, 3584, None), (24, 1152, 2056, None), (17, 37888, 3584, None)])
 @pytest.mark.parametrize("wdt", [torch.bfloat16, torch.float32])
 def test_product_that_normalises_its_operand_on_the_fly(T, N, K, rows, wdt):
     """The few-token product fed with the recipe of a norm's result (residual stream, partial sums of squares, norm
