@@ -456,6 +456,9 @@ def _single_token_requests(ctx, device, group: int, nkv: int = 1, sms: int | Non
         if ones and len(ones) < B and B < 1 << 15 and span >= SINGLES_MIN_KEYS and (span >= SINGLES_RATIO * rest_span or many) and \
                 all((ctx.h_q_start[b + 1] - ctx.h_q_start[b]) * group < KEY_TILE << 16 for b in range(B)):
             n = len(ones)
+            # longest context first: the decode kernel's blocks start in this order, one (request, KV head) each when
+            # the GPU is full, and a long one that started last would run on alone
+            ones.sort(key=lambda b: -ctx.h_start_pos[b])
             packed = torch.tensor([ctx.h_q_start[b] for b in ones] + [ctx.h_start_pos[b] for b in ones] +
                                   [ctx.h_slots[b] for b in ones], dtype=torch.int32).to(device, non_blocking=True)
             found = {"set": frozenset(ones), "rows": packed[:n], "start_pos": packed[n:2 * n], "slots": packed[2 * n:],

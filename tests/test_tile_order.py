@@ -42,8 +42,8 @@ def test_which_single_tokens_of_a_mixed_step_leave_the_portion_kernel():
     ctx = _ctx([(4000, 1), (0, 300), (50, 1), (2000, 1)])
     found = _single_token_requests(ctx, "cpu", 7)
     assert found["set"] == frozenset({0, 2, 3}) and found["span"] == 4001
-    assert found["rows"].tolist() == [0, 301, 302]
-    assert found["start_pos"].tolist() == [4000, 50, 2000] and found["slots"].tolist() == [10, 12, 13]
+    assert found["rows"].tolist() == [0, 302, 301]                              # the longest context first
+    assert found["start_pos"].tolist() == [4000, 2000, 50] and found["slots"].tolist() == [10, 13, 12]
     assert _single_token_requests(ctx, "cpu", 7) is found                       # once a step
     # the portion reads about as many keys as the longest single token: one kernel for all
     assert _single_token_requests(_ctx([(4000, 1), (2048, 2041)]), "cpu", 7) is None
