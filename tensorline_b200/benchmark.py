@@ -19,7 +19,8 @@ uniform in [64, 512], one arrival per engine step, prompts cut into portions of 
 `Engine.add_request` / `Engine.step`; `value` is generated tokens a second of wall-clock time, `step_kinds`
 the mean time of a step by what it held, `preemptions` how often the scheduler had to recompute a request.
 
-`--profile`: after the measurement, one eager decode step and one prompt step with a CUDA event after every
+`--profile`: after the measurement, one eager decode step and one prompt step (with `--workload mix`: one mixed step
+of 48 single tokens beside a 464-token portion) with a CUDA event after every
 kernel launch of this package and every library product; prints milliseconds per kernel class to stderr and
 adds them to the line as `profile`.
 
@@ -354,6 +355,61 @@ def profile_steps(eng, vocab, batch, ctx0):
     return {what: {name: round(ms, 4) for name, (_, ms) in table.items()} for what, table in out.items()}
 
 
+def profile_mixed_step(eng, vocab, singles=48, contexts=(300, 2500), cached=1024, portion=464):
+    """Milliseconds per kernel class of one mixed step as the continuous-batching mix has them: `singles` requests
+    that bring one token each, at contexts drawn from `contexts`, beside a prompt portion of `portion` tokens on
+    `cached` earlier ones.  The step is run eagerly five times for its time (the requests' positions are put back
+    between the runs, so every run writes the same cache rows) and once more with an event after every launch."""
+    import torch
+    from tensorline_b200 import ops
+    from tensorline_b200.engine.runner import StepEntry
+    runner, cache = eng.runner, eng.cache
+    g = torch.Generator().manual_seed(3)
+    ctxs = torch.randint(contexts[0], contexts[1] + 1, (singles,), generator=g).tolist()
+    reqs = [(f"mixs{i}", torch.randint(0, vocab, (c,), generator=g).tolist()) for i, c in enumerate(ctxs)]
+    fill_context(eng, reqs, chunk=512)
+    ptoks = torch.randint(0, vocab, (cached + portion,), generator=g).tolist()
+    fill_context(eng, [("mixp", ptoks[:cached])], chunk=512)
+    for (rid, _), c in zip(reqs, ctxs):
+        assert cache.grow(rid, c, c + 1)
+    assert cache.grow("mixp", cached, cached + portion)
+    entries = [StepEntry(rid, [7], [0]) for rid, _ in reqs] + [StepEntry("mixp", ptoks[cached:], [portion - 1])]
+    start = dict(runner.positions)
+
+    def step():
+        runner.positions.update(start)
+        runner.step(entries)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 5
+    ops.start_profile()
+    step()
+    table = ops.stop_profile()
+    # the portion's kernel and the single tokens' decode kernel run side by side on two streams, and the events lie on
+    # both: only the sum of the two classes is a time
+    att = [k for k in table if k.startswith("attn_")]
+    if len(att) > 1:
+        table["attention (" + " + ".join(sorted(att)) + ", side by side)"] = (sum(table[k][0] for k in att), sum(table[k][1] for k in att))
+        for k in att:
+            del table[k]
+    for rid, _ in reqs + [("mixp", None)]:
+        cache.release(rid); runner.end_request(rid)
+    total = sum(t for _, t in table.values())
+    what = f"mixed step, {singles} single tokens at {contexts[0]}..{contexts[1]} keys beside {portion} tokens on {cached}"
+    print(f"[profile] {what}: {ms:.3f} ms a step; with an event after every launch {total:.3f} ms in "
+          f"{sum(c for c, _ in table.values())} launches", file=sys.stderr)
+    for name, (calls, t) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+        print(f"[profile]   {name:62s} {calls:5d} calls {t:9.3f} ms {100 * t / total:5.1f} %", file=sys.stderr)
+    return {"ms_per_step": round(ms, 4), "classes": {name: round(t, 4) for name, (_, t) in table.items()}}
+
+
 def run_ours(a):
     import torch
     from tensorline_b200 import Engine, Qwen2Config
@@ -416,6 +472,8 @@ def run_ours(a):
         line["mix"]["total_tok_s"] = round(line["mix"]["total_tok_s"], 1)
         from tensorline_b200 import ops
         line["gpu_launches"] = ops.launch_count()
+        if a.profile:
+            line["profile"] = {"mixed_step": profile_mixed_step(eng, V)}
         print(json.dumps(line))
         return 0
     if a.timeline:
