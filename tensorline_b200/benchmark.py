@@ -565,7 +565,7 @@ def main(argv=None):
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="decode / prefill: a short run of that phase alone (for profilers); prints its own line")
     ap.add_argument("--batch", type=int, default=8, help="decode batch of the main measurement")
-    ap.add_argument("--profile", action="store_true", help="add milliseconds per kernel class of one eager decode and one prompt step")
+    ap.add_argument("--profile", action="store_true", help="add milliseconds per kernel class of one eager decode and one prompt step (mix: of one mixed step)")
     ap.add_argument("--timeline", action="store_true",
                     help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
